@@ -1,0 +1,90 @@
+"""
+ctypes binding of libattorch_b200.so (declared in include/attorch_b200.h).
+
+There is no fallback: if the library is missing or does not load, every entry point raises.
+"""
+
+import ctypes
+from pathlib import Path
+from typing import Optional
+
+PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = PKG_DIR / 'libattorch_b200.so'
+
+# Element type ids (include/attorch_b200.h).
+F32, F16, BF16 = 0, 1, 2
+
+FLAG_FORCE_GENERIC = 1
+FLAG_FORCE_TCGEN05 = 2
+FLAG_FORCE_STREAMK = 4
+FLAG_NO_STREAMK = 8
+
+PATH_TCGEN05, PATH_STREAMK, PATH_GENERIC = 1, 2, 3
+
+_i64 = ctypes.c_int64
+_int = ctypes.c_int
+_ptr = ctypes.c_void_p
+_f32 = ctypes.c_float
+
+# name -> (restype, argtypes); one entry per symbol the header declares.
+SIGNATURES = {
+    'ab200_version': (_int, []),
+    'ab200_error_string': (ctypes.c_char_p, [_int]),
+    'ab200_last_path': (_int, []),
+    'ab200_launch_count': (_i64, []),
+    'ab200_forward_workspace_bytes': (_i64, [_i64, _i64, _i64]),
+    'ab200_linear_forward': (_int, [_ptr, _ptr, _ptr, _ptr, _ptr,
+                                    _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                                    _int, _int, _int, _int, _f32,
+                                    _ptr, _i64, _ptr, _ptr, _int]),
+    'ab200_act_backward_workspace_bytes': (_i64, [_i64, _i64]),
+    'ab200_act_backward': (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64,
+                                  _int, _int, _int, _f32, _ptr, _i64, _ptr]),
+    'ab200_linear_backward_input': (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64,
+                                           _i64, _i64, _i64, _i64, _i64,
+                                           _int, _int, _ptr, _ptr, _int]),
+    'ab200_linear_backward_weight': (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64,
+                                            _i64, _i64, _i64, _i64, _i64,
+                                            _int, _int, _ptr, _ptr, _int]),
+    'ab200_cast_2d': (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _int, _int, _ptr]),
+}
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+class LibraryError(RuntimeError):
+    """Raised when libattorch_b200.so is missing, fails to load, or a call is rejected."""
+
+
+def load() -> ctypes.CDLL:
+    """Loads the library once and attaches the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise LibraryError(
+            f'{LIB_PATH} not found: build it with `python -m attorch_b200.build` '
+            '(needs nvcc with sm_100a support). There is no CPU or PyTorch fallback.')
+    try:
+        lib = ctypes.CDLL(str(LIB_PATH))
+    except OSError as error:
+        raise LibraryError(f'cannot load {LIB_PATH}: {error}') from error
+    for name, (restype, argtypes) in SIGNATURES.items():
+        try:
+            func = getattr(lib, name)
+        except AttributeError as error:
+            raise LibraryError(f'{LIB_PATH} does not export {name}') from error
+        func.restype = restype
+        func.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def error_string(code: int) -> str:
+    return load().ab200_error_string(code).decode()
+
+
+def check(code: int, what: str) -> None:
+    """Raises LibraryError for a negative return code of an entry point."""
+    if code != 0:
+        raise LibraryError(f'{what} failed: {error_string(code)} (code {code})')

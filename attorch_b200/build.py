@@ -1,0 +1,88 @@
+"""
+Builds libattorch_b200.so in-tree with nvcc for sm_100a.
+
+Run as ``python -m attorch_b200.build`` (add ``--force`` to rebuild, ``--verbose`` for
+``-Xptxas -v`` output).  The library links only against the CUDA runtime; it has no torch or
+Python dependency, so the same file serves ctypes (this package) and any other C-ABI binding.
+"""
+
+import argparse
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+CSRC = PKG_DIR / 'csrc'
+INCLUDE = PKG_DIR.parent / 'include'
+LIB_PATH = PKG_DIR / 'libattorch_b200.so'
+STAMP_PATH = PKG_DIR / '.libattorch_b200.stamp'
+
+SOURCES = ['api.cu']
+NVCC_FLAGS = [
+    '-std=c++20', '-O3', '-lineinfo',
+    '-gencode', 'arch=compute_100a,code=sm_100a',
+    '-shared', '-Xcompiler', '-fPIC',
+    '--expt-relaxed-constexpr',
+    '-cudart', 'shared',
+]
+
+
+def find_nvcc() -> str:
+    """Locates nvcc: $CUDA_HOME/bin, the default toolkit location, then PATH."""
+    candidates = []
+    if os.environ.get('CUDA_HOME'):
+        candidates.append(Path(os.environ['CUDA_HOME']) / 'bin' / 'nvcc')
+    candidates.append(Path('/usr/local/cuda/bin/nvcc'))
+    for cand in candidates:
+        if cand.exists():
+            return str(cand)
+    found = shutil.which('nvcc')
+    if found is None:
+        raise RuntimeError('nvcc not found; set CUDA_HOME')
+    return found
+
+
+def source_digest() -> str:
+    """Hash of every file the library is built from, plus the flags."""
+    h = hashlib.sha256()
+    files = sorted(CSRC.glob('*.cu')) + sorted(CSRC.glob('*.cuh')) + sorted(INCLUDE.glob('*.h'))
+    for path in files:
+        h.update(path.name.encode())
+        h.update(path.read_bytes())
+    h.update(' '.join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def is_current() -> bool:
+    return (LIB_PATH.exists() and STAMP_PATH.exists()
+            and STAMP_PATH.read_text().strip() == source_digest())
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compiles the shared library if it is missing or older than its sources."""
+    if not force and is_current():
+        return LIB_PATH
+    cmd = [find_nvcc(), *NVCC_FLAGS, f'-I{INCLUDE}', f'-I{CSRC}']
+    if verbose:
+        cmd += ['-Xptxas', '-v']
+    cmd += [str(CSRC / src) for src in SOURCES]
+    cmd += ['-o', str(LIB_PATH)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or proc.returncode != 0:
+        sys.stderr.write(proc.stdout)
+        sys.stderr.write(proc.stderr)
+    if proc.returncode != 0:
+        raise RuntimeError(f'nvcc failed with exit code {proc.returncode}')
+    STAMP_PATH.write_text(source_digest() + '\n')
+    return LIB_PATH
+
+
+if __name__ == '__main__':
+    parser = argparse.ArgumentParser(description=__doc__)
+    parser.add_argument('--force', action='store_true')
+    parser.add_argument('--verbose', action='store_true')
+    args = parser.parse_args()
+    print(build(force=args.force, verbose=args.verbose))

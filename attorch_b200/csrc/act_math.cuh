@@ -1,0 +1,197 @@
+// Device-side activation functions and their derivatives for the fused linear layer.
+//
+// The set, the formulas and the conventions at the piecewise switch points follow
+// attorch/act_kernels.py:14-628 of the reference (forward functions and *_grad functions;
+// dispatch order in apply_act_func 631-732 and apply_act_func_grad 735-837).  Everything is
+// evaluated in fp32.  Where the reference's literal formula overflows (logsigmoid, softplus,
+// mish and mish' for |x| >~ 88) an algebraically equal, overflow-free form is used.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace ab200 {
+
+// Activation ids shared with the host side (attorch_b200/acts.py keeps the same table).
+enum Act : int {
+  ACT_NONE = 0,
+  ACT_SIGMOID = 1,
+  ACT_LOGSIGMOID = 2,
+  ACT_TANH = 3,
+  ACT_RELU = 4,
+  ACT_GELU = 5,
+  ACT_GELUAPPROX = 6,
+  ACT_SILU = 7,
+  ACT_RELU6 = 8,
+  ACT_HARDSIGMOID = 9,
+  ACT_HARDTANH = 10,
+  ACT_HARDSWISH = 11,
+  ACT_SELU = 12,
+  ACT_MISH = 13,
+  ACT_SOFTPLUS = 14,
+  ACT_SOFTSIGN = 15,
+  ACT_TANHSHRINK = 16,
+  ACT_LEAKY_RELU = 17,
+  ACT_ELU = 18,
+  ACT_CELU = 19,
+  ACT_HARDSHRINK = 20,
+  ACT_SOFTSHRINK = 21,
+  ACT_COUNT = 22
+};
+
+namespace actm {
+
+__device__ __forceinline__ float sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+// tanh as 2*sigmoid(2x) - 1 (act_kernels.py:71-81).
+__device__ __forceinline__ float tanh_(float x) { return 2.0f * sigmoid(2.0f * x) - 1.0f; }
+// log(1 + e^x) without overflow.
+__device__ __forceinline__ float softplus(float x) {
+  return fmaxf(x, 0.0f) + log1pf(__expf(-fabsf(x)));
+}
+
+constexpr float kSeluScale = 1.0507009873554805f;
+constexpr float kSeluAlpha = 1.6732632423543772f;
+constexpr float kRsqrt2 = 0.707106781f;
+constexpr float kRsqrt2Pi = 0.39894228f;
+constexpr float kSqrt2OverPi = 0.7978845608f;
+
+template <int A>
+__device__ __forceinline__ float fwd(float x, float p) {
+  if constexpr (A == ACT_NONE) return x;
+  if constexpr (A == ACT_SIGMOID) return sigmoid(x);
+  if constexpr (A == ACT_LOGSIGMOID) return fminf(x, 0.0f) - log1pf(__expf(-fabsf(x)));
+  if constexpr (A == ACT_TANH) return tanh_(x);
+  if constexpr (A == ACT_RELU) return fmaxf(0.0f, x);
+  if constexpr (A == ACT_GELU) return x * 0.5f * (1.0f + erff(kRsqrt2 * x));
+  if constexpr (A == ACT_GELUAPPROX)
+    return x * 0.5f * (1.0f + tanh_(kSqrt2OverPi * x * (1.0f + 0.044715f * x * x)));
+  if constexpr (A == ACT_SILU) return x * sigmoid(x);
+  if constexpr (A == ACT_RELU6) return fminf(fmaxf(0.0f, x), 6.0f);
+  if constexpr (A == ACT_HARDSIGMOID) return fmaxf(0.0f, fminf(1.0f, x / 6.0f + 0.5f));
+  if constexpr (A == ACT_HARDTANH) return fmaxf(-1.0f, fminf(1.0f, x));
+  if constexpr (A == ACT_HARDSWISH) return x * fminf(fmaxf(0.0f, x + 3.0f), 6.0f) / 6.0f;
+  if constexpr (A == ACT_SELU)
+    return kSeluScale * (fmaxf(0.0f, x) + fminf(0.0f, kSeluAlpha * (__expf(x) - 1.0f)));
+  if constexpr (A == ACT_MISH) return x * tanh_(softplus(x));
+  if constexpr (A == ACT_SOFTPLUS) return softplus(x);
+  if constexpr (A == ACT_SOFTSIGN) return x / (1.0f + fabsf(x));
+  if constexpr (A == ACT_TANHSHRINK) return x - tanh_(x);
+  if constexpr (A == ACT_LEAKY_RELU) return fmaxf(0.0f, x) + p * fminf(0.0f, x);
+  if constexpr (A == ACT_ELU) return x <= 0.0f ? p * (__expf(x) - 1.0f) : x;
+  if constexpr (A == ACT_CELU)
+    return fmaxf(0.0f, x) + fminf(0.0f, p * (__expf(__fdividef(x, p)) - 1.0f));
+  if constexpr (A == ACT_HARDSHRINK) return fabsf(x) <= p ? 0.0f : x;
+  if constexpr (A == ACT_SOFTSHRINK) return x > p ? x - p : (x < -p ? x + p : 0.0f);
+  return x;
+}
+
+// d act(x) / dx.
+template <int A>
+__device__ __forceinline__ float grad(float x, float p) {
+  if constexpr (A == ACT_NONE) return 1.0f;
+  if constexpr (A == ACT_SIGMOID) {
+    const float s = sigmoid(x);
+    return s * (1.0f - s);
+  }
+  if constexpr (A == ACT_LOGSIGMOID) return sigmoid(-x);  // 1 / (1 + e^x)
+  if constexpr (A == ACT_TANH) {
+    const float t = tanh_(x);
+    return 1.0f - t * t;
+  }
+  if constexpr (A == ACT_RELU) return x <= 0.0f ? 0.0f : 1.0f;
+  if constexpr (A == ACT_GELU)
+    return 0.5f * (1.0f + erff(kRsqrt2 * x)) + x * kRsqrt2Pi * __expf(-0.5f * x * x);
+  if constexpr (A == ACT_GELUAPPROX) {
+    const float t = tanh_(kSqrt2OverPi * x * (1.0f + 0.044715f * x * x));
+    return 0.5f * ((1.0f + t) +
+                   x * (1.0f - t * t) * kSqrt2OverPi * (1.0f + 3.0f * 0.044715f * x * x));
+  }
+  if constexpr (A == ACT_SILU) {
+    const float s = sigmoid(x);
+    return s * (x * (1.0f - s) + 1.0f);
+  }
+  if constexpr (A == ACT_RELU6) return (x > 0.0f && x < 6.0f) ? 1.0f : 0.0f;
+  if constexpr (A == ACT_HARDSIGMOID) return (x > -3.0f && x < 3.0f) ? (1.0f / 6.0f) : 0.0f;
+  if constexpr (A == ACT_HARDTANH) return (x > -1.0f && x < 1.0f) ? 1.0f : 0.0f;
+  if constexpr (A == ACT_HARDSWISH) return x < -3.0f ? 0.0f : (x <= 3.0f ? x / 3.0f + 0.5f : 1.0f);
+  if constexpr (A == ACT_SELU) return kSeluScale * (x <= 0.0f ? kSeluAlpha * __expf(x) : 1.0f);
+  if constexpr (A == ACT_MISH) {
+    // tanh(sp) + x * sigmoid(x) * (1 - tanh(sp)^2), equal to the reference's rational form.
+    const float t = tanh_(softplus(x));
+    return t + x * sigmoid(x) * (1.0f - t * t);
+  }
+  if constexpr (A == ACT_SOFTPLUS) return sigmoid(x);
+  if constexpr (A == ACT_SOFTSIGN) {
+    const float d = 1.0f + fabsf(x);
+    return 1.0f / (d * d);
+  }
+  if constexpr (A == ACT_TANHSHRINK) {
+    const float t = tanh_(x);
+    return t * t;  // 1 - (1 - tanh^2)
+  }
+  if constexpr (A == ACT_LEAKY_RELU) return x <= 0.0f ? p : 1.0f;
+  if constexpr (A == ACT_ELU) return x <= 0.0f ? p * __expf(x) : 1.0f;
+  if constexpr (A == ACT_CELU) return x <= 0.0f ? __expf(__fdividef(x, p)) : 1.0f;
+  if constexpr (A == ACT_HARDSHRINK) return fabsf(x) <= p ? 0.0f : 1.0f;
+  if constexpr (A == ACT_SOFTSHRINK) return fabsf(x) <= p ? 0.0f : 1.0f;
+  return 1.0f;
+}
+
+}  // namespace actm
+
+// Calls f.template operator()<A>() with the runtime id turned into a compile-time constant,
+// so that loops over elements sit inside the switch and not the other way round.
+template <class F>
+__device__ __forceinline__ void dispatch_act(int act, F&& f) {
+  switch (act) {
+#define AB200_CASE(A) \
+  case A:             \
+    f.template operator()<A>(); \
+    break;
+    AB200_CASE(ACT_SIGMOID)
+    AB200_CASE(ACT_LOGSIGMOID)
+    AB200_CASE(ACT_TANH)
+    AB200_CASE(ACT_RELU)
+    AB200_CASE(ACT_GELU)
+    AB200_CASE(ACT_GELUAPPROX)
+    AB200_CASE(ACT_SILU)
+    AB200_CASE(ACT_RELU6)
+    AB200_CASE(ACT_HARDSIGMOID)
+    AB200_CASE(ACT_HARDTANH)
+    AB200_CASE(ACT_HARDSWISH)
+    AB200_CASE(ACT_SELU)
+    AB200_CASE(ACT_MISH)
+    AB200_CASE(ACT_SOFTPLUS)
+    AB200_CASE(ACT_SOFTSIGN)
+    AB200_CASE(ACT_TANHSHRINK)
+    AB200_CASE(ACT_LEAKY_RELU)
+    AB200_CASE(ACT_ELU)
+    AB200_CASE(ACT_CELU)
+    AB200_CASE(ACT_HARDSHRINK)
+    AB200_CASE(ACT_SOFTSHRINK)
+#undef AB200_CASE
+    default:
+      f.template operator()<ACT_NONE>();
+      break;
+  }
+}
+
+// In-place activation of n consecutive fp32 values.
+template <int N>
+__device__ __forceinline__ void act_fwd_inplace(float (&v)[N], int act, float p) {
+  if (act == ACT_NONE) return;
+  dispatch_act(act, [&]<int A>() {
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = actm::fwd<A>(v[i], p);
+  });
+}
+
+// g[i] *= act'(z[i]).
+template <int N>
+__device__ __forceinline__ void act_grad_mul(float (&g)[N], const float (&z)[N], int act, float p) {
+  if (act == ACT_NONE) return;
+  dispatch_act(act, [&]<int A>() {
+#pragma unroll
+    for (int i = 0; i < N; ++i) g[i] *= actm::grad<A>(z[i], p);
+  });
+}
+
+}  // namespace ab200

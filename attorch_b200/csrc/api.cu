@@ -1,0 +1,490 @@
+// C-ABI entry points of libattorch_b200.so (declared in include/attorch_b200.h): argument checks,
+// kernel selection, TMA tensor-map construction and launches.  No torch types, no allocation.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+
+#include "../../include/attorch_b200.h"
+#include "common.cuh"
+#include "gemm_tcgen05.cuh"
+#include "kernels_misc.cuh"
+
+namespace ab200 {
+namespace {
+
+thread_local int g_last_path = 0;
+thread_local int64_t g_launches = 0;
+
+// ------------------------------------------------------------------------------------------------
+// Driver entry point for tensor-map encoding, resolved through the runtime so that the library
+// does not link against libcuda.
+// ------------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 2-D map over a row-major matrix: `inner` contiguous elements per row, `outer` rows, row pitch in
+// bytes; box = box_inner x box_outer elements; 128-byte swizzle; out-of-range elements read as zero.
+int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
+              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return ERR_DRIVER;
+  const CUtensorMapDataType dt = dtype == DT_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                   : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? OK : ERR_TENSOR_MAP;
+}
+
+int sm_count() {
+  static thread_local int cached_dev = -1;
+  static thread_local int cached = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev != cached_dev) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached = n;
+    cached_dev = dev;
+  }
+  return cached;
+}
+
+bool valid_dtype(int dt) { return dt == DT_F32 || dt == DT_F16 || dt == DT_BF16; }
+bool valid_act(int act) { return act >= 0 && act < ACT_COUNT; }
+
+// A matrix operand as the GEMM sees it: `rows` x `cols` logical elements, element strides.
+struct Operand {
+  const void* ptr;
+  long long stride_row, stride_col;
+};
+
+// Can TMA address this matrix with `contig` as the unit-stride dimension?
+bool tma_ok(const void* p, long long pitch_elems, long long unit_stride, int elt) {
+  if (unit_stride != 1) return false;
+  if (reinterpret_cast<uintptr_t>(p) & 15) return false;
+  if (pitch_elems <= 0 || (pitch_elems * elt) % 16 != 0) return false;
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------------
+// tcgen05 launch
+// ------------------------------------------------------------------------------------------------
+struct TcProblem {
+  const void* a; bool a_mn; long long a_pitch;   // pitch (elements) of the strided dimension
+  const void* b; bool b_mn; long long b_pitch;
+  int op_dtype;
+  GemmArgs g;     // M, N, K and epilogue filled by the caller
+};
+
+template <class Cfg>
+int launch_cfg(const TcProblem& p, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  const uint64_t elt = Cfg::ELT;
+  int rc;
+  // K-major: inner = K, outer = M (or N); box = one 128-byte row of K x tile rows.
+  // MN-major: inner = M (or N), outer = K; box = 128 bytes of M/N x BKE rows of K.
+  if (Cfg::A_MN)
+    rc = encode_2d(&ta, p.op_dtype, p.a, p.g.M, p.g.K, p.a_pitch * elt, Cfg::MN_ATOM, Cfg::BKE);
+  else
+    rc = encode_2d(&ta, p.op_dtype, p.a, p.g.K, p.g.M, p.a_pitch * elt, Cfg::BKE, Cfg::BM);
+  if (rc != OK) return rc;
+  if (Cfg::B_MN)
+    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.N, p.g.K, p.b_pitch * elt, Cfg::MN_ATOM, Cfg::BKE);
+  else
+    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.K, p.g.N, p.b_pitch * elt, Cfg::BKE, Cfg::BN);
+  if (rc != OK) return rc;
+
+  GemmArgs g = p.g;
+  g.tiles_m = (g.M + Cfg::BM - 1) / Cfg::BM;
+  g.tiles_n = (g.N + Cfg::BN - 1) / Cfg::BN;
+  g.k_blocks = (g.K + Cfg::BKE - 1) / Cfg::BKE;
+  g.group_m = 8;
+  const uint32_t fmt = p.op_dtype == DT_F32 ? 2u : (p.op_dtype == DT_BF16 ? 1u : 0u);
+  g.idesc = ptx::make_idesc(fmt, Cfg::A_MN ? 1u : 0u, Cfg::B_MN ? 1u : 0u, Cfg::BM, Cfg::BN);
+
+  static thread_local bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::SMEM_BYTES) != cudaSuccess)
+      return ERR_LAUNCH;
+    attr_set[dev] = true;
+  }
+  const long long tiles = static_cast<long long>(g.tiles_m) * g.tiles_n;
+  const long long work = g.stream_k ? tiles * g.k_blocks : tiles;
+  const int sms = sm_count();
+  const int grid = static_cast<int>(work < sms ? work : sms);
+  if (grid <= 0) return OK;
+  gemm_tcgen05_kernel<Cfg><<<grid, Cfg::kThreads, Cfg::SMEM_BYTES, stream>>>(ta, tb, g);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
+}
+
+template <bool A_MN, bool B_MN>
+int launch_bn(const TcProblem& p, int bn, cudaStream_t stream) {
+  // A 32-wide tile is narrower than one 128-byte row of an MN-major 16-bit B operand, so it
+  // exists only for K-major B (the swap-AB kernel, whose B is the skinny activation matrix).
+  if (p.op_dtype == DT_F32) {
+    switch (bn) {
+      case 32: return launch_cfg<GemmCfg<32, 4, A_MN, B_MN>>(p, stream);
+      case 64: return launch_cfg<GemmCfg<64, 4, A_MN, B_MN>>(p, stream);
+      case 128: return launch_cfg<GemmCfg<128, 4, A_MN, B_MN>>(p, stream);
+      default: return launch_cfg<GemmCfg<256, 4, A_MN, B_MN>>(p, stream);
+    }
+  }
+  switch (bn) {
+    case 32:
+      if constexpr (!B_MN) return launch_cfg<GemmCfg<32, 2, A_MN, B_MN>>(p, stream);
+      [[fallthrough]];
+    case 64: return launch_cfg<GemmCfg<64, 2, A_MN, B_MN>>(p, stream);
+    case 128: return launch_cfg<GemmCfg<128, 2, A_MN, B_MN>>(p, stream);
+    default: return launch_cfg<GemmCfg<256, 2, A_MN, B_MN>>(p, stream);
+  }
+}
+
+int launch_tc(const TcProblem& p, int bn, cudaStream_t stream) {
+  if (!p.a_mn && p.b_mn) return launch_bn<false, true>(p, bn, stream);
+  if (!p.a_mn && !p.b_mn) return launch_bn<false, false>(p, bn, stream);
+  if (p.a_mn && p.b_mn) return launch_bn<true, true>(p, bn, stream);
+  return launch_bn<true, false>(p, bn, stream);
+}
+
+// Widest tile that still gives every SM work; otherwise the narrowest that covers N.
+int pick_bn(long long M, long long N) {
+  const long long tm = (M + 127) / 128;
+  const int sms = sm_count();
+  if (N > 128 && tm * ((N + 255) / 256) >= sms) return 256;
+  if (N > 64 && tm * ((N + 127) / 128) >= sms) return 128;
+  if (N > 128) return 256;
+  if (N > 64) return 128;
+  if (N > 32) return 64;
+  return 32;
+}
+
+int launch_any(const AnyGemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0) return OK;
+  dim3 grid((a.N + 63) / 64, (a.M + 63) / 64);
+  gemm_any_kernel<<<grid, 256, 0, stream>>>(a);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
+}
+
+bool fits_int(int64_t v) { return v >= 0 && v < (1ll << 31); }
+
+}  // namespace
+}  // namespace ab200
+
+using namespace ab200;
+
+extern "C" {
+
+int ab200_version(void) { return 1000; }
+
+const char* ab200_error_string(int code) {
+  switch (code) {
+    case OK: return "ok";
+    case ERR_NULL_POINTER: return "a required pointer is NULL";
+    case ERR_BAD_SHAPE: return "negative or inconsistent shape";
+    case ERR_BAD_DTYPE: return "unsupported element type";
+    case ERR_BAD_ACT: return "unknown activation id";
+    case ERR_BAD_STRIDE: return "operand strides or alignment not addressable by the requested kernel";
+    case ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case ERR_TENSOR_MAP: return "cuTensorMapEncodeTiled rejected the operand";
+    case ERR_LAUNCH: return "kernel launch failed";
+    case ERR_TOO_LARGE: return "a dimension exceeds 2^31 - 1";
+    case ERR_DRIVER: return "CUDA driver entry point unavailable";
+    case DEV_TIMEOUT_PRODUCER: return "device: TMA producer gave up waiting for a free stage";
+    case DEV_TIMEOUT_MMA: return "device: MMA issuer gave up waiting for operands or an accumulator";
+    case DEV_TIMEOUT_EPILOGUE: return "device: epilogue gave up waiting for an accumulator";
+    case DEV_TIMEOUT_TRANSFORM: return "device: transform warps gave up waiting";
+    default: return "unknown code";
+  }
+}
+
+int ab200_last_path(void) { return g_last_path; }
+int64_t ab200_launch_count(void) { return g_launches; }
+
+int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N) {
+  (void)K;
+  if (M <= 0 || N <= 0) return 0;
+  return M <= 128 ? M * N * 4 : 0;
+}
+
+int ab200_linear_forward(const void* x, const void* w, const void* bias, void* pre_act, void* out,
+                         int64_t M, int64_t K, int64_t N, int64_t x_stride_m, int64_t x_stride_k,
+                         int64_t w_stride_k, int64_t w_stride_n, int64_t ld_pre, int64_t ld_out,
+                         int op_dtype, int out_dtype, int bias_dtype, int act, float act_param,
+                         void* workspace, int64_t workspace_bytes, int* status, void* stream_,
+                         int flags) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || K < 0 || N < 0) return ERR_BAD_SHAPE;
+  if (!fits_int(M) || !fits_int(K) || !fits_int(N)) return ERR_TOO_LARGE;
+  if (!valid_dtype(op_dtype) || !valid_dtype(out_dtype) || (bias && !valid_dtype(bias_dtype)))
+    return ERR_BAD_DTYPE;
+  if (!valid_act(act)) return ERR_BAD_ACT;
+  if (M == 0 || N == 0) return OK;
+  if (!out || (K > 0 && (!x || !w))) return ERR_NULL_POINTER;
+  if (ld_out < N || (pre_act && ld_pre < N)) return ERR_BAD_STRIDE;
+
+  const int elt = dtype_size(op_dtype);
+  const bool tc_ok = K > 0 && tma_ok(x, x_stride_m, x_stride_k, elt) && tma_ok(w, w_stride_k, w_stride_n, elt) &&
+                     x_stride_m >= K && w_stride_k >= N;
+  if ((flags & AB200_FLAG_FORCE_TCGEN05) && !tc_ok) return ERR_BAD_STRIDE;
+  const bool use_tc = tc_ok && !(flags & AB200_FLAG_FORCE_GENERIC) && status != nullptr;
+
+  if (!use_tc) {
+    AnyGemmArgs a{};
+    a.a = x; a.sam = x_stride_m; a.sak = x_stride_k; a.a_dtype = op_dtype;
+    a.b = w; a.sbk = w_stride_k; a.sbn = w_stride_n; a.b_dtype = op_dtype;
+    a.M = static_cast<int>(M); a.N = static_cast<int>(N); a.K = static_cast<int>(K);
+    a.out = out; a.ld_out = ld_out; a.out_dtype = out_dtype;
+    a.aux = pre_act; a.ld_aux = ld_pre;
+    a.bias = bias; a.bias_dtype = bias_dtype;
+    a.act = act; a.act_param = act_param;
+    g_last_path = AB200_PATH_GENERIC;
+    return launch_any(a, stream);
+  }
+
+  TcProblem p{};
+  p.op_dtype = op_dtype;
+  GemmArgs& g = p.g;
+  g.status = status;
+  const bool skinny = ((M <= 128 && !(flags & AB200_FLAG_NO_STREAMK)) || (flags & AB200_FLAG_FORCE_STREAMK));
+  if (skinny) {
+    // Swap-AB: D'[N, M] = W^T[N, K] * X^T[K, M].  A = W (MN-major), B = X (K-major).  The fp32
+    // partial sums land in workspace as [M, N] (coalesced along N) and a finishing kernel applies
+    // bias and activation.
+    const int64_t need = M * N * 4;
+    if (workspace == nullptr || workspace_bytes < need) return ERR_WORKSPACE_TOO_SMALL;
+    if (cudaMemsetAsync(workspace, 0, need, stream) != cudaSuccess) return ERR_LAUNCH;
+    p.a = w; p.a_mn = true; p.a_pitch = w_stride_k;
+    p.b = x; p.b_mn = false; p.b_pitch = x_stride_m;
+    g.M = static_cast<int>(N); g.N = static_cast<int>(M); g.K = static_cast<int>(K);
+    g.stream_k = 1;
+    g.partial = static_cast<float*>(workspace);
+    g.ld_partial = N;
+    g.partial_transposed = 1;
+    const int bn = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
+    g_last_path = AB200_PATH_STREAMK;
+    int rc = launch_tc(p, bn, stream);
+    if (rc != OK) return rc;
+    const long long total = M * N;
+    int blocks = static_cast<int>((total + 255) / 256);
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+    streamk_finish_kernel<<<blocks, 256, 0, stream>>>(static_cast<float*>(workspace), N, static_cast<int>(M),
+                                                      static_cast<int>(N), bias, bias_dtype, pre_act, ld_pre,
+                                                      out, ld_out, out_dtype, act, act_param);
+    ++g_launches;
+    return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
+  }
+
+  p.a = x; p.a_mn = false; p.a_pitch = x_stride_m;
+  p.b = w; p.b_mn = true; p.b_pitch = w_stride_k;
+  g.M = static_cast<int>(M); g.N = static_cast<int>(N); g.K = static_cast<int>(K);
+  g.stream_k = 0;
+  g.out = out; g.ld_out = ld_out; g.out_dtype = out_dtype;
+  g.aux = pre_act; g.ld_aux = ld_pre;
+  g.bias = bias; g.bias_dtype = bias_dtype;
+  g.act = act; g.act_param = act_param;
+  g_last_path = AB200_PATH_TCGEN05;
+  return launch_tc(p, pick_bn(M, N), stream);
+}
+
+int64_t ab200_act_backward_workspace_bytes(int64_t M, int64_t N) {
+  if (M <= 0 || N <= 0) return 0;
+  return ((M + kActRows - 1) / kActRows) * N * 4;
+}
+
+int ab200_act_backward(const void* dy, const void* z, void* dz, void* db, int64_t M, int64_t N,
+                       int64_t ld_dy, int64_t ld_z, int64_t ld_dz, int dtype, int db_dtype, int act,
+                       float act_param, void* workspace, int64_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || N < 0) return ERR_BAD_SHAPE;
+  if (!fits_int(M) || !fits_int(N)) return ERR_TOO_LARGE;
+  if (!valid_dtype(dtype) || (db && !valid_dtype(db_dtype))) return ERR_BAD_DTYPE;
+  if (!valid_act(act)) return ERR_BAD_ACT;
+  if (N == 0) return OK;
+  if (M > 0 && (!dy || (act != ACT_NONE && !z))) return ERR_NULL_POINTER;
+  if (dz == nullptr && db == nullptr) return OK;
+  if (ld_dy < N || (z && ld_z < N) || (dz && ld_dz < N)) return ERR_BAD_STRIDE;
+  const int chunks = static_cast<int>((M + kActRows - 1) / kActRows);
+  float* partial = nullptr;
+  if (db != nullptr) {
+    if (M == 0) {
+      // Empty sum.
+      return cudaMemsetAsync(db, 0, N * dtype_size(db_dtype), stream) == cudaSuccess ? OK : ERR_LAUNCH;
+    }
+    if (!workspace || workspace_bytes < ab200_act_backward_workspace_bytes(M, N)) return ERR_WORKSPACE_TOO_SMALL;
+    partial = static_cast<float*>(workspace);
+  }
+  if (M == 0) return OK;
+  const int elt = dtype_size(dtype);
+  auto aligned = [&](const void* p, long long ld) {
+    return p == nullptr || ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * elt) % 16 == 0);
+  };
+  const bool vec = (N % 8 == 0) && aligned(dy, ld_dy) && aligned(z, ld_z) && aligned(dz, ld_dz);
+  dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(chunks));
+  const int Mi = static_cast<int>(M), Ni = static_cast<int>(N);
+#define AB200_LAUNCH_ACT(T)                                                                              \
+  do {                                                                                                   \
+    if (vec)                                                                                             \
+      act_backward_kernel<T, true><<<grid, 256, 0, stream>>>(static_cast<const T*>(dy), ld_dy,          \
+          static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param); \
+    else                                                                                                 \
+      act_backward_kernel<T, false><<<grid, 256, 0, stream>>>(static_cast<const T*>(dy), ld_dy,         \
+          static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param); \
+  } while (0)
+  if (dtype == DT_F32) AB200_LAUNCH_ACT(float);
+  else if (dtype == DT_F16) AB200_LAUNCH_ACT(__half);
+  else AB200_LAUNCH_ACT(__nv_bfloat16);
+#undef AB200_LAUNCH_ACT
+  ++g_launches;
+  if (cudaGetLastError() != cudaSuccess) return ERR_LAUNCH;
+  if (db != nullptr) {
+    colsum_finish_kernel<<<(Ni + 255) / 256, 256, 0, stream>>>(partial, chunks, Ni, db, db_dtype);
+    ++g_launches;
+    if (cudaGetLastError() != cudaSuccess) return ERR_LAUNCH;
+  }
+  return OK;
+}
+
+int ab200_linear_backward_input(const void* dz, const void* w, void* dx, int64_t M, int64_t K,
+                                int64_t N, int64_t dz_stride_m, int64_t dz_stride_n,
+                                int64_t w_stride_k, int64_t w_stride_n, int64_t ld_dx, int op_dtype,
+                                int dx_dtype, int* status, void* stream_, int flags) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || K < 0 || N < 0) return ERR_BAD_SHAPE;
+  if (!fits_int(M) || !fits_int(K) || !fits_int(N)) return ERR_TOO_LARGE;
+  if (!valid_dtype(op_dtype) || !valid_dtype(dx_dtype)) return ERR_BAD_DTYPE;
+  if (M == 0 || K == 0) return OK;
+  if (!dx || (N > 0 && (!dz || !w))) return ERR_NULL_POINTER;
+  if (ld_dx < K) return ERR_BAD_STRIDE;
+  const int elt = dtype_size(op_dtype);
+  // dX[M, K] = dZ[M, N] * W^T: the reduction runs over N, contiguous in both dZ rows and W rows.
+  const bool tc_ok = N > 0 && tma_ok(dz, dz_stride_m, dz_stride_n, elt) && tma_ok(w, w_stride_k, w_stride_n, elt) &&
+                     dz_stride_m >= N && w_stride_k >= N;
+  if ((flags & AB200_FLAG_FORCE_TCGEN05) && !tc_ok) return ERR_BAD_STRIDE;
+  if (tc_ok && !(flags & AB200_FLAG_FORCE_GENERIC) && status != nullptr) {
+    TcProblem p{};
+    p.op_dtype = op_dtype;
+    p.a = dz; p.a_mn = false; p.a_pitch = dz_stride_m;
+    p.b = w; p.b_mn = false; p.b_pitch = w_stride_k;
+    GemmArgs& g = p.g;
+    g.status = status;
+    g.M = static_cast<int>(M); g.N = static_cast<int>(K); g.K = static_cast<int>(N);
+    g.out = dx; g.ld_out = ld_dx; g.out_dtype = dx_dtype;
+    g.act = ACT_NONE;
+    g_last_path = AB200_PATH_TCGEN05;
+    return launch_tc(p, pick_bn(M, K), stream);
+  }
+  AnyGemmArgs a{};
+  a.a = dz; a.sam = dz_stride_m; a.sak = dz_stride_n; a.a_dtype = op_dtype;
+  a.b = w; a.sbk = w_stride_n; a.sbn = w_stride_k; a.b_dtype = op_dtype;   // B[n, k] = W[k, n]
+  a.M = static_cast<int>(M); a.N = static_cast<int>(K); a.K = static_cast<int>(N);
+  a.out = dx; a.ld_out = ld_dx; a.out_dtype = dx_dtype;
+  a.act = ACT_NONE;
+  g_last_path = AB200_PATH_GENERIC;
+  return launch_any(a, stream);
+}
+
+int ab200_linear_backward_weight(const void* x, const void* dz, void* dw, int64_t M, int64_t K,
+                                 int64_t N, int64_t x_stride_m, int64_t x_stride_k,
+                                 int64_t dz_stride_m, int64_t dz_stride_n, int64_t ld_dw,
+                                 int op_dtype, int dw_dtype, int* status, void* stream_, int flags) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || K < 0 || N < 0) return ERR_BAD_SHAPE;
+  if (!fits_int(M) || !fits_int(K) || !fits_int(N)) return ERR_TOO_LARGE;
+  if (!valid_dtype(op_dtype) || !valid_dtype(dw_dtype)) return ERR_BAD_DTYPE;
+  if (K == 0 || N == 0) return OK;
+  if (!dw || (M > 0 && (!x || !dz))) return ERR_NULL_POINTER;
+  if (ld_dw < N) return ERR_BAD_STRIDE;
+  const int elt = dtype_size(op_dtype);
+  // dW[K, N] = X^T[K, M] * dZ[M, N]: the reduction runs over M, the strided dimension of both.
+  const bool tc_ok = M > 0 && tma_ok(x, x_stride_m, x_stride_k, elt) && tma_ok(dz, dz_stride_m, dz_stride_n, elt) &&
+                     x_stride_m >= K && dz_stride_m >= N;
+  if ((flags & AB200_FLAG_FORCE_TCGEN05) && !tc_ok) return ERR_BAD_STRIDE;
+  if (tc_ok && !(flags & AB200_FLAG_FORCE_GENERIC) && status != nullptr) {
+    TcProblem p{};
+    p.op_dtype = op_dtype;
+    p.a = x; p.a_mn = true; p.a_pitch = x_stride_m;
+    p.b = dz; p.b_mn = true; p.b_pitch = dz_stride_m;
+    GemmArgs& g = p.g;
+    g.status = status;
+    g.M = static_cast<int>(K); g.N = static_cast<int>(N); g.K = static_cast<int>(M);
+    g.out = dw; g.ld_out = ld_dw; g.out_dtype = dw_dtype;
+    g.act = ACT_NONE;
+    g_last_path = AB200_PATH_TCGEN05;
+    return launch_tc(p, pick_bn(K, N), stream);
+  }
+  AnyGemmArgs a{};
+  a.a = x; a.sam = x_stride_k; a.sak = x_stride_m; a.a_dtype = op_dtype;   // A[k_feat, m] = X[m, k_feat]
+  a.b = dz; a.sbk = dz_stride_m; a.sbn = dz_stride_n; a.b_dtype = op_dtype;
+  a.M = static_cast<int>(K); a.N = static_cast<int>(N); a.K = static_cast<int>(M);
+  a.out = dw; a.ld_out = ld_dw; a.out_dtype = dw_dtype;
+  a.act = ACT_NONE;
+  g_last_path = AB200_PATH_GENERIC;
+  return launch_any(a, stream);
+}
+
+int ab200_cast_2d(const void* src, void* dst, int64_t rows, int64_t cols, int64_t src_stride_r,
+                  int64_t src_stride_c, int src_dtype, int dst_dtype, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows < 0 || cols < 0) return ERR_BAD_SHAPE;
+  if (!valid_dtype(src_dtype) || !valid_dtype(dst_dtype)) return ERR_BAD_DTYPE;
+  if (rows == 0 || cols == 0) return OK;
+  if (!src || !dst) return ERR_NULL_POINTER;
+  const bool vec = src_stride_c == 1 && cols % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(dst) & 15) == 0 &&
+                   (src_stride_r * dtype_size(src_dtype)) % 16 == 0;
+  const long long work = vec ? rows * (cols / 8) : rows * cols;
+  long long blocks = (work + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+#define AB200_CAST(S, D)                                                                             \
+  do {                                                                                               \
+    if (vec)                                                                                         \
+      cast_kernel<S, D, true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                  \
+          static_cast<const S*>(src), src_stride_r, src_stride_c, static_cast<D*>(dst), rows, cols); \
+    else                                                                                             \
+      cast_kernel<S, D, false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                 \
+          static_cast<const S*>(src), src_stride_r, src_stride_c, static_cast<D*>(dst), rows, cols); \
+  } while (0)
+#define AB200_CAST_TO(S)                                    \
+  do {                                                      \
+    if (dst_dtype == DT_F32) AB200_CAST(S, float);          \
+    else if (dst_dtype == DT_F16) AB200_CAST(S, __half);    \
+    else AB200_CAST(S, __nv_bfloat16);                      \
+  } while (0)
+  if (src_dtype == DT_F32) AB200_CAST_TO(float);
+  else if (src_dtype == DT_F16) AB200_CAST_TO(__half);
+  else AB200_CAST_TO(__nv_bfloat16);
+#undef AB200_CAST_TO
+#undef AB200_CAST
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
+}
+
+}  // extern "C"

@@ -1,0 +1,381 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a:
+//
+//     D[M, N] = A[M, K] * B[K, N]        (fp32 accumulation in tensor memory)
+//
+// with either operand K-major (reduction dimension contiguous in global memory) or MN-major
+// (output dimension contiguous).  The three GEMMs of the fused linear layer map onto it as
+//
+//     forward   Y  = X  * W      A = X   K-major,   B = W   MN-major   (W is [in, out], out contiguous)
+//     backward  dX = dZ * W^T    A = dZ  K-major,   B = W   K-major
+//     backward  dW = X^T * dZ    A = X   MN-major,  B = dZ  MN-major
+//     skinny    Y^T = W^T * X^T  A = W   MN-major,  B = X   K-major    (swap-AB, stream-K)
+//
+// which replaces the reference's Triton tile loop (attorch/linear_kernels.py:143-165) and the two
+// cuBLAS matmuls of its backward (attorch/linear_layer.py:152-155).
+//
+// Structure of one CTA (192 threads, one CTA per SM, grid = min(work, #SM)):
+//   warp 0      TMA producer: fills a ring of kStages shared-memory stages (A tile + B tile,
+//               128-byte swizzle) with cp.async.bulk.tensor, completion on "full" mbarriers.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x BN x 32 bytes of K each) from the
+//               shared-memory descriptors into one of two accumulators in tensor memory;
+//               tcgen05.commit releases the stage ("empty") and publishes the accumulator.
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (each warp owns 32 TMEM lanes), add
+//               bias, store the pre-activation, apply the activation, store the output.  The second
+//               accumulator lets the epilogue of tile i overlap the main loop of tile i + 1.
+//
+// Work is either whole output tiles (tile-parallel, direct epilogue) or equal contiguous ranges of
+// (tile, k-block) units (stream-K, fp32 atomic accumulation into a zeroed workspace that a small
+// finishing kernel turns into the output).
+#pragma once
+#include "act_math.cuh"
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace ab200 {
+
+struct GemmArgs {
+  int M, N, K;            // output rows, output columns, reduction length
+  int tiles_m, tiles_n;   // ceil(M / 128), ceil(N / BN)
+  int group_m;            // row-blocks per rasterisation group
+  int k_blocks;           // ceil(K / elements per stage)
+  int stream_k;           // 0: one CTA per whole tile; 1: equal (tile, k-block) ranges + atomics
+  uint32_t idesc;         // tcgen05 instruction descriptor (operand format, majorness, 128 x BN)
+  // Direct epilogue
+  void* out;              // [M, N], row pitch ld_out elements
+  long long ld_out;
+  int out_dtype;
+  void* aux;              // optional second output written before the activation (pre-activation)
+  long long ld_aux;
+  const void* bias;       // optional [N]
+  int bias_dtype;
+  int act;
+  float act_param;
+  // Stream-K epilogue
+  float* partial;         // fp32, zero on entry; [M, N] (pitch ld_partial) or, if transposed, [N, M]
+  long long ld_partial;
+  int partial_transposed;
+  int* status;            // device word; a bounded wait that runs out stores a DeviceStatus here
+};
+
+template <int BN_, int ELT_, bool A_MN_, bool B_MN_>
+struct GemmCfg {
+  static constexpr int BM = 128;
+  static constexpr int BN = BN_;
+  static constexpr int ELT = ELT_;               // bytes per operand element (2: f16/bf16, 4: tf32)
+  static constexpr bool A_MN = A_MN_;
+  static constexpr bool B_MN = B_MN_;
+  static constexpr int BKE = 128 / ELT;          // K elements per stage (one 128-byte swizzle row)
+  static constexpr int UMMA_K = 32 / ELT;        // K elements per tcgen05.mma
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int kMaxSmem = 227 * 1024;
+  static constexpr int kBarrierBytes = 512;
+  static constexpr int kStagesFit = (kMaxSmem - 1024 - kBarrierBytes) / STAGE_BYTES;
+  static constexpr int STAGES = kStagesFit > 8 ? 8 : kStagesFit;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + kBarrierBytes;
+  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;   // power of two for BN in {16..256}
+  static constexpr int MN_ATOM = 128 / ELT;      // elements in one 128-byte row of an MN-major tile
+  static constexpr int MN_BOX_BYTES = BKE * 128; // one TMA box of an MN-major tile
+  static constexpr int kThreads = 192;
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be 32, 64, 128 or 256");
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM allocation must be a power of two");
+  static_assert(!B_MN_ || BN_ % (128 / ELT_) == 0, "an MN-major B tile is made of 128-byte wide boxes");
+};
+
+struct Segment {
+  int m_blk, n_blk;
+  int kb0, kb1;     // k-block range [kb0, kb1)
+};
+
+// Every role of a CTA walks the same sequence of segments, computed from blockIdx alone.
+struct SegmentIter {
+  long long unit, unit_end;   // stream-K: position in (tile, k-block) units
+  int tile;                   // tile-parallel: next tile
+  __device__ __forceinline__ SegmentIter(const GemmArgs& a) {
+    const long long tiles = static_cast<long long>(a.tiles_m) * a.tiles_n;
+    if (a.stream_k) {
+      const long long total = tiles * a.k_blocks;
+      unit = total * blockIdx.x / gridDim.x;
+      unit_end = total * (blockIdx.x + 1) / gridDim.x;
+      tile = 0;
+    } else {
+      unit = 0;
+      unit_end = tiles;
+      tile = blockIdx.x;
+    }
+  }
+  __device__ __forceinline__ bool next(const GemmArgs& a, Segment& s) {
+    int t;
+    if (a.stream_k) {
+      if (unit >= unit_end) return false;
+      t = static_cast<int>(unit / a.k_blocks);
+      s.kb0 = static_cast<int>(unit - static_cast<long long>(t) * a.k_blocks);
+      const long long left = unit_end - unit;
+      s.kb1 = (a.k_blocks - s.kb0 < left) ? a.k_blocks : s.kb0 + static_cast<int>(left);
+      unit += s.kb1 - s.kb0;
+    } else {
+      if (tile >= unit_end) return false;
+      t = tile;
+      tile += gridDim.x;
+      s.kb0 = 0;
+      s.kb1 = a.k_blocks;
+    }
+    // Grouped rasterisation: group_m row-blocks at a time, row-block index fastest.
+    const int per_group = a.group_m * a.tiles_n;
+    const int g = t / per_group;
+    const int first_m = g * a.group_m;
+    const int gsz = (a.tiles_m - first_m < a.group_m) ? a.tiles_m - first_m : a.group_m;
+    const int r = t - g * per_group;
+    s.m_blk = first_m + r % gsz;
+    s.n_blk = r / gsz;
+    return true;
+  }
+};
+
+// Stores up to 32 consecutive columns of one output row.
+__device__ __forceinline__ void store_row_chunk(void* base, int dt, long long offset,
+                                                const float (&v)[32], int valid) {
+  if (dt == DT_F32) {
+    float* p = static_cast<float*>(base) + offset;
+    if (valid == 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4*>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < valid) p[i] = v[i];
+    }
+  } else {
+    uint16_t* p = static_cast<uint16_t*>(base) + offset;
+    if (valid == 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 q;
+        q.x = pack2(v[8 * i + 0], v[8 * i + 1], dt);
+        q.y = pack2(v[8 * i + 2], v[8 * i + 3], dt);
+        q.z = pack2(v[8 * i + 4], v[8 * i + 5], dt);
+        q.w = pack2(v[8 * i + 6], v[8 * i + 7], dt);
+        reinterpret_cast<uint4*>(p)[i] = q;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < valid) store_from_f32(p, dt, i, v[i]);
+    }
+  }
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
+  constexpr int BM = Cfg::BM, BN = Cfg::BN, BKE = Cfg::BKE, STAGES = Cfg::STAGES;
+  constexpr bool kTf32 = (Cfg::ELT == 4);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
+  uint8_t* smem = smem_raw + pad;              // 1024-byte aligned: required by the 128-byte swizzle
+  const uint32_t smem_base = raw_addr + pad;
+  uint8_t* bar_region = smem + STAGES * Cfg::STAGE_BYTES;
+  const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+  // Barrier layout (8 bytes each): full[STAGES], empty[STAGES], acc_full[2], acc_empty[2].
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_region + 8 * (2 * STAGES + 4));
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(acc_full_bar(b), 1);
+      ptx::mbar_init(acc_empty_bar(b), 4);   // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<1>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+    ptx::tmem_relinquish<1>();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // A bounded wait that also gives up as soon as another role of this CTA has given up.
+  auto wait = [&](uint32_t bar, uint32_t parity, int code) -> bool {
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+      if ((++spins & 0x3FFu) == 0) {
+        if (*abort_flag) return false;
+        const uint64_t now = ptx::globaltimer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > ptx::kWaitLimitNs) {
+          *abort_flag = 1;
+          atomicCAS(args.status, 0, code);
+          return false;
+        }
+      }
+    }
+    return true;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      SegmentIter it(args);
+      Segment seg;
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      while (ok && it.next(args, seg)) {
+        const int m0 = seg.m_blk * BM;
+        const int n0 = seg.n_blk * BN;
+        for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
+          if (!wait(empty_bar(s), ph ^ 1u, DEV_TIMEOUT_PRODUCER)) { ok = false; break; }
+          ptx::mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+          const uint32_t a_dst = smem_base + s * Cfg::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+          const int k0 = kb * BKE;
+          if constexpr (Cfg::A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / Cfg::MN_ATOM; ++j)
+              ptx::tma_load_2d(a_dst + j * Cfg::MN_BOX_BYTES, &tmap_a, full_bar(s),
+                               m0 + j * Cfg::MN_ATOM, k0);
+          } else {
+            ptx::tma_load_2d(a_dst, &tmap_a, full_bar(s), k0, m0);
+          }
+          if constexpr (Cfg::B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / Cfg::MN_ATOM; ++j)
+              ptx::tma_load_2d(b_dst + j * Cfg::MN_BOX_BYTES, &tmap_b, full_bar(s),
+                               n0 + j * Cfg::MN_ATOM, k0);
+          } else {
+            ptx::tma_load_2d(b_dst, &tmap_b, full_bar(s), k0, n0);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      SegmentIter it(args);
+      Segment seg;
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t n_acc = 0;
+      bool ok = true;
+      while (ok && it.next(args, seg)) {
+        const uint32_t b = n_acc & 1u;
+        const uint32_t acc_ph = (n_acc >> 1) & 1u;
+        if (!wait(acc_empty_bar(b), acc_ph ^ 1u, DEV_TIMEOUT_MMA)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + b * BN;
+        for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
+          if (!wait(full_bar(s), ph, DEV_TIMEOUT_MMA)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + s * Cfg::STAGE_BYTES;
+          const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BKE / Cfg::UMMA_K; ++k) {
+            // K-major: the next 32 bytes of every 128-byte row.  MN-major: the next UMMA_K rows.
+            const uint64_t a_desc =
+                Cfg::A_MN ? ptx::make_smem_desc(a_addr + k * Cfg::UMMA_K * 128, Cfg::MN_BOX_BYTES, 1024)
+                          : ptx::make_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t b_desc =
+                Cfg::B_MN ? ptx::make_smem_desc(b_addr + k * Cfg::UMMA_K * 128, Cfg::MN_BOX_BYTES, 1024)
+                          : ptx::make_smem_desc(b_addr + k * 32, 16, 1024);
+            ptx::umma<1, kTf32>(d_tmem, a_desc, b_desc, args.idesc,
+                                (kb > seg.kb0 || k > 0) ? 1u : 0u);
+          }
+          ptx::umma_commit(empty_bar(s));      // stage reusable once these MMAs have read it
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::umma_commit(acc_full_bar(b));     // accumulator complete
+        ++n_acc;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                    // TMEM lane quarter this warp may access
+    SegmentIter it(args);
+    Segment seg;
+    uint32_t n_acc = 0;
+    bool ok = true;
+    while (ok && it.next(args, seg)) {
+      const uint32_t b = n_acc & 1u;
+      const uint32_t acc_ph = (n_acc >> 1) & 1u;
+      if (!wait(acc_full_bar(b), acc_ph, DEV_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      const int row = seg.m_blk * BM + q * 32 + lane;
+      const bool row_ok = row < args.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = seg.n_blk * BN + c * 32;
+        if (col0 >= args.N) break;             // warp-uniform
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * BN + c * 32, r);
+        ptx::tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        const int valid = (args.N - col0 < 32) ? args.N - col0 : 32;
+        if (args.stream_k) {
+          if (row_ok) {
+            if (args.partial_transposed) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < valid) atomicAdd(args.partial + static_cast<long long>(col0 + i) * args.ld_partial + row, v[i]);
+            } else {
+              float* p = args.partial + static_cast<long long>(row) * args.ld_partial + col0;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < valid) atomicAdd(p + i, v[i]);
+            }
+          }
+        } else {
+          if (args.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < valid) v[i] += load_as_f32(args.bias, args.bias_dtype, col0 + i);
+          }
+          if (args.aux != nullptr && row_ok)
+            store_row_chunk(args.aux, args.out_dtype, static_cast<long long>(row) * args.ld_aux + col0, v, valid);
+          act_fwd_inplace(v, args.act, args.act_param);
+          if (row_ok)
+            store_row_chunk(args.out, args.out_dtype, static_cast<long long>(row) * args.ld_out + col0, v, valid);
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(acc_empty_bar(b));
+      ++n_acc;
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc<1>(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace ab200

@@ -1,0 +1,260 @@
+// The memory-bound and the any-shape kernels around the tcgen05 GEMM:
+//   * act_backward_kernel   dZ = dY * act'(Z) with the bias-gradient column sums fused in
+//                           (reference: act_func_backward_kernel, attorch/act_kernels.py:883-927,
+//                           and pre_act_grad.sum(dim=0), attorch/linear_layer.py:156)
+//   * colsum_finish_kernel  fixed-order reduction of the per-row-block column sums -> db
+//   * streamk_finish_kernel fp32 partial sums -> bias, pre-activation, activation, output
+//   * cast_kernel           strided 2-D copy with element-type conversion (autocast operand casts)
+//   * gemm_any_kernel       CUDA-core GEMM for shapes the TMA path cannot address (row pitches that
+//                           are not multiples of 16 bytes, arbitrary element strides)
+#pragma once
+#include "act_math.cuh"
+#include "common.cuh"
+
+namespace ab200 {
+
+// ------------------------------------------------------------------------------------------------
+// dZ = dY * act'(Z), plus per-row-block column sums of dZ.
+// Block: 256 threads = 32 column groups (8 columns each) x 8 row lanes; covers 256 columns x
+// kActRows rows.  partial is [gridDim.y][N] fp32.
+// ------------------------------------------------------------------------------------------------
+constexpr int kActRows = 128;
+
+template <class T, bool kVec>
+__global__ void __launch_bounds__(256)
+act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restrict__ z, long long ld_z,
+                    T* __restrict__ dz, long long ld_dz, float* __restrict__ partial, int M, int N,
+                    int act, float act_param) {
+  const int cg = threadIdx.x & 31;
+  const int rl = threadIdx.x >> 5;
+  const int col0 = blockIdx.x * 256 + cg * 8;
+  const int row_begin = blockIdx.y * kActRows;
+  const int row_end = min(M, row_begin + kActRows);
+  float sum[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
+
+  if (col0 < N) {
+    for (int r = row_begin + rl; r < row_end; r += 8) {
+      float g[8], zz[8];
+      if constexpr (kVec) {
+        // 8 elements: one 16-byte load for 2-byte types, two for fp32.
+        constexpr int kWords = sizeof(T) * 8 / 16;
+        uint4 gq[kWords], zq[kWords];
+        const uint4* gp = reinterpret_cast<const uint4*>(dy + r * ld_dy + col0);
+#pragma unroll
+        for (int w = 0; w < kWords; ++w) gq[w] = __ldg(gp + w);
+        if (z != nullptr) {
+          const uint4* zp = reinterpret_cast<const uint4*>(z + r * ld_z + col0);
+#pragma unroll
+          for (int w = 0; w < kWords; ++w) zq[w] = __ldg(zp + w);
+        }
+        const T* ge = reinterpret_cast<const T*>(gq);
+        const T* ze = reinterpret_cast<const T*>(zq);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          g[i] = to_f32<T>(ge[i]);
+          zz[i] = (z != nullptr) ? to_f32<T>(ze[i]) : 0.0f;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const bool in = col0 + i < N;
+          g[i] = in ? to_f32<T>(dy[r * ld_dy + col0 + i]) : 0.0f;
+          zz[i] = (in && z != nullptr) ? to_f32<T>(z[r * ld_z + col0 + i]) : 0.0f;
+        }
+      }
+      act_grad_mul(g, zz, act, act_param);
+      // The stored dZ is rounded to the element type; the column sums use the rounded values,
+      // as a sum over the stored dZ would.
+      T o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        o[i] = from_f32<T>(g[i]);
+        sum[i] += to_f32<T>(o[i]);
+      }
+      if (dz != nullptr) {
+        if constexpr (kVec) {
+          constexpr int kWords = sizeof(T) * 8 / 16;
+          uint4* op = reinterpret_cast<uint4*>(dz + r * ld_dz + col0);
+#pragma unroll
+          for (int w = 0; w < kWords; ++w) op[w] = reinterpret_cast<const uint4*>(o)[w];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (col0 + i < N) dz[r * ld_dz + col0 + i] = o[i];
+        }
+      }
+    }
+  }
+
+  if (partial != nullptr) {
+    __shared__ float red[8][256 + 8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[rl][cg * 8 + i] = sum[i];
+    __syncthreads();
+    const int c = threadIdx.x;   // one column per thread
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += red[j][c];
+    const int col = blockIdx.x * 256 + c;
+    if (col < N) partial[static_cast<long long>(blockIdx.y) * N + col] = s;
+  }
+}
+
+// db[n] = sum over row blocks, in block order (deterministic), rounded once to the output type.
+__global__ void colsum_finish_kernel(const float* __restrict__ partial, int chunks, int N, void* db,
+                                     int db_dtype) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  float s = 0.0f;
+  for (int c = 0; c < chunks; ++c) s += partial[static_cast<long long>(c) * N + n];
+  store_from_f32(db, db_dtype, n, s);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Finishing pass of the stream-K GEMM: partial[M, N] fp32 -> (+bias) -> aux -> act -> out.
+// Clears the partial sums behind itself so that the workspace is zero again for the next call.
+// ------------------------------------------------------------------------------------------------
+__global__ void streamk_finish_kernel(float* __restrict__ partial, long long ld_partial, int M, int N,
+                                      const void* bias, int bias_dtype, void* aux, long long ld_aux,
+                                      void* out, long long ld_out, int out_dtype, int act,
+                                      float act_param) {
+  const long long total = static_cast<long long>(M) * N;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int m = static_cast<int>(i / N);
+    const int n = static_cast<int>(i - static_cast<long long>(m) * N);
+    float* pp = partial + m * ld_partial + n;
+    float v[1] = {*pp};
+    *pp = 0.0f;
+    if (bias != nullptr) v[0] += load_as_f32(bias, bias_dtype, n);
+    if (aux != nullptr) store_from_f32(aux, out_dtype, m * ld_aux + n, v[0]);
+    act_fwd_inplace(v, act, act_param);
+    store_from_f32(out, out_dtype, m * ld_out + n, v[0]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dst[r, c] (contiguous) = convert(src[r * sr + c * sc])
+// ------------------------------------------------------------------------------------------------
+template <class S, class D, bool kVec>
+__global__ void cast_kernel(const S* __restrict__ src, long long sr, long long sc, D* __restrict__ dst,
+                            long long rows, long long cols) {
+  if constexpr (kVec) {
+    // cols % 8 == 0, sc == 1, both sides 16-byte aligned: 8 elements per thread.
+    const long long groups_per_row = cols / 8;
+    const long long total = rows * groups_per_row;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long r = i / groups_per_row;
+      const long long c = (i - r * groups_per_row) * 8;
+      constexpr int kSw = sizeof(S) * 8 / 16, kDw = sizeof(D) * 8 / 16;
+      uint4 in[kSw], outv[kDw];
+      const uint4* sp = reinterpret_cast<const uint4*>(src + r * sr + c);
+#pragma unroll
+      for (int w = 0; w < kSw; ++w) in[w] = __ldg(sp + w);
+      const S* se = reinterpret_cast<const S*>(in);
+      D* de = reinterpret_cast<D*>(outv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) de[k] = from_f32<D>(to_f32<S>(se[k]));
+      uint4* dp = reinterpret_cast<uint4*>(dst + r * cols + c);
+#pragma unroll
+      for (int w = 0; w < kDw; ++w) dp[w] = outv[w];
+    }
+  } else {
+    const long long total = rows * cols;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long r = i / cols;
+      const long long c = i - r * cols;
+      dst[i] = from_f32<D>(to_f32<S>(src[r * sr + c * sc]));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Any-shape GEMM on CUDA cores: C[m, n] = sum_k A[m * sam + k * sak] * B[k * sbk + n * sbn], fp32
+// accumulation, same fused epilogue as the tensor-core kernel.  64 x 64 tile, 256 threads, 4 x 4
+// outputs per thread.
+// ------------------------------------------------------------------------------------------------
+struct AnyGemmArgs {
+  const void* a; long long sam, sak; int a_dtype;
+  const void* b; long long sbk, sbn; int b_dtype;
+  int M, N, K;
+  void* out; long long ld_out; int out_dtype;
+  void* aux; long long ld_aux;
+  const void* bias; int bias_dtype;
+  int act; float act_param;
+};
+
+__global__ void __launch_bounds__(256) gemm_any_kernel(const AnyGemmArgs g) {
+  constexpr int T = 64, KS = 16;
+  __shared__ float As[KS][T + 4];
+  __shared__ float Bs[KS][T + 4];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * T, n0 = blockIdx.x * T;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+  for (int k0 = 0; k0 < g.K; k0 += KS) {
+    // 64 x 16 elements of each operand, 4 per thread.
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = threadIdx.x + e * 256;
+      {
+        const int mm = idx % T, kk = idx / T;   // consecutive threads -> consecutive m
+        const int m = m0 + mm, k = k0 + kk;
+        float v = 0.0f;
+        if (m < g.M && k < g.K) {
+          v = load_as_f32(g.a, g.a_dtype, m * g.sam + k * g.sak);
+        }
+        As[kk][mm] = v;
+      }
+      {
+        const int nn = idx % T, kk = idx / T;
+        const int n = n0 + nn, k = k0 + kk;
+        float v = 0.0f;
+        if (n < g.N && k < g.K) {
+          v = load_as_f32(g.b, g.b_dtype, k * g.sbk + n * g.sbn);
+        }
+        Bs[kk][nn] = v;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < KS; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= g.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= g.N) continue;
+      float v[1] = {acc[i][j]};
+      if (g.bias != nullptr) v[0] += load_as_f32(g.bias, g.bias_dtype, n);
+      if (g.aux != nullptr) store_from_f32(g.aux, g.out_dtype, m * g.ld_aux + n, v[0]);
+      act_fwd_inplace(v, g.act, g.act_param);
+      store_from_f32(g.out, g.out_dtype, m * g.ld_out + n, v[0]);
+    }
+  }
+}
+
+}  // namespace ab200

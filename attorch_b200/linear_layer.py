@@ -1,0 +1,325 @@
+"""
+Drop-in replacement for ``attorch.Linear`` (attorch/linear_layer.py:164-205 of the reference) whose
+device work runs in hand-written sm_100a CUDA kernels behind a C ABI (include/attorch_b200.h).
+
+``Y = act(X @ W + b)`` with ``W`` of shape ``[in_features, out_features]``; forward and backward
+(``dX``, ``dW``, ``db``).  This module only mirrors the reference's host logic - argument checks,
+activation-string parsing, flattening, the autocast / output-dtype rule, which tensors are saved
+and which gradients are produced - and hands raw device pointers to the library.  There is no
+Triton, no PyTorch matmul and no CPU path: on a machine without the built library or without a
+CUDA device the layer raises.
+"""
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+from torch import Tensor, nn
+
+from . import _lib
+from .acts import act_id, parse_act_func
+
+_DTYPE_IDS = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+# Per (device index, stream) scratch: a grow-only workspace and the device status word.
+_scratch: Dict[Tuple[int, int], Dict[str, Tensor]] = {}
+
+# Flags forwarded to every GEMM entry point (tests use them to pin a kernel family).
+_gemm_flags = 0
+
+
+def set_gemm_flags(flags: int) -> int:
+    """Sets the AB200_FLAG_* bits passed to the GEMM entry points; returns the previous value."""
+    global _gemm_flags
+    previous, _gemm_flags = _gemm_flags, int(flags)
+    return previous
+
+
+def get_output_dtype(input_dtype: torch.dtype) -> torch.dtype:
+    """
+    Output dtype of the layer: the CUDA autocast dtype while autocast is enabled, else the input
+    dtype.  The reference (attorch/utils.py:27-60 with autocast='fp16', attorch/linear_layer.py:80)
+    returns fp16 under autocast and asserts that the autocast dtype is fp16 or fp32; here bf16
+    autocast is accepted too and yields bf16, and fp32 "autocast" leaves the input dtype alone.
+    """
+    if torch.is_autocast_enabled('cuda'):
+        dtype = torch.get_autocast_dtype('cuda')
+        assert dtype in (torch.float32, torch.float16, torch.bfloat16), \
+            'Only fp16, bf16 and fp32 casting are supported'
+        return input_dtype if dtype is torch.float32 else dtype
+    return input_dtype
+
+
+def _dtype_id(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_IDS[dtype]
+    except KeyError:
+        raise TypeError(f'Unsupported dtype {dtype}; supported: float32, float16, bfloat16') from None
+
+
+def _ptr(tensor: Optional[Tensor]) -> Optional[int]:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _stream_scratch(device: torch.device) -> Dict[str, Tensor]:
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    entry = _scratch.get(key)
+    if entry is None:
+        entry = {'status': torch.zeros(1, dtype=torch.int32, device=device),
+                 'workspace': torch.empty(0, dtype=torch.uint8, device=device)}
+        _scratch[key] = entry
+    return entry
+
+
+def _workspace(device: torch.device, nbytes: int) -> Tensor:
+    entry = _stream_scratch(device)
+    if entry['workspace'].numel() < nbytes:
+        entry['workspace'] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    return entry['workspace']
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """
+    Synchronises and raises if any kernel launched through this module gave up on a bounded wait
+    (the device status word of include/attorch_b200.h).  The layer never synchronises on its
+    own; call this where the program synchronises anyway.
+    """
+    for (index, _), entry in list(_scratch.items()):
+        if device is not None and device.index is not None and device.index != index:
+            continue
+        code = int(entry['status'].item())
+        if code != 0:
+            entry['status'].zero_()
+            raise _lib.LibraryError(f'device status {code}: {_lib.error_string(code)}')
+
+
+def _require_cuda(tensor: Tensor, what: str) -> None:
+    if not tensor.is_cuda:
+        raise RuntimeError(
+            f'attorch_b200.Linear runs only on CUDA devices (sm_100a); {what} is on {tensor.device}. '
+            'There is no CPU fallback.')
+
+
+def _tma_addressable(tensor: Tensor) -> bool:
+    """Unit inner stride, 16-byte aligned base and row pitch."""
+    elt = tensor.element_size()
+    return (tensor.stride(1) == 1 and tensor.data_ptr() % 16 == 0
+            and tensor.stride(0) >= tensor.shape[1] and (tensor.stride(0) * elt) % 16 == 0)
+
+
+def _as_operand(tensor: Tensor, dtype: torch.dtype, stream: int) -> Tensor:
+    """
+    Returns a 2-D operand of ``dtype`` that the kernels can read: the tensor itself if it already
+    has that dtype and TMA can address it (or a copy could not make it addressable either),
+    otherwise a contiguous converted copy made by the library's cast kernel.
+    """
+    rows, cols = tensor.shape
+    if tensor.dtype is dtype:
+        copy_helps = (cols * tensor.element_size()) % 16 == 0
+        if _tma_addressable(tensor) or not copy_helps:
+            return tensor
+    out = torch.empty((rows, cols), dtype=dtype, device=tensor.device)
+    if out.numel():
+        lib = _lib.load()
+        _lib.check(lib.ab200_cast_2d(tensor.data_ptr(), out.data_ptr(), rows, cols,
+                                     tensor.stride(0), tensor.stride(1),
+                                     _dtype_id(tensor.dtype), _dtype_id(dtype), stream),
+                   'ab200_cast_2d')
+    return out
+
+
+class LinearAutoGrad(torch.autograd.Function):
+    """
+    Autodiff for the fused linear layer; same call contract as the reference's
+    ``LinearAutoGrad`` (attorch/linear_layer.py:19-161): ``apply(input, weight, bias, act_func)``.
+    Two optional trailing arguments let a caller supply the buffers ``dW`` and ``db`` are written
+    into (e.g. views of a flat all-reduce bucket).
+    """
+    @staticmethod
+    def forward(ctx, input: Tensor, weight: Tensor, bias: Optional[Tensor] = None,
+                act_func: Optional[str] = None, weight_grad_out: Optional[Tensor] = None,
+                bias_grad_out: Optional[Tensor] = None) -> Tensor:
+        assert weight.ndim == 2, \
+            f'Weights must be 2D, received shape {weight.shape}'
+        assert bias is None or bias.ndim == 1, \
+            f'Bias must be 1D, received shape {bias.shape}'
+        assert input.shape[-1] == weight.shape[0], \
+            f'Incompatible input ({input.shape}) and weights ({weight.shape}) shape'
+        assert bias is None or weight.shape[1] == bias.shape[0], \
+            f'Incompatible weights ({weight.shape}) and bias ({bias.shape}) shape'
+
+        name, param = parse_act_func(act_func)
+        _require_cuda(input, 'input')
+        _require_cuda(weight, 'weight')
+
+        flattened_input = input.flatten(0, -2)
+        batch_dim, in_feat_dim = flattened_input.shape
+        _, out_feat_dim = weight.shape
+
+        requires_grad = (input.requires_grad or weight.requires_grad or
+                         (bias is not None and bias.requires_grad))
+        save_pre_act = requires_grad and (name is not None)
+
+        output_dtype = get_output_dtype(input.dtype)
+        op_dtype = output_dtype  # operands are multiplied in the output dtype (fp32 -> TF32)
+        lib = _lib.load()
+
+        with torch.cuda.device(input.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            scratch = _stream_scratch(input.device)
+            x_op = _as_operand(flattened_input, op_dtype, stream)
+            w_op = _as_operand(weight, op_dtype, stream)
+            # With a 16-bit output the reference rounds the bias to that dtype before adding it
+            # to the fp32 accumulator (attorch/linear_kernels.py:171-172).
+            bias_op = bias
+            if bias is not None and bias.dtype is not op_dtype and op_dtype is not torch.float32:
+                bias_op = _as_operand(bias.view(1, -1), op_dtype, stream).view(-1)
+            if bias_op is not None and not bias_op.is_contiguous():
+                bias_op = bias_op.contiguous()
+
+            output = torch.empty((batch_dim, out_feat_dim), device=input.device, dtype=output_dtype)
+            pre_act = torch.empty_like(output) if save_pre_act else None
+
+            ws_bytes = lib.ab200_forward_workspace_bytes(batch_dim, in_feat_dim, out_feat_dim)
+            workspace = _workspace(input.device, ws_bytes) if ws_bytes else None
+            _lib.check(lib.ab200_linear_forward(
+                _ptr(x_op), _ptr(w_op), _ptr(bias_op), _ptr(pre_act), _ptr(output),
+                batch_dim, in_feat_dim, out_feat_dim,
+                x_op.stride(0), x_op.stride(1), w_op.stride(0), w_op.stride(1),
+                out_feat_dim, out_feat_dim,
+                _dtype_id(op_dtype), _dtype_id(output_dtype),
+                _dtype_id(bias_op.dtype) if bias_op is not None else 0,
+                act_id(name), 0.0 if param is None else param,
+                _ptr(workspace), ws_bytes, _ptr(scratch['status']), stream, _gemm_flags),
+                'ab200_linear_forward')
+
+        ctx.param = param
+        ctx.act_func = name
+        ctx.bias_requires_grad = False if bias is None else bias.requires_grad
+        ctx.bias_dtype = None if bias is None else bias.dtype
+        ctx.output_dtype = output_dtype
+        ctx.input_shape = input.shape
+        ctx.input_dtype = input.dtype
+        ctx.input_requires_grad = input.requires_grad
+        ctx.weight_requires_grad = weight.requires_grad
+        ctx.weight_dtype = weight.dtype
+        ctx.weight_shape = weight.shape
+        ctx.has_grad_out = (weight_grad_out is not None, bias_grad_out is not None)
+        if requires_grad:
+            # Backward multiplies in the output dtype, so the converted operands are what it
+            # needs; keeping them avoids converting X and W a second time.
+            saved = [x_op, pre_act, w_op]
+            if weight_grad_out is not None:
+                saved.append(weight_grad_out)
+            if bias_grad_out is not None:
+                saved.append(bias_grad_out)
+            ctx.save_for_backward(*saved)
+
+        return output.view(*input.shape[:-1], out_feat_dim)
+
+    @staticmethod
+    def backward(ctx, output_grad: Tensor) -> Tuple[Optional[Tensor], ...]:
+        saved = list(ctx.saved_tensors)
+        x_op, pre_act, w_op = saved[:3]
+        extra = saved[3:]
+        weight_grad_out = extra.pop(0) if ctx.has_grad_out[0] else None
+        bias_grad_out = extra.pop(0) if ctx.has_grad_out[1] else None
+
+        batch_dim, in_feat_dim = x_op.shape
+        out_feat_dim = w_op.shape[1]
+        op_dtype = ctx.output_dtype
+        lib = _lib.load()
+        device = x_op.device
+
+        input_grad = weight_grad = bias_grad = None
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream().cuda_stream
+            scratch = _stream_scratch(device)
+            status = _ptr(scratch['status'])
+            # The upstream gradient may arrive with any strides (expanded, transposed, ...).
+            dy = _as_operand(output_grad.reshape(batch_dim, out_feat_dim), op_dtype, stream)
+            if dy.stride(1) != 1 or dy.stride(0) < out_feat_dim:
+                dy = dy.contiguous()
+
+            need_db = ctx.bias_requires_grad
+            if need_db:
+                bias_grad = (bias_grad_out if bias_grad_out is not None else
+                             torch.empty(out_feat_dim, dtype=ctx.bias_dtype, device=device))
+            if ctx.act_func is None:
+                pre_act_grad = dy
+            else:
+                pre_act_grad = torch.empty((batch_dim, out_feat_dim), dtype=op_dtype, device=device)
+            if ctx.act_func is not None or need_db:
+                ws_bytes = lib.ab200_act_backward_workspace_bytes(batch_dim, out_feat_dim) if need_db else 0
+                workspace = _workspace(device, ws_bytes) if ws_bytes else None
+                _lib.check(lib.ab200_act_backward(
+                    _ptr(dy), _ptr(pre_act),
+                    _ptr(pre_act_grad) if ctx.act_func is not None else None,
+                    _ptr(bias_grad) if need_db else None,
+                    batch_dim, out_feat_dim, dy.stride(0),
+                    pre_act.stride(0) if pre_act is not None else out_feat_dim,
+                    pre_act_grad.stride(0), _dtype_id(op_dtype),
+                    _dtype_id(bias_grad.dtype) if need_db else 0,
+                    act_id(ctx.act_func), 0.0 if ctx.param is None else ctx.param,
+                    _ptr(workspace), ws_bytes, stream), 'ab200_act_backward')
+
+            # dW before dX: in a data-parallel step the all-reduce of dW can then start while
+            # dX is still being computed.
+            if ctx.weight_requires_grad:
+                weight_grad = (weight_grad_out if weight_grad_out is not None else
+                               torch.empty(ctx.weight_shape, dtype=ctx.weight_dtype, device=device))
+                _lib.check(lib.ab200_linear_backward_weight(
+                    _ptr(x_op), _ptr(pre_act_grad), _ptr(weight_grad),
+                    batch_dim, in_feat_dim, out_feat_dim,
+                    x_op.stride(0), x_op.stride(1), pre_act_grad.stride(0), pre_act_grad.stride(1),
+                    weight_grad.stride(0), _dtype_id(op_dtype), _dtype_id(weight_grad.dtype),
+                    status, stream, _gemm_flags), 'ab200_linear_backward_weight')
+            if ctx.input_requires_grad:
+                input_grad = torch.empty((batch_dim, in_feat_dim), dtype=ctx.input_dtype, device=device)
+                _lib.check(lib.ab200_linear_backward_input(
+                    _ptr(pre_act_grad), _ptr(w_op), _ptr(input_grad),
+                    batch_dim, in_feat_dim, out_feat_dim,
+                    pre_act_grad.stride(0), pre_act_grad.stride(1), w_op.stride(0), w_op.stride(1),
+                    in_feat_dim, _dtype_id(op_dtype), _dtype_id(input_grad.dtype),
+                    status, stream, _gemm_flags), 'ab200_linear_backward_input')
+                input_grad = input_grad.view(ctx.input_shape)
+
+        # One slot per forward argument (attorch/linear_layer.py:158-161 pads with None).
+        return input_grad, weight_grad, bias_grad, None, None, None
+
+
+class Linear(nn.Linear):
+    """
+    Linearly transforms the input using weights, optionally adding bias and fusing an activation
+    function.  Same constructor, parameters and state_dict as the reference's ``attorch.Linear``
+    (attorch/linear_layer.py:164-205).
+
+    Note: as in the reference, the weight matrix is of shape ``[in_features, out_features]``,
+    the transpose of ``torch.nn.Linear``'s.
+
+    Args:
+        in_features: Number of input features.
+        out_features: Number of output features.
+        bias: Flag for additive bias.
+        act_func: Name of activation function to apply, with None for identity.
+            Options are 'sigmoid', 'logsigmoid', 'tanh', 'relu', 'gelu', 'geluapprox', 'silu',
+            'relu6', 'hardsigmoid', 'hardtanh', 'hardswish', 'selu', 'mish', 'softplus',
+            'softsign', 'tanhshrink', 'leaky_relu_PARAM', 'elu_PARAM', 'celu_PARAM',
+            'hardshrink_PARAM', and 'softshrink_PARAM' (e.g. 'leaky_relu_0.01').
+        device: Device to use.
+        dtype: Dtype of layer.
+    """
+    def __init__(self, in_features: int, out_features: int, bias: bool = True,
+                 act_func: Optional[str] = None, device='cuda',
+                 dtype: torch.dtype = torch.float32) -> None:
+        super().__init__(in_features, out_features, bias, device, dtype)
+        self.weight = nn.Parameter(self.weight.T.contiguous())
+        self.act_func = act_func
+        # Optional (dW, db) destination buffers, e.g. views into a gradient bucket.
+        self.weight_grad_out: Optional[Tensor] = None
+        self.bias_grad_out: Optional[Tensor] = None
+
+    def forward(self, input: Tensor) -> Tensor:
+        return LinearAutoGrad.apply(input, self.weight, self.bias, self.act_func,
+                                    self.weight_grad_out, self.bias_grad_out)

@@ -1,0 +1,179 @@
+/*
+ * attorch_b200 -- C ABI of the B200-native (sm_100a) fused linear layer.
+ *
+ * The reference (BobMcDear/attorch) is pure Python + Triton and has no FFI of its own; its
+ * boundary for this path is the Python call LinearAutoGrad.apply(input, weight, bias, act_func)
+ * (attorch/linear_layer.py:19-161).  Each entry point below replaces one device-side step of that
+ * function; the Python module attorch_b200.linear_layer binds them with ctypes.
+ *
+ * Conventions
+ *   - Every pointer is a device pointer owned by the caller.  Except where an entry point says
+ *     otherwise the library allocates no device memory and keeps no pointer after it returns.
+ *   - Matrices are row-major; "ld" arguments are row pitches in ELEMENTS.
+ *   - The weight has the reference's layout [in_features, out_features] (attorch/linear_layer.py:200).
+ *   - Calls are asynchronous on `stream` (a cudaStream_t passed as void*), never synchronise, and
+ *     may be made from any host thread with the right device current.
+ *   - The return value is 0 on success or a negative AB200_ERR_* code for an argument the host
+ *     rejected before launching anything.  A kernel that gives up on a bounded wait writes a
+ *     positive AB200_DEV_* code to `*status` (a device int the caller zeroes and reads when it
+ *     next synchronises); the outputs of that call are then undefined.
+ */
+#ifndef ATTORCH_B200_H_
+#define ATTORCH_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types. */
+#define AB200_F32 0
+#define AB200_F16 1
+#define AB200_BF16 2
+
+/* Host-side return codes. */
+#define AB200_OK 0
+#define AB200_ERR_NULL_POINTER (-1)
+#define AB200_ERR_BAD_SHAPE (-2)
+#define AB200_ERR_BAD_DTYPE (-3)
+#define AB200_ERR_BAD_ACT (-4)
+#define AB200_ERR_BAD_STRIDE (-5)
+#define AB200_ERR_WORKSPACE_TOO_SMALL (-6)
+#define AB200_ERR_TENSOR_MAP (-7)
+#define AB200_ERR_LAUNCH (-8)
+#define AB200_ERR_TOO_LARGE (-9)
+#define AB200_ERR_DRIVER (-10)
+
+/* Device-side status codes (written to *status). */
+#define AB200_DEV_OK 0
+#define AB200_DEV_TIMEOUT_PRODUCER 1
+#define AB200_DEV_TIMEOUT_MMA 2
+#define AB200_DEV_TIMEOUT_EPILOGUE 3
+#define AB200_DEV_TIMEOUT_TRANSFORM 4
+
+/* Activation ids: the act_func strings of attorch/linear_layer.py:42-49 in the order of the
+ * dispatcher attorch/act_kernels.py:654-727.  Ids 17..21 take `act_param`. */
+#define AB200_ACT_NONE 0
+#define AB200_ACT_SIGMOID 1
+#define AB200_ACT_LOGSIGMOID 2
+#define AB200_ACT_TANH 3
+#define AB200_ACT_RELU 4
+#define AB200_ACT_GELU 5
+#define AB200_ACT_GELUAPPROX 6
+#define AB200_ACT_SILU 7
+#define AB200_ACT_RELU6 8
+#define AB200_ACT_HARDSIGMOID 9
+#define AB200_ACT_HARDTANH 10
+#define AB200_ACT_HARDSWISH 11
+#define AB200_ACT_SELU 12
+#define AB200_ACT_MISH 13
+#define AB200_ACT_SOFTPLUS 14
+#define AB200_ACT_SOFTSIGN 15
+#define AB200_ACT_TANHSHRINK 16
+#define AB200_ACT_LEAKY_RELU 17
+#define AB200_ACT_ELU 18
+#define AB200_ACT_CELU 19
+#define AB200_ACT_HARDSHRINK 20
+#define AB200_ACT_SOFTSHRINK 21
+#define AB200_ACT_COUNT 22
+
+/* Flags (bit set) accepted by the GEMM entry points. */
+#define AB200_FLAG_FORCE_GENERIC 1  /* use the any-shape CUDA-core kernel                      */
+#define AB200_FLAG_FORCE_TCGEN05 2  /* fail with AB200_ERR_BAD_STRIDE instead of falling back   */
+#define AB200_FLAG_FORCE_STREAMK 4  /* forward only: use the swap-AB stream-K kernel            */
+#define AB200_FLAG_NO_STREAMK 8     /* forward only: never use the swap-AB stream-K kernel      */
+
+/* Which kernel the last call on this host thread chose: 1 tcgen05 tile-parallel, 2 tcgen05
+ * swap-AB stream-K, 3 generic CUDA-core.  For tests and benchmarks. */
+#define AB200_PATH_TCGEN05 1
+#define AB200_PATH_STREAMK 2
+#define AB200_PATH_GENERIC 3
+
+/* Library version, major * 1000 + minor. */
+int ab200_version(void);
+
+/* Text for a host return code or a device status code. */
+const char* ab200_error_string(int code);
+
+/* Kernel chosen by the last GEMM entry point called on this host thread (AB200_PATH_*). */
+int ab200_last_path(void);
+
+/* Number of kernels this library has launched on this host thread since it was loaded. */
+int64_t ab200_launch_count(void);
+
+/*
+ * Forward:  Z = X * W (+ bias);  pre_act <- Z (if not NULL);  out <- act(Z).
+ * Replaces linear_forward_kernel (attorch/linear_kernels.py:59-188) as launched at
+ * attorch/linear_layer.py:88-98.
+ *   x        [M, K], element strides (x_stride_m, x_stride_k), type op_dtype
+ *   w        [K, N], element strides (w_stride_k, w_stride_n), type op_dtype
+ *   bias     [N] of bias_dtype, or NULL
+ *   pre_act  [M, N] of out_dtype, row pitch ld_pre, or NULL: the value before the activation,
+ *            rounded to out_dtype (what backward differentiates through)
+ *   out      [M, N] of out_dtype, row pitch ld_out
+ * Accumulation is fp32; fp32 operands are multiplied as TF32 on the tensor cores
+ * (attorch/linear_kernels.py:57,165).  The activation is evaluated on the unrounded fp32 value
+ * (attorch/linear_kernels.py:183).
+ * Operands with unit inner stride and 16-byte aligned base and row pitch run on the tcgen05
+ * kernels; anything else runs on the generic kernel.  M <= 128 uses the swap-AB stream-K kernel,
+ * which needs workspace_bytes >= ab200_forward_workspace_bytes(M, K, N); the workspace is
+ * cleared by the call itself.
+ */
+int ab200_linear_forward(const void* x, const void* w, const void* bias, void* pre_act, void* out,
+                         int64_t M, int64_t K, int64_t N, int64_t x_stride_m, int64_t x_stride_k,
+                         int64_t w_stride_k, int64_t w_stride_n, int64_t ld_pre, int64_t ld_out,
+                         int op_dtype, int out_dtype, int bias_dtype, int act, float act_param,
+                         void* workspace, int64_t workspace_bytes, int* status, void* stream,
+                         int flags);
+
+/* Workspace the forward call may need for this shape (0 when it needs none). */
+int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N);
+
+/*
+ * Backward, step 1:  dZ = dY * act'(Z)  and  db[n] = sum_m dZ[m, n].
+ * Replaces act_func_backward_kernel (attorch/act_kernels.py:883-927, launched at
+ * attorch/linear_layer.py:143-146) and pre_act_grad.sum(dim=0) (attorch/linear_layer.py:156).
+ *   dy, z, dz  [M, N] of `dtype`; z may be NULL iff act == AB200_ACT_NONE; dz may be NULL when
+ *              only db is wanted (act == NONE, where dZ is dY itself)
+ *   db         [N] of db_dtype or NULL; summed in fp32 in a fixed order, rounded once
+ *   workspace  needed iff db != NULL: ab200_act_backward_workspace_bytes(M, N) bytes
+ */
+int ab200_act_backward(const void* dy, const void* z, void* dz, void* db, int64_t M, int64_t N,
+                       int64_t ld_dy, int64_t ld_z, int64_t ld_dz, int dtype, int db_dtype, int act,
+                       float act_param, void* workspace, int64_t workspace_bytes, void* stream);
+
+int64_t ab200_act_backward_workspace_bytes(int64_t M, int64_t N);
+
+/*
+ * Backward, step 2:  dX[M, K] = dZ[M, N] * W^T.   Replaces `pre_act_grad @ weight.T`
+ * (attorch/linear_layer.py:153).  dz and w are of op_dtype, dx of dx_dtype.
+ */
+int ab200_linear_backward_input(const void* dz, const void* w, void* dx, int64_t M, int64_t K,
+                                int64_t N, int64_t dz_stride_m, int64_t dz_stride_n,
+                                int64_t w_stride_k, int64_t w_stride_n, int64_t ld_dx, int op_dtype,
+                                int dx_dtype, int* status, void* stream, int flags);
+
+/*
+ * Backward, step 3:  dW[K, N] = X^T * dZ.   Replaces `flattened_input.T @ pre_act_grad`
+ * (attorch/linear_layer.py:154-155).  x and dz are of op_dtype, dw of dw_dtype (pass AB200_F32 to
+ * keep the fp32 accumulator unrounded, e.g. for fp32 master weights or an fp32 all-reduce bucket).
+ */
+int ab200_linear_backward_weight(const void* x, const void* dz, void* dw, int64_t M, int64_t K,
+                                 int64_t N, int64_t x_stride_m, int64_t x_stride_k,
+                                 int64_t dz_stride_m, int64_t dz_stride_n, int64_t ld_dw,
+                                 int op_dtype, int dw_dtype, int* status, void* stream, int flags);
+
+/*
+ * dst[r, c] (contiguous, dst_dtype) = src[r * src_stride_r + c * src_stride_c] (src_dtype).
+ * The operand casts that autocast implies (attorch/linear_kernels.py:161-163 casts in registers;
+ * torch.autocast casts before its matmuls, attorch/linear_layer.py:152) and the copy that makes a
+ * strided input addressable by TMA.
+ */
+int ab200_cast_2d(const void* src, void* dst, int64_t rows, int64_t cols, int64_t src_stride_r,
+                  int64_t src_stride_c, int src_dtype, int dst_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATTORCH_B200_H_ */

@@ -1,0 +1,264 @@
+"""
+TEST INFRASTRUCTURE - CPU oracle for the fused linear layer.  Not part of the product: only
+``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline legs of ``bench.py`` may import it.
+
+A plain torch-on-CPU restatement of what the reference's ``attorch.Linear`` computes
+(forward and backward), following its data flow and rounding points step by step:
+
+    forward    attorch/linear_kernels.py:143-188  (fp32 accumulate, operand cast 161-163, bias cast
+               171-172, pre-activation store 176-181, activation on the unrounded accumulator 183)
+    dtype rule attorch/utils.py:27-60, attorch/linear_layer.py:80
+    backward   attorch/linear_layer.py:125-161  (dZ in the pre-activation's dtype 137-139,
+               matmuls in the output dtype 152-155, bias gradient as a sum over dZ 156)
+    math       attorch/act_kernels.py:14-628     (formulas and piecewise conventions),
+               655-721 / 759-832                 (which activations are evaluated in fp32 and which
+               in the dtype of the loaded tensor)
+
+Parity pinned: tests/test_oracle.py checks this file against golden vectors produced by the
+reference itself (its Triton kernels run by the Triton CPU interpreter; generator
+tests/golden/make_golden.py) for fp32 and fp16, all 22 activation settings, the piecewise
+switch points, strided 3-D inputs, and BASELINE config 1.  bf16 has no reference-made vectors
+(the interpreter's bf16 dot product is broken); the bf16 rules are the fp16 rules with the
+other 16-bit type, and on GPU boxes that have the reference the GPU tests compare against it.
+"""
+
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+SELU_SCALE = 1.0507009873554805
+SELU_ALPHA = 1.6732632423543772
+
+# Activations whose dispatcher branch up-casts the argument to fp32 first
+# (attorch/act_kernels.py:655-721 forward, 759-832 backward); the rest run in the loaded dtype.
+FP32_ACTS = frozenset({'sigmoid', 'logsigmoid', 'tanh', 'gelu', 'geluapprox', 'silu', 'selu', 'mish',
+                       'softplus', 'tanhshrink', 'elu', 'celu'})
+
+ALL_ACT_FUNCS = [None, 'sigmoid', 'logsigmoid', 'tanh', 'relu', 'gelu', 'geluapprox', 'silu', 'relu6',
+                 'hardsigmoid', 'hardtanh', 'hardswish', 'selu', 'mish', 'softplus', 'softsign',
+                 'tanhshrink', 'leaky_relu_0.01', 'elu_1', 'celu_1', 'hardshrink_0.5',
+                 'softshrink_0.5']
+
+
+def parse_act_func(act_func: Optional[str]) -> Tuple[Optional[str], Optional[float]]:
+    """Name / parameter split of attorch/linear_layer.py:65-69."""
+    param = None
+    if act_func is not None and '_' in act_func:
+        comps = act_func.split('_')
+        act_func = '_'.join(comps[:-1])
+        param = float(comps[-1])
+    return act_func, param
+
+
+def _sigmoid(x: Tensor) -> Tensor:
+    return 1 / (1 + torch.exp(-x))                                   # act_kernels.py:14-24
+
+
+def _tanh(x: Tensor) -> Tensor:
+    return 2 * _sigmoid(2 * x) - 1                                   # act_kernels.py:71-81
+
+
+def act_forward(name: Optional[str], x: Tensor, param: Optional[float] = None) -> Tensor:
+    """act(x), formulas of attorch/act_kernels.py:14-613; x is used in the dtype it comes in."""
+    if name is None:
+        return x
+    zero = torch.zeros((), dtype=x.dtype)
+    if name == 'sigmoid':
+        return _sigmoid(x)
+    if name == 'logsigmoid':
+        return torch.log(_sigmoid(x))                                # 43-53
+    if name == 'tanh':
+        return _tanh(x)
+    if name == 'relu':
+        return torch.maximum(zero, x)                                # 100-110
+    if name == 'gelu':
+        return 0.5 * (1 + torch.erf(0.707106781 * x)) * x            # 128-139
+    if name == 'geluapprox':
+        return 0.5 * (1 + _tanh(0.7978845608 * x * (1 + 0.044715 * x * x))) * x   # 159-170
+    if name == 'silu':
+        return x * _sigmoid(x)                                       # 190-200
+    if name == 'relu6':
+        return torch.clamp(x, 0, 6)                                  # 219-229
+    if name == 'hardsigmoid':
+        return torch.clamp(x / 6 + 0.5, 0, 1)                        # 247-257
+    if name == 'hardtanh':
+        return torch.clamp(x, -1, 1)                                 # 275-285
+    if name == 'hardswish':
+        return x * torch.clamp(x + 3, 0, 6) / 6                      # 303-313
+    if name == 'selu':
+        return SELU_SCALE * (torch.maximum(zero, x) +
+                             torch.minimum(zero, SELU_ALPHA * (torch.exp(x) - 1)))   # 331-344
+    if name == 'mish':
+        return x * _tanh(torch.log(1 + torch.exp(x)))                # 364-374
+    if name == 'softplus':
+        return torch.log(1 + torch.exp(x))                           # 395-405
+    if name == 'softsign':
+        return x / (1 + torch.abs(x))                                # 423-433
+    if name == 'tanhshrink':
+        return x - _tanh(x)                                          # 452-462
+    if name == 'leaky_relu':
+        return torch.maximum(zero, x) + param * torch.minimum(zero, x)   # 480-491
+    if name == 'elu':
+        return torch.where(x <= 0, param * (torch.exp(x) - 1), x)    # 510-521
+    if name == 'celu':
+        return torch.maximum(zero, x) + torch.minimum(zero, param * (torch.exp(x / param) - 1))  # 540-551
+    if name == 'hardshrink':
+        return torch.where(torch.abs(x) <= param, zero, x)           # 571-582
+    if name == 'softshrink':
+        return torch.where(x > param, x - param,
+                           torch.where(x < -param, x + param, zero))  # 601-613
+    raise ValueError(f'unknown activation {name!r}')
+
+
+def act_grad(name: Optional[str], x: Tensor, param: Optional[float] = None) -> Tensor:
+    """d act(x) / dx, formulas of attorch/act_kernels.py:28-628 (the *_grad functions)."""
+    one = torch.ones((), dtype=x.dtype)
+    zero = torch.zeros((), dtype=x.dtype)
+    if name is None:
+        return torch.ones_like(x)
+    if name == 'sigmoid':
+        s = _sigmoid(x)
+        return s * (1 - s)                                           # 28-39
+    if name == 'logsigmoid':
+        return 1 / (1 + torch.exp(x))                                # 57-67
+    if name == 'tanh':
+        t = _tanh(x)
+        return 1 - t * t                                             # 85-96
+    if name == 'relu':
+        return torch.where(x <= 0, zero, one)                        # 114-124
+    if name == 'gelu':
+        cdf = 0.5 * (1 + torch.erf(0.707106781 * x))
+        return 0.39894228 * torch.exp(-0.5 * x * x) * x + cdf        # 143-155
+    if name == 'geluapprox':
+        t = _tanh(0.7978845608 * x * (1 + 0.044715 * x * x))
+        return 0.5 * (1 + t + x * (1 - t * t) * 0.7978845608 * (1 + 3 * 0.044715 * x * x))   # 174-186
+    if name == 'silu':
+        s = _sigmoid(x)
+        return s * (x * (1 - s) + 1)                                 # 204-215
+    if name == 'relu6':
+        return torch.where((0 < x) & (x < 6), one, zero)             # 233-243
+    if name == 'hardsigmoid':
+        return torch.where((-3 < x) & (x < 3), one / 6, zero)        # 261-271
+    if name == 'hardtanh':
+        return torch.where((-1 < x) & (x < 1), one, zero)            # 289-299
+    if name == 'hardswish':
+        return torch.where(x < -3, zero, torch.where(x <= 3, x / 3 + 0.5, one))   # 317-327
+    if name == 'selu':
+        return SELU_SCALE * torch.where(x <= 0, SELU_ALPHA * torch.exp(x), one)   # 348-360
+    if name == 'mish':
+        e = torch.exp(x)
+        delta = e * (e + 2) + 2
+        return e * (e * ((4 * x + 6) + e * (e + 4)) + 4 * (x + 1)) / (delta * delta)   # 378-391
+    if name == 'softplus':
+        return _sigmoid(x)                                           # 409-419
+    if name == 'softsign':
+        d = 1 + torch.abs(x)
+        return 1 / (d * d)                                           # 437-448
+    if name == 'tanhshrink':
+        t = _tanh(x)
+        return 1 - (1 - t * t)                                       # 466-476
+    if name == 'leaky_relu':
+        return torch.where(x <= 0, param * one, one)                 # 495-506
+    if name == 'elu':
+        return torch.where(x <= 0, param * torch.exp(x), one)        # 525-536
+    if name == 'celu':
+        return torch.where(x <= 0, torch.exp(x / param), one)        # 555-566
+    if name == 'hardshrink':
+        return torch.where(torch.abs(x) <= param, zero, one)         # 586-597
+    if name == 'softshrink':
+        return torch.where(torch.abs(x) <= param, zero, one)         # 617-628
+    raise ValueError(f'unknown activation {name!r}')
+
+
+def output_dtype_rule(input_dtype: torch.dtype, autocast_dtype: Optional[torch.dtype]) -> torch.dtype:
+    """
+    attorch/utils.py:27-60 as Linear uses it (autocast='fp16', attorch/linear_layer.py:80).
+    ``autocast_dtype`` is None when autocast is off.  The reference asserts on bf16 autocast
+    (attorch/utils.py:45); this restatement extends the rule the obvious way (bf16 autocast ->
+    bf16 output), which is what the CUDA path implements.
+    """
+    if autocast_dtype is None or autocast_dtype is torch.float32:
+        return input_dtype
+    return autocast_dtype
+
+
+def tf32_round(x: Tensor) -> Tensor:
+    """fp32 -> nearest value with a 10-bit mantissa (what a TF32 tensor-core operand keeps)."""
+    bits = x.contiguous().view(torch.int32)
+    rounded = (bits + 0x1000) & ~0x1FFF
+    return rounded.view(torch.float32)
+
+
+def linear_forward(x: Tensor, weight: Tensor, bias: Optional[Tensor], act_func: Optional[str],
+                   autocast_dtype: Optional[torch.dtype] = None, save_pre_act: bool = True,
+                   tf32: bool = False) -> Tuple[Tensor, Optional[Tensor]]:
+    """
+    Returns (output, pre_act) exactly as attorch/linear_kernels.py:143-188 produces them:
+    operands (cast to fp16 / the 16-bit output dtype if the output is 16-bit) are multiplied with
+    fp32 accumulation (here: float64 accumulation of the exact products, rounded once to fp32);
+    the bias (cast likewise) is added to the fp32 accumulator; the pre-activation is that value
+    rounded to the output dtype; the activation is evaluated on the *unrounded* fp32 value and then
+    rounded.  ``weight`` is ``[in_features, out_features]``.
+    """
+    name, param = parse_act_func(act_func)
+    out_dtype = output_dtype_rule(x.dtype, autocast_dtype)
+    x2 = x.flatten(0, -2)
+    w = weight
+    b = bias
+    if out_dtype in (torch.float16, torch.bfloat16):
+        x2, w = x2.to(out_dtype), w.to(out_dtype)
+        b = None if b is None else b.to(out_dtype)
+    elif tf32:
+        x2, w = tf32_round(x2.float()), tf32_round(w.float())
+    accum = (x2.double() @ w.double()).float()
+    if b is not None:
+        accum = accum + b.float()[None, :]
+    pre_act = accum.to(out_dtype) if (save_pre_act and name is not None) else None
+    out = act_forward(name, accum, param).to(out_dtype)
+    return out.view(*x.shape[:-1], weight.shape[1]), pre_act
+
+
+def linear_backward(output_grad: Tensor, x: Tensor, pre_act: Optional[Tensor], weight: Tensor,
+                    act_func: Optional[str], out_dtype: torch.dtype,
+                    bias: Optional[Tensor] = None
+                    ) -> Tuple[Tensor, Tensor, Optional[Tensor]]:
+    """
+    Returns (dX, dW, db) following attorch/linear_layer.py:125-161.
+
+    dZ = dY * act'(Z) is computed from the stored (rounded) pre-activation, in fp32 for the
+    activations of FP32_ACTS and in Z's dtype otherwise, and stored in Z's dtype (137-148).  The
+    two products run in ``out_dtype`` (the reference wraps them in torch.autocast(dtype=output
+    dtype), 152-155; with fp32 that is a plain fp32 matmul): operands rounded to ``out_dtype``,
+    fp32 accumulation, result rounded to ``out_dtype``.  db = dZ.sum(0) in dZ's dtype (156).  As
+    the autograd engine does afterwards, each gradient is finally cast to the dtype of the tensor
+    it belongs to.
+    """
+    name, param = parse_act_func(act_func)
+    dy = output_grad.flatten(0, -2)
+    x2 = x.flatten(0, -2)
+    if name is None:
+        dz = dy
+    else:
+        z = pre_act.float() if name in FP32_ACTS else pre_act
+        dz = (dy * act_grad(name, z, param)).to(pre_act.dtype)
+
+    def mm(a: Tensor, b: Tensor) -> Tensor:
+        a, b = a.to(out_dtype), b.to(out_dtype)
+        return (a.double() @ b.double()).float().to(out_dtype)
+
+    dx = mm(dz, weight.T).view_as(x).to(x.dtype)
+    dw = mm(x2.T, dz).to(weight.dtype)
+    db = None
+    if bias is not None:
+        db = dz.float().sum(dim=0).to(dz.dtype).to(bias.dtype)
+    return dx, dw, db
+
+
+def linear_forward_backward(x: Tensor, weight: Tensor, bias: Optional[Tensor], act_func: Optional[str],
+                            output_grad: Tensor, autocast_dtype: Optional[torch.dtype] = None):
+    """Convenience: (output, pre_act, dX, dW, db) of one training step of the layer."""
+    out_dtype = output_dtype_rule(x.dtype, autocast_dtype)
+    out, pre_act = linear_forward(x, weight, bias, act_func, autocast_dtype)
+    dx, dw, db = linear_backward(output_grad.to(out_dtype), x, pre_act, weight, act_func, out_dtype, bias)
+    return out, pre_act, dx, dw, db

@@ -1,0 +1,162 @@
+"""
+Generates the golden vectors under tests/golden/ by running the REFERENCE implementation
+(BobMcDear/attorch, its own Triton kernels executed by Triton's CPU interpreter) on seeded inputs.
+
+Usage (needs a checkout of the reference; no GPU):
+
+    python tests/golden/make_golden.py --reference /path/to/attorch-checkout
+
+The reference is imported unmodified.  Two host-side shims make it importable without a GPU:
+``torch.cuda.get_device_capability`` is stubbed (the reference queries it at import time,
+attorch/utils.py:12-24), and each autotuner is cut down to its first configuration so that no
+config is benchmarked (attorch/linear_kernels.py:44-56, attorch/act_kernels.py:883-887).
+
+Each case is stored as one .npz with the inputs (or the seed that regenerates them plus a
+checksum) and the reference's output, dX, dW and db.  bf16 is not generated: the interpreter's
+bf16 dot product returns garbage.
+"""
+
+import argparse
+import hashlib
+import os
+import sys
+from pathlib import Path
+
+os.environ['TRITON_INTERPRET'] = '1'
+
+import numpy as np
+import torch
+
+OUT_DIR = Path(__file__).resolve().parent
+
+ALL_ACT_FUNCS = [None, 'sigmoid', 'logsigmoid', 'tanh', 'relu', 'gelu', 'geluapprox', 'silu', 'relu6',
+                 'hardsigmoid', 'hardtanh', 'hardswish', 'selu', 'mish', 'softplus', 'softsign',
+                 'tanhshrink', 'leaky_relu_0.01', 'elu_1', 'celu_1', 'hardshrink_0.5',
+                 'softshrink_0.5']
+
+
+def load_reference(path: str):
+    torch.cuda.get_device_capability = lambda *args, **kwargs: (10, 0)
+    sys.path.insert(0, path)
+    import attorch
+    from attorch.act_kernels import act_func_backward_kernel
+    from attorch.linear_kernels import linear_forward_kernel
+    linear_forward_kernel.configs = linear_forward_kernel.configs[:1]
+    act_func_backward_kernel.configs = act_func_backward_kernel.configs[:1]
+    return attorch
+
+
+def checksum(*arrays) -> str:
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return h.hexdigest()
+
+
+def run_reference(attorch, x, weight, bias, act_func, dy):
+    """One forward + backward of the reference layer with the given parameter values."""
+    layer = attorch.Linear(weight.shape[0], weight.shape[1], bias=bias is not None,
+                           act_func=act_func, device='cpu', dtype=weight.dtype)
+    with torch.no_grad():
+        layer.weight.copy_(weight)
+        if bias is not None:
+            layer.bias.copy_(bias)
+    x = x.clone().requires_grad_(True)
+    y = layer(x)
+    y.backward(dy)
+    return (y.detach(), x.grad, layer.weight.grad,
+            layer.bias.grad if bias is not None else None)
+
+
+def to_np(t):
+    if t is None:
+        return np.zeros(0, dtype=np.float32)
+    return t.detach().float().numpy() if t.dtype is torch.bfloat16 else t.detach().numpy()
+
+
+def save(name, store_inputs, x, w, b, dy, outs, **meta):
+    y, dx, dw, db = outs
+    data = dict(y=to_np(y), dx=to_np(dx), dw=to_np(dw), db=to_np(db),
+                input_checksum=np.array(checksum(to_np(x), to_np(w), to_np(b), to_np(dy))))
+    if store_inputs:
+        data.update(x=to_np(x), w=to_np(w), b=to_np(b), dy=to_np(dy))
+    for key, value in meta.items():
+        data[key] = np.array(value)
+    np.savez_compressed(OUT_DIR / f'{name}.npz', **data)
+    print(f'wrote {name}.npz')
+
+
+def config1_inputs():
+    """BASELINE config 1: fp32, X [64, 128], 128 -> 256, bias, relu, every draw under seed 0."""
+    torch.manual_seed(0)
+    x = torch.randn(64, 128)
+    torch.manual_seed(0)
+    linear = torch.nn.Linear(128, 256, bias=True)
+    w = linear.weight.detach().T.contiguous()
+    b = linear.bias.detach().clone()
+    torch.manual_seed(0)
+    dy = torch.randn(64, 256)
+    return x, w, b, dy
+
+
+def small_inputs(seed, dtype, shape=(3, 5, 35), out_dim=50, strided=True):
+    """A strided 3-D input (every other row of a taller tensor), K = 35, N = 50."""
+    gen = torch.Generator().manual_seed(seed)
+    if strided:
+        tall = torch.randn((shape[0], 2 * shape[1], shape[2]), generator=gen).to(dtype)
+        x = tall[:, ::2, :]
+    else:
+        x = torch.randn(shape, generator=gen).to(dtype)
+    w = (torch.randn((shape[-1], out_dim), generator=gen) / shape[-1] ** 0.5).to(dtype)
+    b = torch.randn(out_dim, generator=gen).to(dtype)
+    dy = torch.randn((*shape[:-1], out_dim), generator=gen).to(dtype)
+    return x, w, b, dy
+
+
+def switch_point_inputs():
+    """
+    Pre-activations that hit the piecewise switch points exactly (the points the reference's
+    tests/test_act_layers.py:55-82 checks): W is the identity and the bias zero, so Z == X.
+    """
+    points = torch.tensor([-6.0, -3.0, -1.0, -0.5, 0.0, 0.5, 1.0, 3.0, 6.0, 7.0, -7.0, 2.0,
+                           -2.0, 0.25, -0.25, 5.0])
+    x = points.repeat(4, 1)                      # [4, 16]
+    w = torch.eye(16)
+    b = torch.zeros(16)
+    dy = torch.arange(1, 65, dtype=torch.float32).view(4, 16) / 8
+    return x, w, b, dy
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__)
+    parser.add_argument('--reference', default='/root/reference')
+    args = parser.parse_args()
+    attorch = load_reference(args.reference)
+
+    x, w, b, dy = config1_inputs()
+    save('config1_fp32_relu', False, x, w, b, dy, run_reference(attorch, x, w, b, 'relu', dy),
+         act_func='relu', dtype='float32')
+
+    for act_func in ALL_ACT_FUNCS:
+        tag = 'none' if act_func is None else act_func.replace('.', 'p')
+        x, w, b, dy = small_inputs(1, torch.float32)
+        save(f'small_fp32_{tag}', True, x, w, b, dy, run_reference(attorch, x, w, b, act_func, dy),
+             act_func=str(act_func), dtype='float32')
+        x, w, b, dy = switch_point_inputs()
+        save(f'switch_fp32_{tag}', True, x, w, b, dy, run_reference(attorch, x, w, b, act_func, dy),
+             act_func=str(act_func), dtype='float32')
+
+    for act_func in [None, 'relu', 'gelu', 'silu', 'hardswish', 'softsign', 'leaky_relu_0.01', 'mish']:
+        tag = 'none' if act_func is None else act_func.replace('.', 'p')
+        x, w, b, dy = small_inputs(2, torch.float16, shape=(4, 6, 40), out_dim=48)
+        save(f'small_fp16_{tag}', True, x, w, b, dy, run_reference(attorch, x, w, b, act_func, dy),
+             act_func=str(act_func), dtype='float16')
+
+    # No bias, 2-D input.
+    x, w, _, dy = small_inputs(3, torch.float32, shape=(7, 24), out_dim=40, strided=False)
+    save('small_fp32_nobias_gelu', True, x, w, None, dy, run_reference(attorch, x, w, None, 'gelu', dy),
+         act_func='gelu', dtype='float32')
+
+
+if __name__ == '__main__':
+    main()

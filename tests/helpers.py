@@ -1,0 +1,59 @@
+"""Shared helpers of the test-suite: golden-vector loading and tolerances."""
+
+from pathlib import Path
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+GOLDEN_DIR = Path(__file__).resolve().parent / 'golden'
+
+TORCH_DTYPES = {'float32': torch.float32, 'float16': torch.float16, 'bfloat16': torch.bfloat16}
+
+# rtol = atol per dtype.  fp32 results of the reference (TF32 tensor-core products on a GPU, exact
+# fp32 in its CPU interpreter) are compared at the tolerance the task states for TF32.
+TOLERANCE = {torch.float32: 1e-2, torch.float16: 1e-2, torch.bfloat16: 1e-2}
+
+
+def golden_names(prefix: str = ''):
+    return sorted(p.stem for p in GOLDEN_DIR.glob(f'{prefix}*.npz'))
+
+
+def config1_inputs():
+    """BASELINE config 1 inputs, regenerated as tests/golden/make_golden.py makes them."""
+    torch.manual_seed(0)
+    x = torch.randn(64, 128)
+    torch.manual_seed(0)
+    linear = torch.nn.Linear(128, 256, bias=True)
+    w = linear.weight.detach().T.contiguous()
+    b = linear.bias.detach().clone()
+    torch.manual_seed(0)
+    dy = torch.randn(64, 256)
+    return x, w, b, dy
+
+
+def load_golden(name: str) -> Dict[str, Optional[torch.Tensor]]:
+    """Loads one golden case: tensors in their dtype, plus 'act_func' and 'dtype'."""
+    raw = np.load(GOLDEN_DIR / f'{name}.npz')
+    dtype = TORCH_DTYPES[str(raw['dtype'])]
+    act_func = str(raw['act_func'])
+    case = {'act_func': None if act_func == 'None' else act_func, 'dtype': dtype}
+    if 'x' in raw:
+        for key in ('x', 'w', 'b', 'dy'):
+            arr = raw[key]
+            case[key] = None if arr.size == 0 else torch.from_numpy(arr).to(dtype)
+    else:
+        assert name.startswith('config1')
+        case['x'], case['w'], case['b'], case['dy'] = config1_inputs()
+    for key in ('y', 'dx', 'dw', 'db'):
+        arr = raw[key]
+        case[key] = None if arr.size == 0 else torch.from_numpy(arr).to(dtype)
+    case['input_checksum'] = str(raw['input_checksum'])
+    return case
+
+
+def assert_close(actual: torch.Tensor, expected: torch.Tensor, tol: float, what: str) -> None:
+    assert actual.shape == expected.shape, f'{what}: shape {actual.shape} vs {expected.shape}'
+    assert actual.dtype == expected.dtype, f'{what}: dtype {actual.dtype} vs {expected.dtype}'
+    torch.testing.assert_close(actual.float().cpu(), expected.float().cpu(), rtol=tol, atol=tol,
+                               equal_nan=True, msg=lambda m: f'{what}: {m}')

@@ -1,0 +1,284 @@
+"""
+GPU parity tests of the fused linear layer: the CUDA kernels, called through the C ABI by
+attorch_b200.Linear, against (1) golden vectors produced by the reference itself and (2) the CPU
+oracle on seeded inputs.  Tolerance: rtol = atol = 1e-2 for bf16 / fp16 / TF32 (fp32 accumulation),
+1e-4 where the exact-fp32 generic kernel is forced; shapes and dtypes must match exactly.
+"""
+
+import pytest
+import torch
+
+import attorch_b200
+from attorch_b200 import _lib
+from oracle import linear_oracle as oracle
+from tests.helpers import assert_close, golden_names, load_golden
+
+pytestmark = pytest.mark.gpu
+
+DEV = 'cuda'
+TOL = 1e-2
+
+
+def make_layer(w, b, act_func, dtype):
+    layer = attorch_b200.Linear(w.shape[0], w.shape[1], bias=b is not None, act_func=act_func,
+                                device=DEV, dtype=dtype)
+    with torch.no_grad():
+        layer.weight.copy_(w)
+        if b is not None:
+            layer.bias.copy_(b)
+    return layer
+
+
+def run_layer(x, w, b, act_func, dy, autocast_dtype=None, flags=0, param_dtype=None):
+    """Forward + backward on the GPU; returns (y, dx, dw, db) on the CPU."""
+    layer = make_layer(w, b, act_func, param_dtype or w.dtype)
+    xg = x.to(DEV).requires_grad_(True)
+    previous = attorch_b200.set_gemm_flags(flags)
+    try:
+        with torch.autocast('cuda', dtype=autocast_dtype or torch.float16,
+                            enabled=autocast_dtype is not None):
+            y = layer(xg)
+        y.backward(dy.to(DEV).to(y.dtype))
+        attorch_b200.check_status()
+    finally:
+        attorch_b200.set_gemm_flags(previous)
+    db = layer.bias.grad.cpu() if b is not None else None
+    return y.detach().cpu(), xg.grad.cpu(), layer.weight.grad.cpu(), db
+
+
+def check_against(expected, got, tol, has_bias=True):
+    names = ('output', 'input grad', 'weight grad', 'bias grad')
+    for name, e, g in zip(names, expected, got):
+        if name == 'bias grad' and not has_bias:
+            assert g is None
+            continue
+        assert_close(g, e, tol, name)
+
+
+# ------------------------------------------------------------------------------------------------
+# 1. Golden vectors made by the reference
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize('name', golden_names())
+def test_golden(name):
+    case = load_golden(name)
+    got = run_layer(case['x'], case['w'], case['b'], case['act_func'], case['dy'])
+    expected = (case['y'], case['dx'], case['dw'], case['db'])
+    check_against(expected, got, TOL, has_bias=case['b'] is not None)
+
+
+@pytest.mark.parametrize('name', golden_names('switch_'))
+def test_golden_switch_points_exact_on_generic_kernel(name):
+    """Exact-fp32 kernel: the piecewise conventions at the switch points are bit-exact."""
+    case = load_golden(name)
+    act = case['act_func']
+    if act is not None and act.split('_')[0] in oracle.FP32_ACTS | {'softsign'}:
+        pytest.skip('no switch point')
+    got = run_layer(case['x'], case['w'], case['b'], act, case['dy'], flags=_lib.FLAG_FORCE_GENERIC)
+    assert torch.equal(got[0], case['y'])
+    assert torch.equal(got[1], case['dx'])
+
+
+# ------------------------------------------------------------------------------------------------
+# 2. Seeded inputs against the oracle, per kernel family
+# ------------------------------------------------------------------------------------------------
+def seeded(shape, out_dim, dtype, seed=0, bias=True, scale=1.0):
+    gen = torch.Generator().manual_seed(seed)
+    x = (torch.randn(shape, generator=gen) * scale).to(dtype)
+    w = (torch.randn((shape[-1], out_dim), generator=gen) / shape[-1] ** 0.5).to(dtype)
+    b = torch.randn(out_dim, generator=gen).to(dtype) if bias else None
+    dy = torch.randn((*shape[:-1], out_dim), generator=gen).to(dtype)
+    return x, w, b, dy
+
+
+SHAPES = [
+    ((128, 64), 256),        # exactly one tile, one k-block
+    ((256, 512), 512),       # several tiles and k-blocks
+    ((300, 264), 520),       # ragged in M, K and N
+    ((4, 50, 128), 96),      # 3-D input, narrow N
+    ((1000, 72), 40),        # short K, N below one MMA atom width of 64
+    ((129, 2048), 136),      # long K
+]
+FAMILIES = [('tcgen05', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK),
+            ('streamk', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_FORCE_STREAMK),
+            ('generic', _lib.FLAG_FORCE_GENERIC)]
+
+
+@pytest.mark.parametrize('family,flags', FAMILIES)
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize('shape,out_dim', SHAPES)
+@pytest.mark.parametrize('act_func', [None, 'gelu', 'relu'])
+def test_oracle_parity(family, flags, dtype, shape, out_dim, act_func):
+    x, w, b, dy = seeded(shape, out_dim, dtype)
+    expected = oracle.linear_forward_backward(x, w, b, act_func, dy)
+    got = run_layer(x, w, b, act_func, dy, flags=flags)
+    tol = 1e-4 if (family == 'generic' and dtype is torch.float32) else TOL
+    check_against((expected[0], expected[2], expected[3], expected[4]), got, tol)
+
+
+@pytest.mark.parametrize('act_func', oracle.ALL_ACT_FUNCS)
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_every_activation(act_func, dtype):
+    x, w, b, dy = seeded((200, 192), 320, dtype, seed=3)
+    expected = oracle.linear_forward_backward(x, w, b, act_func, dy)
+    got = run_layer(x, w, b, act_func, dy)
+    check_against((expected[0], expected[2], expected[3], expected[4]), got, TOL)
+
+
+@pytest.mark.parametrize('autocast_dtype', [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize('input_dtype', [torch.float32, torch.float16])
+def test_autocast(autocast_dtype, input_dtype):
+    """fp32 parameters under autocast: 16-bit output, gradients in the parameters' dtypes."""
+    x, w, b, dy = seeded((6, 40, 256), 384, torch.float32, seed=5)
+    x = x.to(input_dtype)
+    y, pre_act, dx, dw, db = oracle.linear_forward_backward(x, w, b, 'silu', dy, autocast_dtype)
+    got = run_layer(x, w, b, 'silu', dy, autocast_dtype=autocast_dtype)
+    assert got[0].dtype is autocast_dtype
+    assert got[1].dtype is input_dtype and got[2].dtype is torch.float32 and got[3].dtype is torch.float32
+    check_against((y, dx, dw, db), got, TOL)
+
+
+# ------------------------------------------------------------------------------------------------
+# 3. Edge cases of the drop-in contract
+# ------------------------------------------------------------------------------------------------
+def test_strided_input_and_expanded_grad():
+    """Non-contiguous input; y.sum().backward() hands backward a zero-stride gradient."""
+    torch.manual_seed(0)
+    tall = torch.randn(8, 20, 64)
+    x = tall[:, ::2, :]
+    w = torch.randn(64, 48) / 8
+    b = torch.randn(48)
+    layer = make_layer(w, b, 'tanh', torch.float32)
+    xg = x.to(DEV).requires_grad_(True)
+    y = layer(xg)
+    y.sum().backward()
+    attorch_b200.check_status()
+    e_y, _, e_dx, e_dw, e_db = oracle.linear_forward_backward(x, w, b, 'tanh', torch.ones(8, 10, 48))
+    check_against((e_y, e_dx, e_dw, e_db),
+                  (y.detach().cpu(), xg.grad.cpu(), layer.weight.grad.cpu(), layer.bias.grad.cpu()), TOL)
+
+
+@pytest.mark.parametrize('shape,out_dim', [((1, 8000), 16), ((12288, 1), 16), ((5, 196), 196),
+                                           ((2048, 64, 16), 96), ((3, 7), 1)])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float16])
+def test_reference_test_matrix_odd_shapes(shape, out_dim, dtype):
+    """Shapes from the reference's own test matrix that TMA cannot address or that are tiny."""
+    x, w, b, dy = seeded(shape, out_dim, dtype, seed=7)
+    expected = oracle.linear_forward_backward(x, w, b, 'relu', dy)
+    got = run_layer(x, w, b, 'relu', dy)
+    check_against((expected[0], expected[2], expected[3], expected[4]), got, TOL)
+
+
+def test_empty_batch():
+    layer = attorch_b200.Linear(32, 48, act_func='relu', device=DEV)
+    x = torch.empty(0, 32, device=DEV, requires_grad=True)
+    y = layer(x)
+    assert y.shape == (0, 48)
+    y.sum().backward()
+    attorch_b200.check_status()
+    assert x.grad.shape == (0, 32)
+    assert torch.count_nonzero(layer.weight.grad) == 0 and torch.count_nonzero(layer.bias.grad) == 0
+
+
+def test_requires_grad_combinations():
+    x, w, b, dy = seeded((64, 128), 128, torch.float32, seed=9)
+    layer = make_layer(w, b, 'gelu', torch.float32)
+    # Input without grad: only parameter gradients.
+    y = layer(x.to(DEV))
+    y.backward(dy.to(DEV))
+    assert layer.weight.grad is not None and layer.bias.grad is not None
+    # Frozen parameters: only the input gradient.
+    frozen = make_layer(w, b, 'gelu', torch.float32)
+    for p in frozen.parameters():
+        p.requires_grad_(False)
+    xg = x.to(DEV).requires_grad_(True)
+    frozen(xg).backward(dy.to(DEV))
+    assert xg.grad is not None and frozen.weight.grad is None and frozen.bias.grad is None
+    # no_grad forward.
+    with torch.no_grad():
+        y2 = layer(x.to(DEV))
+    assert not y2.requires_grad
+    attorch_b200.check_status()
+    torch.testing.assert_close(y2, y.detach())
+
+
+def test_error_behaviour():
+    layer = attorch_b200.Linear(16, 8, device=DEV)
+    with pytest.raises(AssertionError, match='Incompatible input'):
+        layer(torch.randn(4, 15, device=DEV))
+    with pytest.raises(IndexError):
+        layer(torch.randn(16, device=DEV))
+    with pytest.raises(ValueError):
+        attorch_b200.Linear(16, 8, act_func='leaky_relu', device=DEV)(torch.randn(2, 16, device=DEV))
+    with pytest.raises(ValueError):
+        attorch_b200.Linear(16, 8, act_func='swish', device=DEV)(torch.randn(2, 16, device=DEV))
+    with pytest.raises(RuntimeError, match='no CPU fallback'):
+        attorch_b200.Linear(16, 8, device='cpu')(torch.randn(2, 16))
+
+
+def test_state_dict_layout():
+    layer = attorch_b200.Linear(24, 40, device=DEV)
+    sd = layer.state_dict()
+    assert sd['weight'].shape == (24, 40) and sd['bias'].shape == (40,)
+    assert layer.in_features == 24 and layer.out_features == 40
+
+
+def test_bitwise_repeatable():
+    """Same inputs, same bits: catches pipeline races in the warp-specialised kernels."""
+    x, w, b, dy = seeded((1024, 1024), 1024, torch.bfloat16, seed=11)
+    first = run_layer(x, w, b, 'gelu', dy)
+    for _ in range(5):
+        again = run_layer(x, w, b, 'gelu', dy)
+        for a, c in zip(first, again):
+            assert torch.equal(a, c)
+
+
+# ------------------------------------------------------------------------------------------------
+# 4. Full-size BASELINE configurations, checked through sub-sampled oracle products
+# ------------------------------------------------------------------------------------------------
+def test_config2_full_size_bf16():
+    """
+    BASELINE config 2 (bf16, M = 8192, 4096 -> 4096, gelu, bias).  The oracle is evaluated on 48
+    sampled rows (output, dX) and 48 sampled input features (dW); db in full.
+    """
+    torch.manual_seed(0)
+    M, K, N = 8192, 4096, 4096
+    x = torch.randn(M, K).bfloat16()
+    lin = torch.nn.Linear(K, N)
+    w = lin.weight.detach().T.contiguous().bfloat16()
+    b = lin.bias.detach().bfloat16()
+    dy = (torch.randn(M, N) * 0.01).bfloat16()
+    y, dx, dw, db = run_layer(x, w, b, 'gelu', dy)
+    rows = torch.randperm(M)[:48]
+    e_y, e_z = oracle.linear_forward(x[rows], w, b, 'gelu')
+    assert_close(y[rows], e_y, TOL, 'output rows')
+    e_dx, _, _ = oracle.linear_backward(dy[rows], x[rows], e_z, w, 'gelu', torch.bfloat16, b)
+    assert_close(dx[rows], e_dx, TOL, 'dX rows')
+    # dW[k, :] needs dZ for every row: recompute dZ from the GPU's own output path via the oracle
+    # on the full Z would take minutes on a CPU, so use the identity dW[k, :] = X[:, k]^T dZ with dZ
+    # taken from the oracle on a row subset for a *reduced* problem instead: run the layer again on
+    # that subset and compare all of dW and db.
+    sub = torch.randperm(M)[:512]
+    y2, dx2, dw2, db2 = run_layer(x[sub], w, b, 'gelu', dy[sub], flags=_lib.FLAG_NO_STREAMK)
+    e = oracle.linear_forward_backward(x[sub], w, b, 'gelu', dy[sub])
+    check_against((e[0], e[2], e[3], e[4]), (y2, dx2, dw2, db2), TOL)
+    # Size-independent property at full size: the gradients are linear in dY.
+    y3, dx3, dw3, db3 = run_layer(x, w, b, 'gelu', dy * 2)
+    torch.testing.assert_close(dw3.float(), 2 * dw.float(), rtol=2e-2, atol=1e-3)
+    torch.testing.assert_close(db3.float(), 2 * db.float(), rtol=2e-2, atol=1e-3)
+    torch.testing.assert_close(dx3.float(), 2 * dx.float(), rtol=2e-2, atol=1e-4)
+
+
+@pytest.mark.parametrize('m', [1, 8, 32, 128])
+def test_config4_skinny_fp16(m):
+    """BASELINE config 4 at reduced N (fp16, forward only, K = 8192): the swap-AB stream-K kernel."""
+    gen = torch.Generator().manual_seed(m)
+    K, N = 8192, 4096
+    x = torch.randn(m, K, generator=gen).half()
+    w = (torch.randn(K, N, generator=gen) * 0.02).half()
+    layer = make_layer(w, None, None, torch.float16)
+    with torch.no_grad():
+        y = layer(x.to(DEV))
+    attorch_b200.check_status()
+    assert _lib.load().ab200_last_path() == _lib.PATH_STREAMK
+    e_y, _ = oracle.linear_forward(x, w, None, None)
+    assert_close(y.cpu(), e_y, TOL, 'output')
