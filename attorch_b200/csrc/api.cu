@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdint>
 #include <cstring>
 
@@ -15,7 +16,7 @@ namespace ab200 {
 namespace {
 
 thread_local int g_last_path = 0;
-thread_local int64_t g_launches = 0;
+std::atomic<int64_t> g_launches{0};   // all host threads: backward runs on autograd's threads
 
 // ------------------------------------------------------------------------------------------------
 // Driver entry point for tensor-map encoding, resolved through the runtime so that the library
@@ -39,9 +40,10 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D map over a row-major matrix: `inner` contiguous elements per row, `outer` rows, row pitch in
-// bytes; box = box_inner x box_outer elements; 128-byte swizzle; out-of-range elements read as zero.
+// bytes; box = box_inner x box_outer elements; 128-byte swizzle (of 32-byte units if `atom32`, the
+// layout MN-major tf32 operands need); out-of-range elements read as zero.
 int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
-              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32 = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return ERR_DRIVER;
   const CUtensorMapDataType dt = dtype == DT_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
@@ -52,7 +54,8 @@ int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uin
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? OK : ERR_TENSOR_MAP;
 }
@@ -74,13 +77,7 @@ int sm_count() {
 bool valid_dtype(int dt) { return dt == DT_F32 || dt == DT_F16 || dt == DT_BF16; }
 bool valid_act(int act) { return act >= 0 && act < ACT_COUNT; }
 
-// A matrix operand as the GEMM sees it: `rows` x `cols` logical elements, element strides.
-struct Operand {
-  const void* ptr;
-  long long stride_row, stride_col;
-};
-
-// Can TMA address this matrix with `contig` as the unit-stride dimension?
+// Can TMA address this matrix: unit inner stride, 16-byte aligned base and row pitch?
 bool tma_ok(const void* p, long long pitch_elems, long long unit_stride, int elt) {
   if (unit_stride != 1) return false;
   if (reinterpret_cast<uintptr_t>(p) & 15) return false;
@@ -106,12 +103,12 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   // K-major: inner = K, outer = M (or N); box = one 128-byte row of K x tile rows.
   // MN-major: inner = M (or N), outer = K; box = 128 bytes of M/N x BKE rows of K.
   if (Cfg::A_MN)
-    rc = encode_2d(&ta, p.op_dtype, p.a, p.g.M, p.g.K, p.a_pitch * elt, Cfg::MN_ATOM, Cfg::BKE);
+    rc = encode_2d(&ta, p.op_dtype, p.a, p.g.M, p.g.K, p.a_pitch * elt, Cfg::MN_ATOM, Cfg::BKE, Cfg::MN_BASE32);
   else
     rc = encode_2d(&ta, p.op_dtype, p.a, p.g.K, p.g.M, p.a_pitch * elt, Cfg::BKE, Cfg::BM);
   if (rc != OK) return rc;
   if (Cfg::B_MN)
-    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.N, p.g.K, p.b_pitch * elt, Cfg::MN_ATOM, Cfg::BKE);
+    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.N, p.g.K, p.b_pitch * elt, Cfg::MN_ATOM, Cfg::BKE, Cfg::MN_BASE32);
   else
     rc = encode_2d(&tb, p.op_dtype, p.b, p.g.K, p.g.N, p.b_pitch * elt, Cfg::BKE, Cfg::BN);
   if (rc != OK) return rc;
@@ -225,7 +222,7 @@ const char* ab200_error_string(int code) {
 }
 
 int ab200_last_path(void) { return g_last_path; }
-int64_t ab200_launch_count(void) { return g_launches; }
+int64_t ab200_launch_count(void) { return g_launches.load(); }
 
 int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N) {
   (void)K;

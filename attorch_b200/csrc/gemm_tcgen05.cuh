@@ -77,6 +77,11 @@ struct GemmCfg {
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;   // power of two for BN in {16..256}
   static constexpr int MN_ATOM = 128 / ELT;      // elements in one 128-byte row of an MN-major tile
   static constexpr int MN_BOX_BYTES = BKE * 128; // one TMA box of an MN-major tile
+  // MN-major tiles of 4-byte elements use the 128-byte swizzle with 32-byte units, whose pattern
+  // repeats every 4 rows of K; everything else the ordinary one (16-byte units, 8 rows).
+  static constexpr bool MN_BASE32 = (ELT == 4);
+  static constexpr uint32_t MN_LAYOUT = MN_BASE32 ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
+  static constexpr uint32_t MN_SBO = MN_BASE32 ? 512 : 1024;
   static constexpr int kThreads = 192;
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be 32, 64, 128 or 256");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM allocation must be a power of two");
@@ -296,10 +301,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int k = 0; k < BKE / Cfg::UMMA_K; ++k) {
             // K-major: the next 32 bytes of every 128-byte row.  MN-major: the next UMMA_K rows.
             const uint64_t a_desc =
-                Cfg::A_MN ? ptx::make_smem_desc(a_addr + k * Cfg::UMMA_K * 128, Cfg::MN_BOX_BYTES, 1024)
+                Cfg::A_MN ? ptx::make_smem_desc(a_addr + k * Cfg::UMMA_K * 128, Cfg::MN_BOX_BYTES,
+                                                Cfg::MN_SBO, Cfg::MN_LAYOUT)
                           : ptx::make_smem_desc(a_addr + k * 32, 16, 1024);
             const uint64_t b_desc =
-                Cfg::B_MN ? ptx::make_smem_desc(b_addr + k * Cfg::UMMA_K * 128, Cfg::MN_BOX_BYTES, 1024)
+                Cfg::B_MN ? ptx::make_smem_desc(b_addr + k * Cfg::UMMA_K * 128, Cfg::MN_BOX_BYTES,
+                                                Cfg::MN_SBO, Cfg::MN_LAYOUT)
                           : ptx::make_smem_desc(b_addr + k * 32, 16, 1024);
             ptx::umma<1, kTf32>(d_tmem, a_desc, b_desc, args.idesc,
                                 (kb > seg.kb0 || k > 0) ? 1u : 0u);

@@ -266,16 +266,21 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // ----------------------------------------------------------------------------------------------
 // Shared-memory matrix descriptor for a 128-byte-swizzled operand tile (base 1024-byte aligned).
 //   K-major  : rows of 128 bytes along K; 8-row groups `sbo` bytes apart; `lbo` unused (1).
-//   MN-major : rows of 128 bytes along M/N (one row per k); 8-k groups `sbo` bytes apart;
-//              128-byte-wide column blocks `lbo` bytes apart.
+//   MN-major : rows of 128 bytes along M/N (one row per k); groups of 8 k-rows (4 for the
+//              32-byte-atom swizzle) `sbo` bytes apart; 128-byte-wide column blocks `lbo` bytes apart.
+// layout_type: 2 = 128-byte swizzle of 16-byte units; 1 = 128-byte swizzle of 32-byte units, the
+// only layout tcgen05 accepts for MN-major operands of 4-byte (tf32) elements.
+constexpr uint32_t kLayoutSw128 = 2;
+constexpr uint32_t kLayoutSw128Base32 = 1;
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes,
+                                                   uint32_t layout_type = kLayoutSw128) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= 1ull << 46;  // descriptor version for sm_100
-  d |= 2ull << 61;  // 128-byte swizzle
+  d |= static_cast<uint64_t>(layout_type) << 61;
   return d;
 }
 

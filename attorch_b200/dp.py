@@ -1,0 +1,111 @@
+"""
+Data-parallel training step for models made of ``attorch_b200.Linear`` layers.
+
+The reference has no distributed code.  This harness covers the one pattern the fused linear layer
+needs at scale: one process per GPU, the batch (token) dimension split evenly across ranks, weights
+replicated, and a SUM all-reduce of every layer's ``dW`` / ``db`` - the only collective, issued with
+``torch.distributed`` (NCCL over NVLink / NVSwitch on GPUs, gloo on CPUs for tests).
+
+Each layer writes its weight and bias gradient straight into a slice of one flat bucket
+(no copy), and as soon as the kernels that produce them are enqueued the bucket slice is
+all-reduced on a side stream while the layer's ``dX`` product - and the backward of the layers
+before it - still run on the compute stream.  Because the upstream gradient is given per token,
+SUM reproduces the single-GPU full-batch gradient.
+"""
+
+from typing import Iterable, List, Optional
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from .linear_layer import Linear
+
+
+def shard_rows(tensor: Tensor, rank: int, world_size: int) -> Tensor:
+    """Contiguous block of rows ``rank`` owns when dim 0 is split evenly over ``world_size`` ranks."""
+    rows = tensor.shape[0]
+    if rows % world_size != 0:
+        raise ValueError(f'{rows} rows do not split evenly over {world_size} ranks')
+    per_rank = rows // world_size
+    return tensor[rank * per_rank:(rank + 1) * per_rank]
+
+
+class GradientBuckets:
+    """
+    One flat gradient buffer per model; every Linear gets views of it as its ``dW`` / ``db``
+    destinations and a callback that all-reduces its slice.
+
+    Args:
+        layers: The Linear layers, in forward order.
+        process_group: Group to reduce over; None for the default group.  With a world size of 1
+            (or torch.distributed not initialised) no collective is issued.
+        overlap: Issue each layer's all-reduce on a side stream as soon as its gradients are
+            enqueued (CUDA only); otherwise reduce everything in ``finish``.
+    """
+    def __init__(self, layers: Iterable[Linear], process_group=None, overlap: bool = True) -> None:
+        self.layers: List[Linear] = list(layers)
+        self.group = process_group
+        self.world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        first = self.layers[0].weight
+        self.device = first.device
+        self.dtype = first.dtype
+        total = sum(layer.weight.numel() + (layer.bias.numel() if layer.bias is not None else 0)
+                    for layer in self.layers)
+        self.flat = torch.zeros(total, dtype=self.dtype, device=self.device)
+        self.slices: List[Tensor] = []
+        self.overlap = overlap and self.device.type == 'cuda' and self.world_size > 1
+        self.comm_stream = torch.cuda.Stream(self.device) if self.overlap else None
+        self._pending: List[torch.cuda.Event] = []
+        offset = 0
+        for index, layer in enumerate(self.layers):
+            if layer.weight.dtype is not self.dtype:
+                raise TypeError('all layers of one bucket must share a parameter dtype')
+            begin = offset
+            n = layer.weight.numel()
+            layer.weight_grad_out = self.flat[offset:offset + n].view_as(layer.weight)
+            offset += n
+            if layer.bias is not None:
+                n = layer.bias.numel()
+                layer.bias_grad_out = self.flat[offset:offset + n]
+                offset += n
+            self.slices.append(self.flat[begin:offset])
+            layer.grad_ready = self._make_callback(index)
+
+    def _make_callback(self, index: int):
+        def grad_ready() -> None:
+            if self.overlap:
+                self._reduce_async(index)
+        return grad_ready
+
+    def _reduce_async(self, index: int) -> None:
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ready)
+            dist.all_reduce(self.slices[index], op=dist.ReduceOp.SUM, group=self.group)
+            done = torch.cuda.Event()
+            done.record(self.comm_stream)
+        self._pending.append(done)
+
+    def finish(self) -> None:
+        """
+        Completes the gradient exchange of one step: after it returns (in stream order on the
+        current stream) every layer's ``.grad`` holds the sum over ranks.
+        """
+        if self.world_size == 1:
+            return
+        if self.overlap:
+            current = torch.cuda.current_stream(self.device)
+            for done in self._pending:
+                current.wait_event(done)
+            self._pending.clear()
+        else:
+            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+
+    def zero_grad(self) -> None:
+        """Drops the ``.grad`` aliases so that the next backward writes the bucket afresh."""
+        for layer in self.layers:
+            layer.weight.grad = None
+            if layer.bias is not None:
+                layer.bias.grad = None

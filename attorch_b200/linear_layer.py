@@ -10,7 +10,6 @@ Triton, no PyTorch matmul and no CPU path: on a machine without the built librar
 CUDA device the layer raises.
 """
 
-import ctypes
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -133,13 +132,15 @@ class LinearAutoGrad(torch.autograd.Function):
     """
     Autodiff for the fused linear layer; same call contract as the reference's
     ``LinearAutoGrad`` (attorch/linear_layer.py:19-161): ``apply(input, weight, bias, act_func)``.
-    Two optional trailing arguments let a caller supply the buffers ``dW`` and ``db`` are written
-    into (e.g. views of a flat all-reduce bucket).
+    Three optional trailing arguments serve data-parallel training: the buffers ``dW`` and ``db``
+    are written into (e.g. views of a flat all-reduce bucket), and a callable that backward invokes
+    once the kernels producing ``dW`` and ``db`` are enqueued and before ``dX`` is, so that the
+    gradient exchange of this layer can overlap the remaining work.
     """
     @staticmethod
     def forward(ctx, input: Tensor, weight: Tensor, bias: Optional[Tensor] = None,
                 act_func: Optional[str] = None, weight_grad_out: Optional[Tensor] = None,
-                bias_grad_out: Optional[Tensor] = None) -> Tensor:
+                bias_grad_out: Optional[Tensor] = None, grad_ready=None) -> Tensor:
         assert weight.ndim == 2, \
             f'Weights must be 2D, received shape {weight.shape}'
         assert bias is None or bias.ndim == 1, \
@@ -206,6 +207,7 @@ class LinearAutoGrad(torch.autograd.Function):
         ctx.weight_dtype = weight.dtype
         ctx.weight_shape = weight.shape
         ctx.has_grad_out = (weight_grad_out is not None, bias_grad_out is not None)
+        ctx.grad_ready = grad_ready
         if requires_grad:
             # Backward multiplies in the output dtype, so the converted operands are what it
             # needs; keeping them avoids converting X and W a second time.
@@ -275,6 +277,8 @@ class LinearAutoGrad(torch.autograd.Function):
                     x_op.stride(0), x_op.stride(1), pre_act_grad.stride(0), pre_act_grad.stride(1),
                     weight_grad.stride(0), _dtype_id(op_dtype), _dtype_id(weight_grad.dtype),
                     status, stream, _gemm_flags), 'ab200_linear_backward_weight')
+            if ctx.grad_ready is not None:
+                ctx.grad_ready()
             if ctx.input_requires_grad:
                 input_grad = torch.empty((batch_dim, in_feat_dim), dtype=ctx.input_dtype, device=device)
                 _lib.check(lib.ab200_linear_backward_input(
@@ -286,7 +290,7 @@ class LinearAutoGrad(torch.autograd.Function):
                 input_grad = input_grad.view(ctx.input_shape)
 
         # One slot per forward argument (attorch/linear_layer.py:158-161 pads with None).
-        return input_grad, weight_grad, bias_grad, None, None, None
+        return input_grad, weight_grad, bias_grad, None, None, None, None
 
 
 class Linear(nn.Linear):
@@ -319,7 +323,9 @@ class Linear(nn.Linear):
         # Optional (dW, db) destination buffers, e.g. views into a gradient bucket.
         self.weight_grad_out: Optional[Tensor] = None
         self.bias_grad_out: Optional[Tensor] = None
+        # Optional callable run in backward once dW and db are enqueued (see LinearAutoGrad).
+        self.grad_ready = None
 
     def forward(self, input: Tensor) -> Tensor:
         return LinearAutoGrad.apply(input, self.weight, self.bias, self.act_func,
-                                    self.weight_grad_out, self.bias_grad_out)
+                                    self.weight_grad_out, self.bias_grad_out, self.grad_ready)

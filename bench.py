@@ -1,0 +1,369 @@
+"""
+Benchmark of the fused linear layer (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c5] [--impl reference]
+
+For N > 1 launch one rank per GPU with torchrun (RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the
+environment).  Rank 0 prints one JSON line.
+
+Workloads (synthetic, seeded; shapes of BASELINE.json's configs):
+  c2  attorch.Linear 4096 -> 4096, bias, gelu, under bf16 autocast with fp32 parameters and fp32
+      input; 8192 tokens per GPU (weak scaling: the global batch is 8192 * N); forward + backward
+      (dX, dW, db); with N > 1 the fp32 dW / db are SUM-all-reduced every step, overlapped with dX.
+  c5  two layers 8192 -> 8192 (gelu + bias, then bias), bf16 parameters, global batch 65536 tokens
+      split over the N GPUs (strong scaling), same all-reduce.
+
+One "step" is one forward + backward of the workload on one batch.  ``value`` is the whole-job
+TFLOP/s at 6 * M * K * N floating-point operations per layer and step with the inputs resident in
+HBM; ``e2e`` is the same through the same module with the step's input copied from pinned host
+memory and the bias gradient read back every step (copies double-buffered on a side stream).
+``--impl reference`` times the CPU computation the reference's tests compare against
+(torch.nn.Linear + activation, all host cores) on a bounded sample of the same workload.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PEAK_FALLBACK = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0}
+
+# DRAM bytes per launch of the dominant kernel (forward GEMM of c2) from the ncu capture summarised
+# in profiles/; None until a capture exists.
+NCU_DRAM_BYTES_PER_LAUNCH = None
+
+WORKLOADS = {
+    'c2': dict(layers=[(4096, 4096, 'gelu', True)], tokens_per_gpu=8192, global_tokens=None,
+               param_dtype=torch.float32, input_dtype=torch.float32, autocast=torch.bfloat16,
+               scaling='weak'),
+    'c5': dict(layers=[(8192, 8192, 'gelu', True), (8192, 8192, None, True)], tokens_per_gpu=None,
+               global_tokens=65536, param_dtype=torch.bfloat16, input_dtype=torch.bfloat16,
+               autocast=None, scaling='strong'),
+}
+
+
+def measured_peaks():
+    path = ROOT / 'MEASURED_PEAKS.json'
+    if path.exists():
+        data = json.loads(path.read_text())
+        return {k: float(data[k]) for k in PEAK_FALLBACK}, 'measured'
+    return dict(PEAK_FALLBACK), 'fallback'
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    def __init__(self, index: int) -> None:
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _run(self) -> None:
+        nv = self._nvml
+        names = {'hw_slowdown': 'nvmlClocksEventReasonHwSlowdown',
+                 'hw_thermal_slowdown': 'nvmlClocksEventReasonHwThermalSlowdown',
+                 'sw_thermal_slowdown': 'nvmlClocksEventReasonSwThermalSlowdown',
+                 'sw_power_cap': 'nvmlClocksEventReasonSwPowerCap'}
+        fallback = {'hw_slowdown': 0x8, 'hw_thermal_slowdown': 0x40, 'sw_thermal_slowdown': 0x20,
+                    'sw_power_cap': 0x4}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+                for name, attr in names.items():
+                    bit = getattr(nv, attr, fallback[name])
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {'sm_mhz': None, 'sm_max_mhz': self.max_mhz, 'reasons': ['unavailable']}
+        return {'sm_mhz': statistics.median(self.samples), 'sm_max_mhz': self.max_mhz,
+                'reasons': sorted(self.reasons), 'samples': len(self.samples)}
+
+
+def flops_per_step(spec, tokens):
+    return sum(6.0 * tokens * k * n for (k, n, _, _) in spec['layers'])
+
+
+def run_reference(args, spec, world_size, rank):
+    """CPU arm: torch.nn.Linear + activation on all host cores, bounded sample of the workload."""
+    if rank != 0:
+        return
+    from oracle.cpu_baseline import time_torch_cpu_linear
+    sample_rows = 512
+    seconds, threads = 0.0, 1
+    for (k, n, act, bias) in spec['layers']:
+        r = time_torch_cpu_linear(sample_rows, k, n, act, bias, None, args.steps, args.warmup)
+        seconds += r['seconds_per_step']
+        threads = r['threads']
+    tflops = flops_per_step(spec, sample_rows) / seconds / 1e12
+    sample = (f'{sample_rows} of the batch rows per step, torch.nn.Linear + activation fwd+bwd in fp32 '
+              f'on {threads} host threads')
+    line = {
+        'impl': 'reference', 'metric': 'linear_fwd_bwd_tflops', 'value': tflops, 'unit': 'TFLOP/s',
+        'n_gpus': world_size, 'steps': args.steps, 'warmup': args.warmup,
+        'ms_per_step': seconds * 1e3, 'higher_is_better': True, 'scaling': spec['scaling'],
+        'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': args.workload, 'sample': sample},
+        'cpu_baseline': {'value': tflops, 'unit': 'TFLOP/s', 'cores': threads, 'kind': 'port',
+                         'sample': sample},
+        'e2e': {'value': tflops, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    parser.add_argument('--gpus', type=int, default=1)
+    parser.add_argument('--steps', type=int, default=50)
+    parser.add_argument('--warmup', type=int, default=10)
+    parser.add_argument('--workload', choices=sorted(WORKLOADS), default='c2')
+    parser.add_argument('--impl', choices=['b200', 'reference'], default='b200')
+    parser.add_argument('--no-cpu-baseline', action='store_true')
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3)
+    spec = WORKLOADS[args.workload]
+
+    world_size = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if args.impl == 'reference':
+        run_reference(args, spec, max(world_size, args.gpus), rank)
+        return
+
+    import torch.distributed as dist
+
+    import attorch_b200
+    from attorch_b200 import _lib
+    from attorch_b200.dp import GradientBuckets
+
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: the layer has no CPU fallback')
+    lib = _lib.load()
+    torch.cuda.set_device(local_rank)
+    device = torch.device('cuda', local_rank)
+    if world_size > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', device_id=device)
+
+    tokens = spec['tokens_per_gpu'] or spec['global_tokens'] // world_size
+    total_tokens = tokens * world_size
+    torch.manual_seed(0)
+    layers = [attorch_b200.Linear(k, n, bias=bias, act_func=act, device=device,
+                                  dtype=spec['param_dtype'])
+              for (k, n, act, bias) in spec['layers']]
+    buckets = GradientBuckets(layers)
+    k_in, n_out = spec['layers'][0][0], spec['layers'][-1][1]
+    gen = torch.Generator(device=device).manual_seed(1 + rank)
+    x_dev = torch.randn(tokens, k_in, device=device, generator=gen).to(spec['input_dtype'])
+    x_dev.requires_grad_(True)
+    out_dtype = spec['autocast'] or spec['param_dtype']
+    dy = (torch.randn(tokens, n_out, device=device, generator=gen) * 0.01).to(out_dtype)
+
+    def step(x):
+        buckets.zero_grad()
+        x.grad = None
+        with torch.autocast('cuda', dtype=spec['autocast'] or torch.bfloat16,
+                            enabled=spec['autocast'] is not None):
+            h = x
+            for layer in layers:
+                h = layer(h)
+        h.backward(dy)
+        buckets.finish()
+
+    def barrier():
+        if world_size > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world_size == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------------------------------------------------------- device-resident timing
+    for _ in range(args.warmup):
+        step(x_dev)
+    barrier()
+    attorch_b200.check_status()
+    launches_before = lib.ab200_launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            step(x_dev)
+        stop.record()
+        barrier()
+    launches = lib.ab200_launch_count() - launches_before
+    ms_total = max_over_ranks(start.elapsed_time(stop))
+    attorch_b200.check_status()
+    ms_per_step = ms_total / args.steps
+    step_flops = flops_per_step(spec, tokens)
+    value = step_flops * world_size / (ms_per_step * 1e-3) / 1e12
+
+    # ---------------------------------------------------------------- end to end with host buffers
+    host_x = [torch.randn(tokens, k_in).to(spec['input_dtype']).pin_memory() for _ in range(2)]
+    dev_x = [torch.empty_like(x_dev).requires_grad_(True) for _ in range(2)]
+    bias_grad_host = torch.empty(n_out, dtype=spec['param_dtype']).pin_memory()
+    copy_stream = torch.cuda.Stream(device)
+    copied = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_loop(n_steps):
+        compute = torch.cuda.current_stream()
+        with torch.cuda.stream(copy_stream):
+            dev_x[0].data.copy_(host_x[0], non_blocking=True)
+            copied[0].record(copy_stream)
+        for i in range(n_steps):
+            cur, nxt = i % 2, (i + 1) % 2
+            if i + 1 < n_steps:
+                with torch.cuda.stream(copy_stream):
+                    if i >= 1:
+                        copy_stream.wait_event(consumed[nxt])
+                    dev_x[nxt].data.copy_(host_x[nxt], non_blocking=True)
+                    copied[nxt].record(copy_stream)
+            compute.wait_event(copied[cur])
+            step(dev_x[cur])
+            consumed[cur].record(compute)
+            bias_grad_host.copy_(layers[-1].bias.grad, non_blocking=True)
+        compute.synchronize()
+
+    e2e_loop(3)
+    barrier()
+    e2e_steps = max(10, min(args.steps, 40))
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    e2e_loop(e2e_steps)
+    t1.record()
+    barrier()
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1)) / e2e_steps
+    e2e_value = step_flops * world_size / (e2e_ms * 1e-3) / 1e12
+    attorch_b200.check_status()
+
+    # ---------------------------------------------------------------- roofline of the dominant kernel
+    # The tcgen05 GEMM, launched through the C ABI exactly as the layer launches it (forward of the
+    # first layer: X[M, K] * W[K, N] with bias, gelu and the pre-activation store), event-timed on
+    # the launching stream.
+    peaks, peak_source = measured_peaks()
+    k0, n0, act0, _ = spec['layers'][0]
+    op_dtype = out_dtype
+    xo = torch.randn(tokens, k0, device=device).to(op_dtype)
+    wo = (torch.randn(k0, n0, device=device) / k0 ** 0.5).to(op_dtype)
+    bo = torch.randn(n0, device=device).to(op_dtype)
+    yo, zo = torch.empty(tokens, n0, device=device, dtype=op_dtype), torch.empty(tokens, n0, device=device, dtype=op_dtype)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    dt_id = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[op_dtype]
+    from attorch_b200.acts import act_id, parse_act_func
+    name, param = parse_act_func(act0)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def launch_fwd():
+        rc = lib.ab200_linear_forward(xo.data_ptr(), wo.data_ptr(), bo.data_ptr(), zo.data_ptr(), yo.data_ptr(),
+                                      tokens, k0, n0, k0, 1, n0, 1, n0, n0, dt_id, dt_id, dt_id,
+                                      act_id(name), param or 0.0, None, 0, status.data_ptr(), stream,
+                                      _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK)
+        _lib.check(rc, 'ab200_linear_forward')
+
+    for _ in range(5):
+        launch_fwd()
+    torch.cuda.synchronize()
+    reps = 30
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for _ in range(reps):
+        launch_fwd()
+    r1.record()
+    torch.cuda.synchronize()
+    kernel_ms = r0.elapsed_time(r1) / reps
+    achieved = 2.0 * tokens * k0 * n0 / (kernel_ms * 1e-3) / 1e12
+    roofline = {'bound': 'tensor', 'achieved': achieved, 'peak': peaks['bf16_tflops'], 'unit': 'TFLOP/s',
+                'frac': achieved / peaks['bf16_tflops'], 'traffic': NCU_DRAM_BYTES_PER_LAUNCH,
+                'kernel': 'gemm_tcgen05_kernel (forward, bias + gelu + pre-activation epilogue)',
+                'kernel_ms': kernel_ms, 'peak_source': f'{peak_source} (cuBLAS bf16 burst)',
+                'frac_of_nominal_2250': achieved / 2250.0}
+
+    if rank != 0:
+        if world_size > 1:
+            dist.destroy_process_group()
+        return
+
+    line = {
+        'metric': 'linear_fwd_bwd_tflops', 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world_size,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step,
+        'higher_is_better': True, 'scaling': spec['scaling'], 'vs_baseline': None,
+        'dtype': 'bf16', 'data': 'synthetic',
+        'config': {'workload': args.workload,
+                   'layers': [f'{k}->{n} act={act} bias={bias}' for (k, n, act, bias) in spec['layers']],
+                   'tokens_per_gpu': tokens, 'global_tokens': total_tokens,
+                   'params': str(spec['param_dtype']).replace('torch.', ''),
+                   'input': str(spec['input_dtype']).replace('torch.', ''),
+                   'autocast': str(spec['autocast']).replace('torch.', ''),
+                   'parallelism': f'dp{world_size}',
+                   'collective': 'none' if world_size == 1 else 'NCCL all-reduce of dW/db, overlapped with dX',
+                   'l2': 'per-step working set (operands, activations, gradients) exceeds the 126 MB L2; no flush',
+                   'tflops_per_gpu': value / world_size,
+                   'frac_of_nominal_2250_per_gpu': value / world_size / 2250.0},
+        'clocks': clocks.summary(),
+        'e2e': {'value': e2e_value, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms,
+                'h2d_bytes_per_step': host_x[0].numel() * host_x[0].element_size(),
+                'd2h_bytes_per_step': bias_grad_host.numel() * bias_grad_host.element_size()},
+        'gpu_launches': int(launches),
+        'roofline': roofline,
+    }
+    if world_size == 1 and not args.no_cpu_baseline:
+        from oracle.cpu_baseline import time_torch_cpu_linear
+        sample_rows, seconds, threads = 512, 0.0, 1
+        for (k, n, act, bias) in spec['layers']:
+            r = time_torch_cpu_linear(sample_rows, k, n, act, bias, None, steps=10, warmup=2)
+            seconds += r['seconds_per_step']
+            threads = r['threads']
+        line['cpu_baseline'] = {
+            'value': flops_per_step(spec, sample_rows) / seconds / 1e12, 'unit': 'TFLOP/s', 'cores': threads,
+            'kind': 'port',
+            'sample': f'{sample_rows} of the batch rows per step, 10 steps, torch.nn.Linear + activation '
+                      f'fwd+bwd in fp32 on {threads} host threads'}
+    print(json.dumps(line), flush=True)
+    if world_size > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

@@ -99,7 +99,7 @@ const char* ab200_error_string(int code);
 /* Kernel chosen by the last GEMM entry point called on this host thread (AB200_PATH_*). */
 int ab200_last_path(void);
 
-/* Number of kernels this library has launched on this host thread since it was loaded. */
+/* Number of kernels this library has launched (all host threads) since it was loaded. */
 int64_t ab200_launch_count(void);
 
 /*

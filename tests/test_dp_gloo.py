@@ -1,0 +1,96 @@
+"""
+Data-parallel logic on CPU ranks (gloo, world size 2): row sharding, zero-copy gradient buckets and
+the SUM all-reduce reproduce the single-process full-batch gradient.  The per-rank gradients come
+from the CPU oracle, since the CUDA kernels need a GPU.
+"""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import attorch_b200
+from attorch_b200.dp import GradientBuckets, shard_rows
+from oracle import linear_oracle as oracle
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0))
+        return s.getsockname()[1]
+
+
+def _inputs():
+    gen = torch.Generator().manual_seed(0)
+    x = torch.randn(64, 24, generator=gen)
+    w1 = torch.randn(24, 32, generator=gen) / 5
+    b1 = torch.randn(32, generator=gen)
+    w2 = torch.randn(32, 16, generator=gen) / 6
+    b2 = torch.randn(16, generator=gen)
+    dy = torch.randn(64, 16, generator=gen)
+    return x, w1, b1, w2, b2, dy
+
+
+def _two_layer_grads(x, w1, b1, w2, b2, dy):
+    h, z1 = oracle.linear_forward(x, w1, b1, 'gelu')
+    y, _ = oracle.linear_forward(h, w2, b2, None)
+    dh, dw2, db2 = oracle.linear_backward(dy, h, None, w2, None, torch.float32, b2)
+    _, dw1, db1 = oracle.linear_backward(dh, x, z1, w1, 'gelu', torch.float32, b1)
+    return dw1, db1, dw2, db2
+
+
+def _worker(rank: int, world_size: int, port: int, overlap_requested: bool) -> None:
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world_size)
+    try:
+        x, w1, b1, w2, b2, dy = _inputs()
+        layers = [attorch_b200.Linear(24, 32, act_func='gelu', device='cpu'),
+                  attorch_b200.Linear(32, 16, device='cpu')]
+        buckets = GradientBuckets(layers, overlap=overlap_requested)
+        assert buckets.world_size == world_size
+        assert not buckets.overlap            # side streams exist only on CUDA
+        assert buckets.flat.numel() == 24 * 32 + 32 + 32 * 16 + 16
+        # The gradient destinations alias the flat bucket.
+        assert layers[0].weight_grad_out.data_ptr() == buckets.flat.data_ptr()
+        xs, dys = shard_rows(x, rank, world_size), shard_rows(dy, rank, world_size)
+        dw1, db1, dw2, db2 = _two_layer_grads(xs, w1, b1, w2, b2, dys)
+        layers[0].weight_grad_out.copy_(dw1)
+        layers[0].bias_grad_out.copy_(db1)
+        layers[1].weight_grad_out.copy_(dw2)
+        layers[1].bias_grad_out.copy_(db2)
+        for layer in layers:
+            layer.grad_ready()
+        buckets.finish()
+        f_dw1, f_db1, f_dw2, f_db2 = _two_layer_grads(x, w1, b1, w2, b2, dy)
+        torch.testing.assert_close(layers[0].weight_grad_out, f_dw1, rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(layers[0].bias_grad_out, f_db1, rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(layers[1].weight_grad_out, f_dw2, rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(layers[1].bias_grad_out, f_db2, rtol=1e-5, atol=1e-5)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('overlap', [False, True])
+def test_data_parallel_gradients_match_full_batch(overlap):
+    mp.spawn(_worker, args=(2, _free_port(), overlap), nprocs=2, join=True)
+
+
+def test_shard_rows():
+    t = torch.arange(24).view(8, 3)
+    assert torch.equal(shard_rows(t, 1, 4), t[2:4])
+    with pytest.raises(ValueError):
+        shard_rows(t, 0, 3)
+
+
+def test_single_process_bucket_is_a_no_op():
+    layer = attorch_b200.Linear(4, 6, device='cpu')
+    buckets = GradientBuckets([layer])
+    layer.weight_grad_out.fill_(2.0)
+    buckets.finish()
+    assert torch.all(layer.weight_grad_out == 2.0)
+    buckets.zero_grad()
+    assert layer.weight.grad is None
