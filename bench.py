@@ -147,14 +147,67 @@ def run_reference(args, spec, world_size, rank):
     print(json.dumps(line), flush=True)
 
 
+def forward_kernel_launcher(spec, tokens, device, lib):
+    """
+    Returns (launch, flops): `launch()` enqueues the forward tcgen05 GEMM of the workload's first
+    layer through the C ABI exactly as the layer launches it (X[M, K] * W[K, N] with bias,
+    activation and the pre-activation store), on the current stream.
+    """
+    from attorch_b200 import _lib
+    from attorch_b200.acts import act_id, parse_act_func
+    k0, n0, act0, _ = spec['layers'][0]
+    op_dtype = spec['autocast'] or spec['param_dtype']
+    xo = torch.randn(tokens, k0, device=device).to(op_dtype)
+    wo = (torch.randn(k0, n0, device=device) / k0 ** 0.5).to(op_dtype)
+    bo = torch.randn(n0, device=device).to(op_dtype)
+    yo = torch.empty(tokens, n0, device=device, dtype=op_dtype)
+    zo = torch.empty(tokens, n0, device=device, dtype=op_dtype)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    dt_id = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[op_dtype]
+    name, param = parse_act_func(act0)
+    stream = torch.cuda.current_stream().cuda_stream
+    keep = (xo, wo, bo, yo, zo, status)
+
+    def launch():
+        rc = lib.ab200_linear_forward(xo.data_ptr(), wo.data_ptr(), bo.data_ptr(), zo.data_ptr(), yo.data_ptr(),
+                                      tokens, k0, n0, k0, 1, n0, 1, n0, n0, dt_id, dt_id, dt_id,
+                                      act_id(name), param or 0.0, None, 0, status.data_ptr(), stream,
+                                      _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK)
+        _lib.check(rc, 'ab200_linear_forward')
+        return keep
+
+    return launch, 2.0 * tokens * k0 * n0
+
+
+def kernel_only(args, spec, tokens, device, lib):
+    """A few launches of the dominant kernel and nothing else: the target of ncu captures."""
+    launch, flops = forward_kernel_launcher(spec, tokens, device, lib)
+    for _ in range(max(args.warmup, 1)):
+        launch()
+    torch.cuda.synchronize()
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for _ in range(args.steps):
+        launch()
+    r1.record()
+    torch.cuda.synchronize()
+    ms = r0.elapsed_time(r1) / args.steps
+    print(json.dumps({'kernel_only': True, 'tokens': tokens, 'kernel_ms': ms,
+                      'tflops': flops / (ms * 1e-3) / 1e12}), flush=True)
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     parser.add_argument('--gpus', type=int, default=1)
-    parser.add_argument('--steps', type=int, default=50)
+    parser.add_argument('--steps', type=int, default=200)
     parser.add_argument('--warmup', type=int, default=10)
     parser.add_argument('--workload', choices=sorted(WORKLOADS), default='c2')
     parser.add_argument('--impl', choices=['b200', 'reference'], default='b200')
     parser.add_argument('--no-cpu-baseline', action='store_true')
+    parser.add_argument('--kernel-only', action='store_true',
+                        help='launch only the dominant kernel (for ncu captures of a small case)')
+    parser.add_argument('--tokens', type=int, default=None,
+                        help='override the tokens per GPU (profiling of reduced cases)')
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
     spec = WORKLOADS[args.workload]
@@ -181,7 +234,7 @@ def main():
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         dist.init_process_group('nccl', device_id=device)
 
-    tokens = spec['tokens_per_gpu'] or spec['global_tokens'] // world_size
+    tokens = args.tokens or spec['tokens_per_gpu'] or spec['global_tokens'] // world_size
     total_tokens = tokens * world_size
     torch.manual_seed(0)
     layers = [attorch_b200.Linear(k, n, bias=bias, act_func=act, device=device,
@@ -217,6 +270,10 @@ def main():
         t = torch.tensor([ms], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    if args.kernel_only:
+        kernel_only(args, spec, tokens, device, lib)
+        return
 
     # ---------------------------------------------------------------- device-resident timing
     for _ in range(args.warmup):
@@ -283,24 +340,8 @@ def main():
     # first layer: X[M, K] * W[K, N] with bias, gelu and the pre-activation store), event-timed on
     # the launching stream.
     peaks, peak_source = measured_peaks()
-    k0, n0, act0, _ = spec['layers'][0]
-    op_dtype = out_dtype
-    xo = torch.randn(tokens, k0, device=device).to(op_dtype)
-    wo = (torch.randn(k0, n0, device=device) / k0 ** 0.5).to(op_dtype)
-    bo = torch.randn(n0, device=device).to(op_dtype)
-    yo, zo = torch.empty(tokens, n0, device=device, dtype=op_dtype), torch.empty(tokens, n0, device=device, dtype=op_dtype)
-    status = torch.zeros(1, dtype=torch.int32, device=device)
-    dt_id = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[op_dtype]
-    from attorch_b200.acts import act_id, parse_act_func
-    name, param = parse_act_func(act0)
-    stream = torch.cuda.current_stream().cuda_stream
-
-    def launch_fwd():
-        rc = lib.ab200_linear_forward(xo.data_ptr(), wo.data_ptr(), bo.data_ptr(), zo.data_ptr(), yo.data_ptr(),
-                                      tokens, k0, n0, k0, 1, n0, 1, n0, n0, dt_id, dt_id, dt_id,
-                                      act_id(name), param or 0.0, None, 0, status.data_ptr(), stream,
-                                      _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK)
-        _lib.check(rc, 'ab200_linear_forward')
+    k0, n0 = spec['layers'][0][0], spec['layers'][0][1]
+    launch_fwd, _ = forward_kernel_launcher(spec, tokens, device, lib)
 
     for _ in range(5):
         launch_fwd()
