@@ -32,7 +32,8 @@ SIGNATURES = {
     'ab200_error_string': (ctypes.c_char_p, [_int]),
     'ab200_last_path': (_int, []),
     'ab200_launch_count': (_i64, []),
-    'ab200_forward_workspace_bytes': (_i64, [_i64, _i64, _i64]),
+    'ab200_forward_workspace_bytes': (_i64, [_i64, _i64, _i64, _int]),
+    'ab200_gemm_workspace_bytes': (_i64, [_i64, _i64, _i64]),
     'ab200_linear_forward': (_int, [_ptr, _ptr, _ptr, _ptr, _ptr,
                                     _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
                                     _int, _int, _int, _int, _f32,
@@ -42,10 +43,10 @@ SIGNATURES = {
                                   _int, _int, _int, _f32, _ptr, _i64, _ptr]),
     'ab200_linear_backward_input': (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64,
                                            _i64, _i64, _i64, _i64, _i64,
-                                           _int, _int, _ptr, _ptr, _int]),
+                                           _int, _int, _ptr, _i64, _ptr, _ptr, _int]),
     'ab200_linear_backward_weight': (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64,
                                             _i64, _i64, _i64, _i64, _i64,
-                                            _int, _int, _ptr, _ptr, _int]),
+                                            _int, _int, _ptr, _i64, _ptr, _ptr, _int]),
     'ab200_cast_2d': (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _int, _int, _ptr]),
 }
 

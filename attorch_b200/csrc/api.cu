@@ -191,6 +191,52 @@ int launch_any(const AnyGemmArgs& a, cudaStream_t stream) {
 
 bool fits_int(int64_t v) { return v >= 0 && v < (1ll << 31); }
 
+int launch_finish(float* partial, const GemmArgs& e, long long M, long long N, cudaStream_t stream) {
+  const long long total = M * N;
+  long long blocks = (total + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 8;
+  if (blocks > cap) blocks = cap;
+  streamk_finish_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      partial, N, static_cast<int>(M), static_cast<int>(N), e.bias, e.bias_dtype, e.aux, e.ld_aux, e.out,
+      e.ld_out, e.out_dtype, e.act, e.act_param);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
+}
+
+// Should a GEMM with this output and reduction length be run as equal (tile, k-block) ranges over
+// all SMs instead of whole tiles?  Yes when whole tiles would leave at least half of the SMs idle
+// and the reduction is long enough to share: every CTA then still gets at least 4 k-blocks.
+bool want_split(long long rows, long long cols, long long reduction, int elt) {
+  const int bn = pick_bn(rows, cols);
+  const long long tiles = ((rows + 127) / 128) * ((cols + bn - 1) / bn);
+  const long long k_blocks = (reduction + 128 / elt - 1) / (128 / elt);
+  const int sms = sm_count();
+  return tiles * 2 <= sms && tiles * k_blocks >= 4ll * sms;
+}
+
+// Runs p as whole tiles with the fused epilogue, or, if the shape calls for it and the caller
+// supplied enough workspace, as stream-K partial sums plus the finishing kernel.  p.g holds the
+// epilogue in both cases.
+int run_tiles_or_split(TcProblem& p, void* workspace, int64_t workspace_bytes, cudaStream_t stream) {
+  GemmArgs& g = p.g;
+  const int bn = pick_bn(g.M, g.N);
+  const int64_t need = static_cast<int64_t>(g.M) * g.N * 4;
+  if (want_split(g.M, g.N, g.K, dtype_size(p.op_dtype)) && workspace != nullptr && workspace_bytes >= need) {
+    if (cudaMemsetAsync(workspace, 0, need, stream) != cudaSuccess) return ERR_LAUNCH;
+    g.stream_k = 1;
+    g.partial = static_cast<float*>(workspace);
+    g.ld_partial = g.N;
+    g.partial_transposed = 0;
+    g_last_path = AB200_PATH_STREAMK;
+    const int rc = launch_tc(p, bn, stream);
+    if (rc != OK) return rc;
+    return launch_finish(g.partial, g, g.M, g.N, stream);
+  }
+  g.stream_k = 0;
+  g_last_path = AB200_PATH_TCGEN05;
+  return launch_tc(p, bn, stream);
+}
+
 }  // namespace
 }  // namespace ab200
 
@@ -224,10 +270,16 @@ const char* ab200_error_string(int code) {
 int ab200_last_path(void) { return g_last_path; }
 int64_t ab200_launch_count(void) { return g_launches.load(); }
 
-int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N) {
-  (void)K;
+int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N, int flags) {
   if (M <= 0 || N <= 0) return 0;
-  return M <= 128 ? M * N * 4 : 0;
+  if ((M <= 128 && !(flags & AB200_FLAG_NO_STREAMK)) || (flags & AB200_FLAG_FORCE_STREAMK)) return M * N * 4;
+  return ab200_gemm_workspace_bytes(M, N, K);
+}
+
+int64_t ab200_gemm_workspace_bytes(int64_t rows, int64_t cols, int64_t reduction) {
+  if (rows <= 0 || cols <= 0 || reduction <= 0) return 0;
+  // The narrower element type gives the fewer k-blocks; a caller that sizes for it is safe for both.
+  return (want_split(rows, cols, reduction, 2) || want_split(rows, cols, reduction, 4)) ? rows * cols * 4 : 0;
 }
 
 int ab200_linear_forward(const void* x, const void* w, const void* bias, void* pre_act, void* out,
@@ -288,26 +340,20 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
     g_last_path = AB200_PATH_STREAMK;
     int rc = launch_tc(p, bn, stream);
     if (rc != OK) return rc;
-    const long long total = M * N;
-    int blocks = static_cast<int>((total + 255) / 256);
-    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
-    streamk_finish_kernel<<<blocks, 256, 0, stream>>>(static_cast<float*>(workspace), N, static_cast<int>(M),
-                                                      static_cast<int>(N), bias, bias_dtype, pre_act, ld_pre,
-                                                      out, ld_out, out_dtype, act, act_param);
-    ++g_launches;
-    return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
+    GemmArgs e{};
+    e.bias = bias; e.bias_dtype = bias_dtype; e.aux = pre_act; e.ld_aux = ld_pre;
+    e.out = out; e.ld_out = ld_out; e.out_dtype = out_dtype; e.act = act; e.act_param = act_param;
+    return launch_finish(static_cast<float*>(workspace), e, M, N, stream);
   }
 
   p.a = x; p.a_mn = false; p.a_pitch = x_stride_m;
   p.b = w; p.b_mn = true; p.b_pitch = w_stride_k;
   g.M = static_cast<int>(M); g.N = static_cast<int>(N); g.K = static_cast<int>(K);
-  g.stream_k = 0;
   g.out = out; g.ld_out = ld_out; g.out_dtype = out_dtype;
   g.aux = pre_act; g.ld_aux = ld_pre;
   g.bias = bias; g.bias_dtype = bias_dtype;
   g.act = act; g.act_param = act_param;
-  g_last_path = AB200_PATH_TCGEN05;
-  return launch_tc(p, pick_bn(M, N), stream);
+  return run_tiles_or_split(p, workspace, workspace_bytes, stream);
 }
 
 int64_t ab200_act_backward_workspace_bytes(int64_t M, int64_t N) {
@@ -371,7 +417,8 @@ int ab200_act_backward(const void* dy, const void* z, void* dz, void* db, int64_
 int ab200_linear_backward_input(const void* dz, const void* w, void* dx, int64_t M, int64_t K,
                                 int64_t N, int64_t dz_stride_m, int64_t dz_stride_n,
                                 int64_t w_stride_k, int64_t w_stride_n, int64_t ld_dx, int op_dtype,
-                                int dx_dtype, int* status, void* stream_, int flags) {
+                                int dx_dtype, void* workspace, int64_t workspace_bytes, int* status,
+                                void* stream_, int flags) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M < 0 || K < 0 || N < 0) return ERR_BAD_SHAPE;
   if (!fits_int(M) || !fits_int(K) || !fits_int(N)) return ERR_TOO_LARGE;
@@ -394,8 +441,7 @@ int ab200_linear_backward_input(const void* dz, const void* w, void* dx, int64_t
     g.M = static_cast<int>(M); g.N = static_cast<int>(K); g.K = static_cast<int>(N);
     g.out = dx; g.ld_out = ld_dx; g.out_dtype = dx_dtype;
     g.act = ACT_NONE;
-    g_last_path = AB200_PATH_TCGEN05;
-    return launch_tc(p, pick_bn(M, K), stream);
+    return run_tiles_or_split(p, workspace, workspace_bytes, stream);
   }
   AnyGemmArgs a{};
   a.a = dz; a.sam = dz_stride_m; a.sak = dz_stride_n; a.a_dtype = op_dtype;
@@ -410,7 +456,8 @@ int ab200_linear_backward_input(const void* dz, const void* w, void* dx, int64_t
 int ab200_linear_backward_weight(const void* x, const void* dz, void* dw, int64_t M, int64_t K,
                                  int64_t N, int64_t x_stride_m, int64_t x_stride_k,
                                  int64_t dz_stride_m, int64_t dz_stride_n, int64_t ld_dw,
-                                 int op_dtype, int dw_dtype, int* status, void* stream_, int flags) {
+                                 int op_dtype, int dw_dtype, void* workspace, int64_t workspace_bytes,
+                                 int* status, void* stream_, int flags) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M < 0 || K < 0 || N < 0) return ERR_BAD_SHAPE;
   if (!fits_int(M) || !fits_int(K) || !fits_int(N)) return ERR_TOO_LARGE;
@@ -433,8 +480,7 @@ int ab200_linear_backward_weight(const void* x, const void* dz, void* dw, int64_
     g.M = static_cast<int>(K); g.N = static_cast<int>(N); g.K = static_cast<int>(M);
     g.out = dw; g.ld_out = ld_dw; g.out_dtype = dw_dtype;
     g.act = ACT_NONE;
-    g_last_path = AB200_PATH_TCGEN05;
-    return launch_tc(p, pick_bn(K, N), stream);
+    return run_tiles_or_split(p, workspace, workspace_bytes, stream);
   }
   AnyGemmArgs a{};
   a.a = x; a.sam = x_stride_k; a.sak = x_stride_m; a.a_dtype = op_dtype;   // A[k_feat, m] = X[m, k_feat]

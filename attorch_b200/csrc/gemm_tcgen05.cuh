@@ -13,15 +13,17 @@
 // which replaces the reference's Triton tile loop (attorch/linear_kernels.py:143-165) and the two
 // cuBLAS matmuls of its backward (attorch/linear_layer.py:152-155).
 //
-// Structure of one CTA (192 threads, one CTA per SM, grid = min(work, #SM)):
+// Structure of one CTA (320 threads, one CTA per SM, grid = min(work, #SM)):
 //   warp 0      TMA producer: fills a ring of kStages shared-memory stages (A tile + B tile,
 //               128-byte swizzle) with cp.async.bulk.tensor, completion on "full" mbarriers.
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x BN x 32 bytes of K each) from the
 //               shared-memory descriptors into one of two accumulators in tensor memory;
 //               tcgen05.commit releases the stage ("empty") and publishes the accumulator.
-//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (each warp owns 32 TMEM lanes), add
-//               bias, store the pre-activation, apply the activation, store the output.  The second
-//               accumulator lets the epilogue of tile i overlap the main loop of tile i + 1.
+//   warps 2-9   epilogue: tcgen05.ld the finished accumulator (a warp may read the 32 TMEM lanes of
+//               its quarter, warp id mod 4; the two warps of a quarter take alternate 32-column
+//               chunks), add bias, store the pre-activation, apply the activation, store the output.
+//               The second accumulator lets the epilogue of tile i overlap the main loop of tile
+//               i + 1; two warps per scheduler keep its latency below the main loop's.
 //
 // Work is either whole output tiles (tile-parallel, direct epilogue) or equal contiguous ranges of
 // (tile, k-block) units (stream-K, fp32 atomic accumulation into a zeroed workspace that a small
@@ -82,7 +84,8 @@ struct GemmCfg {
   static constexpr bool MN_BASE32 = (ELT == 4);
   static constexpr uint32_t MN_LAYOUT = MN_BASE32 ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
   static constexpr uint32_t MN_SBO = MN_BASE32 ? 512 : 1024;
-  static constexpr int kThreads = 192;
+  static constexpr int kEpilogueWarps = 8;
+  static constexpr int kThreads = 32 * (2 + kEpilogueWarps);
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be 32, 64, 128 or 256");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM allocation must be a power of two");
   static_assert(!B_MN_ || BN_ % (128 / ELT_) == 0, "an MN-major B tile is made of 128-byte wide boxes");
@@ -172,6 +175,46 @@ __device__ __forceinline__ void store_row_chunk(void* base, int dt, long long of
   }
 }
 
+// v[i] += bias[col0 + i] for the valid columns of a 32-column chunk (same addresses in every lane:
+// the loads are warp-wide broadcasts, 16 bytes at a time when the chunk is whole and aligned).
+__device__ __forceinline__ void add_bias_chunk(float (&v)[32], const void* bias, int dt, int col0,
+                                               int valid) {
+  const int elt = dt == DT_F32 ? 4 : 2;
+  const char* p = static_cast<const char*>(bias) + static_cast<long long>(col0) * elt;
+  if (valid == 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+    if (dt == DT_F32) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 b = __ldg(reinterpret_cast<const float4*>(p) + i);
+        v[4 * i] += b.x; v[4 * i + 1] += b.y; v[4 * i + 2] += b.z; v[4 * i + 3] += b.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + i);
+        const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float lo, hi;
+          if (dt == DT_F16) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+            lo = f.x; hi = f.y;
+          } else {
+            lo = __uint_as_float(w[j] << 16);
+            hi = __uint_as_float(w[j] & 0xFFFF0000u);
+          }
+          v[8 * i + 2 * j] += lo;
+          v[8 * i + 2 * j + 1] += hi;
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < valid) v[i] += load_as_f32(bias, dt, col0 + i);
+  }
+}
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -204,7 +247,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(acc_full_bar(b), 1);
-      ptx::mbar_init(acc_empty_bar(b), 4);   // one arrival per epilogue warp
+      ptx::mbar_init(acc_empty_bar(b), Cfg::kEpilogueWarps);   // one arrival per epilogue warp
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -320,8 +363,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int q = warp & 3;                    // TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;          // which of the quarter's two warps: chunks half, half + 2, ...
     SegmentIter it(args);
     Segment seg;
     uint32_t n_acc = 0;
@@ -334,7 +378,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row = seg.m_blk * BM + q * 32 + lane;
       const bool row_ok = row < args.M;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half; c < BN / 32; c += 2) {
         const int col0 = seg.n_blk * BN + c * 32;
         if (col0 >= args.N) break;             // warp-uniform
         uint32_t r[32];
@@ -352,17 +396,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (i < valid) atomicAdd(args.partial + static_cast<long long>(col0 + i) * args.ld_partial + row, v[i]);
             } else {
               float* p = args.partial + static_cast<long long>(row) * args.ld_partial + col0;
+              if (valid == 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (i < valid) atomicAdd(p + i, v[i]);
+                for (int i = 0; i < 8; ++i)
+                  ptx::red_add_v4_f32(p + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (i < valid) atomicAdd(p + i, v[i]);
+              }
             }
           }
         } else {
-          if (args.bias != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < valid) v[i] += load_as_f32(args.bias, args.bias_dtype, col0 + i);
-          }
+          if (args.bias != nullptr) add_bias_chunk(v, args.bias, args.bias_dtype, col0, valid);
           if (args.aux != nullptr && row_ok)
             store_row_chunk(args.aux, args.out_dtype, static_cast<long long>(row) * args.ld_aux + col0, v, valid);
           act_fwd_inplace(v, args.act, args.act_param);

@@ -182,7 +182,7 @@ class LinearAutoGrad(torch.autograd.Function):
             output = torch.empty((batch_dim, out_feat_dim), device=input.device, dtype=output_dtype)
             pre_act = torch.empty_like(output) if save_pre_act else None
 
-            ws_bytes = lib.ab200_forward_workspace_bytes(batch_dim, in_feat_dim, out_feat_dim)
+            ws_bytes = lib.ab200_forward_workspace_bytes(batch_dim, in_feat_dim, out_feat_dim, _gemm_flags)
             workspace = _workspace(input.device, ws_bytes) if ws_bytes else None
             _lib.check(lib.ab200_linear_forward(
                 _ptr(x_op), _ptr(w_op), _ptr(bias_op), _ptr(pre_act), _ptr(output),
@@ -271,22 +271,28 @@ class LinearAutoGrad(torch.autograd.Function):
             if ctx.weight_requires_grad:
                 weight_grad = (weight_grad_out if weight_grad_out is not None else
                                torch.empty(ctx.weight_shape, dtype=ctx.weight_dtype, device=device))
+                ws_bytes = lib.ab200_gemm_workspace_bytes(in_feat_dim, out_feat_dim, batch_dim)
+                workspace = _workspace(device, ws_bytes) if ws_bytes else None
                 _lib.check(lib.ab200_linear_backward_weight(
                     _ptr(x_op), _ptr(pre_act_grad), _ptr(weight_grad),
                     batch_dim, in_feat_dim, out_feat_dim,
                     x_op.stride(0), x_op.stride(1), pre_act_grad.stride(0), pre_act_grad.stride(1),
                     weight_grad.stride(0), _dtype_id(op_dtype), _dtype_id(weight_grad.dtype),
-                    status, stream, _gemm_flags), 'ab200_linear_backward_weight')
+                    _ptr(workspace), ws_bytes, status, stream, _gemm_flags),
+                    'ab200_linear_backward_weight')
             if ctx.grad_ready is not None:
                 ctx.grad_ready()
             if ctx.input_requires_grad:
                 input_grad = torch.empty((batch_dim, in_feat_dim), dtype=ctx.input_dtype, device=device)
+                ws_bytes = lib.ab200_gemm_workspace_bytes(batch_dim, in_feat_dim, out_feat_dim)
+                workspace = _workspace(device, ws_bytes) if ws_bytes else None
                 _lib.check(lib.ab200_linear_backward_input(
                     _ptr(pre_act_grad), _ptr(w_op), _ptr(input_grad),
                     batch_dim, in_feat_dim, out_feat_dim,
                     pre_act_grad.stride(0), pre_act_grad.stride(1), w_op.stride(0), w_op.stride(1),
                     in_feat_dim, _dtype_id(op_dtype), _dtype_id(input_grad.dtype),
-                    status, stream, _gemm_flags), 'ab200_linear_backward_input')
+                    _ptr(workspace), ws_bytes, status, stream, _gemm_flags),
+                    'ab200_linear_backward_input')
                 input_grad = input_grad.view(ctx.input_shape)
 
         # One slot per forward argument (attorch/linear_layer.py:158-161 pads with None).

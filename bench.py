@@ -285,8 +285,10 @@ def main():
     with ClockSampler(local_rank) as clocks:
         barrier()
         start.record()
+        host_t0 = time.perf_counter()
         for _ in range(args.steps):
             step(x_dev)
+        host_ms_per_step = (time.perf_counter() - host_t0) * 1e3 / args.steps
         stop.record()
         barrier()
     launches = lib.ab200_launch_count() - launches_before
@@ -369,6 +371,7 @@ def main():
     line = {
         'metric': 'linear_fwd_bwd_tflops', 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world_size,
         'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step,
+        'host_enqueue_ms_per_step': host_ms_per_step,
         'higher_is_better': True, 'scaling': spec['scaling'], 'vs_baseline': None,
         'dtype': 'bf16', 'data': 'synthetic',
         'config': {'workload': args.workload,

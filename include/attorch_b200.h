@@ -117,7 +117,7 @@ int64_t ab200_launch_count(void);
  * (attorch/linear_kernels.py:183).
  * Operands with unit inner stride and 16-byte aligned base and row pitch run on the tcgen05
  * kernels; anything else runs on the generic kernel.  M <= 128 uses the swap-AB stream-K kernel,
- * which needs workspace_bytes >= ab200_forward_workspace_bytes(M, K, N); the workspace is
+ * which needs workspace_bytes >= ab200_forward_workspace_bytes(M, K, N, flags); the workspace is
  * cleared by the call itself.
  */
 int ab200_linear_forward(const void* x, const void* w, const void* bias, void* pre_act, void* out,
@@ -127,8 +127,17 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
                          void* workspace, int64_t workspace_bytes, int* status, void* stream,
                          int flags);
 
-/* Workspace the forward call may need for this shape (0 when it needs none). */
-int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N);
+/* Workspace the forward call may use for this shape and these flags (0 when it needs none). */
+int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N, int flags);
+
+/*
+ * Workspace a GEMM entry point may use for an output of rows x cols elements and the given reduction
+ * length (0 when it needs none).  Outputs too small to occupy half of the SMs with whole tiles,
+ * e.g. the weight gradient of a narrow layer over a long batch, are computed as equal shares of the
+ * reduction on all SMs, accumulated in fp32 in the workspace and rounded by a finishing kernel.
+ * Without the workspace the call still succeeds, on whole tiles.
+ */
+int64_t ab200_gemm_workspace_bytes(int64_t rows, int64_t cols, int64_t reduction);
 
 /*
  * Backward, step 1:  dZ = dY * act'(Z)  and  db[n] = sum_m dZ[m, n].
@@ -147,22 +156,26 @@ int64_t ab200_act_backward_workspace_bytes(int64_t M, int64_t N);
 
 /*
  * Backward, step 2:  dX[M, K] = dZ[M, N] * W^T.   Replaces `pre_act_grad @ weight.T`
- * (attorch/linear_layer.py:153).  dz and w are of op_dtype, dx of dx_dtype.
+ * (attorch/linear_layer.py:153).  dz and w are of op_dtype, dx of dx_dtype.  workspace: optional,
+ * ab200_gemm_workspace_bytes(M, K, N) bytes.
  */
 int ab200_linear_backward_input(const void* dz, const void* w, void* dx, int64_t M, int64_t K,
                                 int64_t N, int64_t dz_stride_m, int64_t dz_stride_n,
                                 int64_t w_stride_k, int64_t w_stride_n, int64_t ld_dx, int op_dtype,
-                                int dx_dtype, int* status, void* stream, int flags);
+                                int dx_dtype, void* workspace, int64_t workspace_bytes, int* status,
+                                void* stream, int flags);
 
 /*
  * Backward, step 3:  dW[K, N] = X^T * dZ.   Replaces `flattened_input.T @ pre_act_grad`
  * (attorch/linear_layer.py:154-155).  x and dz are of op_dtype, dw of dw_dtype (pass AB200_F32 to
  * keep the fp32 accumulator unrounded, e.g. for fp32 master weights or an fp32 all-reduce bucket).
+ * workspace: optional, ab200_gemm_workspace_bytes(K, N, M) bytes.
  */
 int ab200_linear_backward_weight(const void* x, const void* dz, void* dw, int64_t M, int64_t K,
                                  int64_t N, int64_t x_stride_m, int64_t x_stride_k,
                                  int64_t dz_stride_m, int64_t dz_stride_n, int64_t ld_dw,
-                                 int op_dtype, int dw_dtype, int* status, void* stream, int flags);
+                                 int op_dtype, int dw_dtype, void* workspace, int64_t workspace_bytes,
+                                 int* status, void* stream, int flags);
 
 /*
  * dst[r, c] (contiguous, dst_dtype) = src[r * src_stride_r + c * src_stride_c] (src_dtype).

@@ -183,23 +183,35 @@ def output_dtype_rule(input_dtype: torch.dtype, autocast_dtype: Optional[torch.d
     return autocast_dtype
 
 
-def tf32_round(x: Tensor) -> Tensor:
-    """fp32 -> nearest value with a 10-bit mantissa (what a TF32 tensor-core operand keeps)."""
+def tf32_round(x: Tensor, mode: str = 'nearest') -> Tensor:
+    """
+    fp32 -> TF32 (10-bit mantissa), the precision a tensor core keeps of an fp32 operand when a dot
+    product is allowed to use TF32 (attorch/linear_kernels.py:57,165).  ``mode='truncate'`` drops the
+    low 13 bits, which is what the B200 tensor cores do with fp32 operands (pinned by
+    tests/test_linear_gpu.py::test_tf32_operands_are_truncated); ``'nearest'`` rounds.
+    """
     bits = x.contiguous().view(torch.int32)
-    rounded = (bits + 0x1000) & ~0x1FFF
+    if mode == 'truncate':
+        rounded = bits & ~0x1FFF
+    elif mode == 'nearest':
+        rounded = (bits + 0x1000) & ~0x1FFF
+    else:
+        raise ValueError(mode)
     return rounded.view(torch.float32)
 
 
 def linear_forward(x: Tensor, weight: Tensor, bias: Optional[Tensor], act_func: Optional[str],
                    autocast_dtype: Optional[torch.dtype] = None, save_pre_act: bool = True,
-                   tf32: bool = False) -> Tuple[Tensor, Optional[Tensor]]:
+                   tf32: Optional[str] = None) -> Tuple[Tensor, Optional[Tensor]]:
     """
     Returns (output, pre_act) exactly as attorch/linear_kernels.py:143-188 produces them:
     operands (cast to fp16 / the 16-bit output dtype if the output is 16-bit) are multiplied with
     fp32 accumulation (here: float64 accumulation of the exact products, rounded once to fp32);
     the bias (cast likewise) is added to the fp32 accumulator; the pre-activation is that value
     rounded to the output dtype; the activation is evaluated on the *unrounded* fp32 value and then
-    rounded.  ``weight`` is ``[in_features, out_features]``.
+    rounded.  ``weight`` is ``[in_features, out_features]``.  ``tf32`` ('truncate' or 'nearest')
+    reduces fp32 operands to TF32 first, as a GPU's tensor cores do; None keeps exact fp32 products,
+    as the reference's CPU interpreter run does.
     """
     name, param = parse_act_func(act_func)
     out_dtype = output_dtype_rule(x.dtype, autocast_dtype)
@@ -209,8 +221,8 @@ def linear_forward(x: Tensor, weight: Tensor, bias: Optional[Tensor], act_func: 
     if out_dtype in (torch.float16, torch.bfloat16):
         x2, w = x2.to(out_dtype), w.to(out_dtype)
         b = None if b is None else b.to(out_dtype)
-    elif tf32:
-        x2, w = tf32_round(x2.float()), tf32_round(w.float())
+    elif tf32 is not None:
+        x2, w = tf32_round(x2.float(), tf32), tf32_round(w.float(), tf32)
     accum = (x2.double() @ w.double()).float()
     if b is not None:
         accum = accum + b.float()[None, :]
@@ -221,7 +233,8 @@ def linear_forward(x: Tensor, weight: Tensor, bias: Optional[Tensor], act_func: 
 
 def linear_backward(output_grad: Tensor, x: Tensor, pre_act: Optional[Tensor], weight: Tensor,
                     act_func: Optional[str], out_dtype: torch.dtype,
-                    bias: Optional[Tensor] = None
+                    bias: Optional[Tensor] = None, tf32: Optional[str] = None,
+                    derivative_in_fp32: bool = False, round_to_out_dtype: bool = True
                     ) -> Tuple[Tensor, Tensor, Optional[Tensor]]:
     """
     Returns (dX, dW, db) following attorch/linear_layer.py:125-161.
@@ -233,6 +246,13 @@ def linear_backward(output_grad: Tensor, x: Tensor, pre_act: Optional[Tensor], w
     fp32 accumulation, result rounded to ``out_dtype``.  db = dZ.sum(0) in dZ's dtype (156).  As
     the autograd engine does afterwards, each gradient is finally cast to the dtype of the tensor
     it belongs to.
+
+    Three switches describe where the CUDA path deliberately differs from the reference, so that
+    tests can compare like with like: ``tf32`` multiplies fp32 operands as TF32 (the reference's
+    backward uses true fp32 products, its forward TF32); ``derivative_in_fp32`` evaluates every
+    activation derivative in fp32 instead of Z's 16-bit dtype; ``round_to_out_dtype=False`` skips
+    the intermediate rounding of dX / dW to the output dtype when the destination is wider (the
+    CUDA kernels write the fp32 accumulator straight into fp32 gradients under autocast).
     """
     name, param = parse_act_func(act_func)
     dy = output_grad.flatten(0, -2)
@@ -240,12 +260,15 @@ def linear_backward(output_grad: Tensor, x: Tensor, pre_act: Optional[Tensor], w
     if name is None:
         dz = dy
     else:
-        z = pre_act.float() if name in FP32_ACTS else pre_act
+        z = pre_act.float() if (name in FP32_ACTS or derivative_in_fp32) else pre_act
         dz = (dy * act_grad(name, z, param)).to(pre_act.dtype)
 
     def mm(a: Tensor, b: Tensor) -> Tensor:
         a, b = a.to(out_dtype), b.to(out_dtype)
-        return (a.double() @ b.double()).float().to(out_dtype)
+        if tf32 is not None and out_dtype is torch.float32:
+            a, b = tf32_round(a, tf32), tf32_round(b, tf32)
+        product = (a.double() @ b.double()).float()
+        return product.to(out_dtype) if round_to_out_dtype else product
 
     dx = mm(dz, weight.T).view_as(x).to(x.dtype)
     dw = mm(x2.T, dz).to(weight.dtype)
@@ -256,9 +279,11 @@ def linear_backward(output_grad: Tensor, x: Tensor, pre_act: Optional[Tensor], w
 
 
 def linear_forward_backward(x: Tensor, weight: Tensor, bias: Optional[Tensor], act_func: Optional[str],
-                            output_grad: Tensor, autocast_dtype: Optional[torch.dtype] = None):
+                            output_grad: Tensor, autocast_dtype: Optional[torch.dtype] = None,
+                            tf32: Optional[str] = None):
     """Convenience: (output, pre_act, dX, dW, db) of one training step of the layer."""
     out_dtype = output_dtype_rule(x.dtype, autocast_dtype)
-    out, pre_act = linear_forward(x, weight, bias, act_func, autocast_dtype)
-    dx, dw, db = linear_backward(output_grad.to(out_dtype), x, pre_act, weight, act_func, out_dtype, bias)
+    out, pre_act = linear_forward(x, weight, bias, act_func, autocast_dtype, tf32=tf32)
+    dx, dw, db = linear_backward(output_grad.to(out_dtype), x, pre_act, weight, act_func, out_dtype, bias,
+                                 tf32=tf32)
     return out, pre_act, dx, dw, db

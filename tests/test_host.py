@@ -78,13 +78,18 @@ def test_argument_validation_without_gpu(lib):
     assert lib.ab200_act_backward(fake, None, fake, None, 4, 8, 8, 8, 8, 2, 2, 5, 0.0, None, 0, None) == -1
     assert lib.ab200_act_backward(fake, fake, fake, fake, 4, 8, 8, 8, 8, 2, 2, 5, 0.0, None, 0, None) == -6
     assert lib.ab200_cast_2d(fake, fake, -1, 2, 2, 1, 0, 2, None) == -2
-    assert lib.ab200_linear_backward_input(fake, fake, None, 4, 8, 8, 8, 1, 8, 1, 8, 2, 2, None, None, 0) == -1
-    assert lib.ab200_linear_backward_weight(fake, fake, fake, 4, 8, 8, 8, 1, 8, 1, 4, 2, 2, None, None, 0) == -5
+    assert lib.ab200_linear_backward_input(fake, fake, None, 4, 8, 8, 8, 1, 8, 1, 8, 2, 2, None, 0, None, None, 0) == -1
+    assert lib.ab200_linear_backward_weight(fake, fake, fake, 4, 8, 8, 8, 1, 8, 1, 4, 2, 2, None, 0, None, None, 0) == -5
 
 
 def test_workspace_sizes(lib):
-    assert lib.ab200_forward_workspace_bytes(8, 8192, 28672) == 8 * 28672 * 4
-    assert lib.ab200_forward_workspace_bytes(8192, 4096, 4096) == 0
+    assert lib.ab200_forward_workspace_bytes(8, 8192, 28672, 0) == 8 * 28672 * 4
+    assert lib.ab200_forward_workspace_bytes(8192, 4096, 4096, 0) == 0
+    assert lib.ab200_forward_workspace_bytes(300, 264, 520, _lib.FLAG_FORCE_STREAMK) == 300 * 520 * 4
+    assert lib.ab200_forward_workspace_bytes(8, 64, 64, _lib.FLAG_NO_STREAMK) == 0
+    # A 16 x 96 weight gradient over 131072 rows is one tile: its reduction is shared out.
+    assert lib.ab200_gemm_workspace_bytes(16, 96, 131072) == 16 * 96 * 4
+    assert lib.ab200_gemm_workspace_bytes(4096, 4096, 8192) == 0
     assert lib.ab200_act_backward_workspace_bytes(8192, 4096) == 64 * 4096 * 4
     assert lib.ab200_act_backward_workspace_bytes(1, 16) == 64
 

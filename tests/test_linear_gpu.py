@@ -12,6 +12,17 @@ therefore feed the oracle's backward the pre-activation the GPU stored (obtained
 kernel with the activation switched off, which is bit-identical), while the forward output is
 checked against the oracle's own forward.  On the exact-fp32 generic kernel no such flip can
 happen and everything is compared with the reference's golden vectors directly.
+
+Where the CUDA path deliberately differs from the reference the oracle is asked for the same
+arithmetic, so that the comparison stays tight:
+  * fp32 operands are multiplied as TF32 in all three products on the tcgen05 kernels (the
+    reference: TF32 in forward, true fp32 in its cuBLAS backward).  The tensor cores truncate fp32
+    operands to TF32 (test_tf32_operands_are_truncated pins that), so the oracle truncates too.
+  * Activation derivatives are evaluated in fp32 for every activation; the reference evaluates
+    the piecewise ones in the 16-bit dtype of the stored pre-activation, whose per-operation
+    rounding is looser than this comparison's tolerance.
+  * Gradients of fp32 parameters / inputs under 16-bit autocast are written from the fp32
+    accumulator without an intermediate rounding to the autocast dtype.
 """
 
 import pytest
@@ -38,10 +49,14 @@ def make_layer(w, b, act_func, dtype):
     return layer
 
 
+LAST_PATH = {'path': None}
+
+
 def run_layer(x, w, b, act_func, dy, autocast_dtype=None, flags=0, param_dtype=None):
     """
     Forward + backward on the GPU.  Returns (y, dx, dw, db, z): the results on the CPU and the
-    pre-activation the kernel stored (None without an activation).
+    pre-activation the kernel stored (None without an activation).  LAST_PATH['path'] records
+    which kernel family the forward call used.
     """
     layer = make_layer(w, b, act_func, param_dtype or w.dtype)
     xg = x.to(DEV).requires_grad_(True)
@@ -50,6 +65,7 @@ def run_layer(x, w, b, act_func, dy, autocast_dtype=None, flags=0, param_dtype=N
         with torch.autocast('cuda', dtype=autocast_dtype or torch.float16,
                             enabled=autocast_dtype is not None):
             y = layer(xg)
+            LAST_PATH['path'] = _lib.load().ab200_last_path()
             z = None
             if act_func is not None:
                 with torch.no_grad():
@@ -65,12 +81,41 @@ def run_layer(x, w, b, act_func, dy, autocast_dtype=None, flags=0, param_dtype=N
 def expected_from_oracle(x, w, b, act_func, dy, z_gpu, autocast_dtype=None):
     """Oracle forward, and oracle backward through the pre-activation the GPU stored."""
     out_dtype = oracle.output_dtype_rule(x.dtype, autocast_dtype)
-    y, z = oracle.linear_forward(x, w, b, act_func, autocast_dtype)
+    tensor_cores = LAST_PATH['path'] != _lib.PATH_GENERIC
+    tf32 = 'truncate' if (out_dtype is torch.float32 and tensor_cores) else None
+    y, z = oracle.linear_forward(x, w, b, act_func, autocast_dtype, tf32=tf32)
     if z_gpu is not None:
         assert_close(z_gpu.view_as(z), z, TOL, 'pre-activation')
         z = z_gpu.view_as(z)
-    dx, dw, db = oracle.linear_backward(dy.to(out_dtype), x, z, w, act_func, out_dtype, b)
+    dx, dw, db = oracle.linear_backward(dy.to(out_dtype), x, z, w, act_func, out_dtype, b, tf32=tf32,
+                                        derivative_in_fp32=True, round_to_out_dtype=False)
+    if b is not None:
+        # db: fp32 sum of the stored dZ, rounded once to the bias dtype.
+        name, param = oracle.parse_act_func(act_func)
+        dz = dy.to(out_dtype).flatten(0, -2)
+        if name is not None:
+            dz = (dz * oracle.act_grad(name, z.float(), param)).to(out_dtype)
+        db = dz.float().sum(0).to(b.dtype)
     return y, dx, dw, db
+
+
+def test_tf32_operands_are_truncated():
+    """fp32 operands reach the tensor cores as TF32 by dropping the low 13 mantissa bits."""
+    values = [1 + 3 * 2 ** -12, 1 + 2 ** -11, 1 + 2 ** -12, 1 + 2 ** -10 + 2 ** -11, -(1 + 3 * 2 ** -12)]
+    x = torch.zeros(256, 32)
+    x[:len(values), 0] = torch.tensor(values)
+    w = torch.zeros(32, 64)
+    w[0, 0] = 1.0
+    layer = make_layer(w, None, None, torch.float32)
+    previous = attorch_b200.set_gemm_flags(_lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK)
+    try:
+        with torch.no_grad():
+            y = layer(x.to(DEV)).cpu()
+    finally:
+        attorch_b200.set_gemm_flags(previous)
+    attorch_b200.check_status()
+    expect = oracle.tf32_round(torch.tensor(values), 'truncate')
+    assert torch.equal(y[:len(values), 0], expect)
 
 
 def check_against(expected, got, tol, has_bias=True):

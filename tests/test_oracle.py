@@ -104,8 +104,11 @@ def test_dtype_rule():
 
 
 def test_tf32_round():
-    x = torch.tensor([1.0, 1.0 + 2 ** -11, 1.0 + 2 ** -10, 3.14159265])
+    x = torch.tensor([1.0, 1.0 + 2 ** -11, 1.0 + 2 ** -10, 3.14159265, 1 + 3 * 2 ** -12])
     r = oracle.tf32_round(x)
-    assert r[0] == 1.0 and r[2] == 1.0 + 2 ** -10
+    assert r[0] == 1.0 and r[2] == 1.0 + 2 ** -10 and r[4] == 1.0 + 2 ** -10
     assert abs(float(r[3]) - 3.14159265) < 3.2 * 2 ** -11
     assert (r.view(torch.int32) & 0x1FFF).eq(0).all()
+    t = oracle.tf32_round(x, 'truncate')
+    assert t[0] == 1.0 and t[1] == 1.0 and t[2] == 1.0 + 2 ** -10 and t[4] == 1.0
+    assert (t.abs() <= x.abs()).all()
