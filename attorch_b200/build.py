@@ -7,6 +7,7 @@ Python dependency, so the same file serves ctypes (this package) and any other C
 """
 
 import argparse
+import concurrent.futures
 import hashlib
 import os
 import shutil
@@ -20,14 +21,14 @@ INCLUDE = PKG_DIR.parent / 'include'
 LIB_PATH = PKG_DIR / 'libattorch_b200.so'
 STAMP_PATH = PKG_DIR / '.libattorch_b200.stamp'
 
-SOURCES = ['api.cu']
+OBJ_DIR = PKG_DIR / '_obj'
 NVCC_FLAGS = [
     '-std=c++20', '-O3', '-lineinfo',
     '-gencode', 'arch=compute_100a,code=sm_100a',
-    '-shared', '-Xcompiler', '-fPIC',
+    '-Xcompiler', '-fPIC',
     '--expt-relaxed-constexpr',
-    '-cudart', 'shared',
 ]
+LINK_FLAGS = ['-shared', '-cudart', 'shared', '-gencode', 'arch=compute_100a,code=sm_100a']
 
 
 def find_nvcc() -> str:
@@ -61,21 +62,37 @@ def is_current() -> bool:
             and STAMP_PATH.read_text().strip() == source_digest())
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compiles the shared library if it is missing or older than its sources."""
-    if not force and is_current():
-        return LIB_PATH
-    cmd = [find_nvcc(), *NVCC_FLAGS, f'-I{INCLUDE}', f'-I{CSRC}']
+def _compile(nvcc: str, src: Path, verbose: bool) -> Path:
+    obj = OBJ_DIR / (src.stem + '.o')
+    cmd = [nvcc, *NVCC_FLAGS, f'-I{INCLUDE}', f'-I{CSRC}']
     if verbose:
         cmd += ['-Xptxas', '-v']
-    cmd += [str(CSRC / src) for src in SOURCES]
-    cmd += ['-o', str(LIB_PATH)]
+    cmd += ['-c', str(src), '-o', str(obj)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or proc.returncode != 0:
         sys.stderr.write(proc.stdout)
         sys.stderr.write(proc.stderr)
     if proc.returncode != 0:
-        raise RuntimeError(f'nvcc failed with exit code {proc.returncode}')
+        raise RuntimeError(f'nvcc failed on {src.name} with exit code {proc.returncode}')
+    return obj
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compiles the shared library if it is missing or older than its sources."""
+    if not force and is_current():
+        return LIB_PATH
+    nvcc = find_nvcc()
+    OBJ_DIR.mkdir(exist_ok=True)
+    sources = sorted(CSRC.glob('*.cu'))
+    workers = min(len(sources), os.cpu_count() or 1)
+    with concurrent.futures.ThreadPoolExecutor(max_workers=workers) as pool:
+        objects = list(pool.map(lambda src: _compile(nvcc, src, verbose), sources))
+    cmd = [nvcc, *LINK_FLAGS, *[str(o) for o in objects], '-o', str(LIB_PATH)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout)
+        sys.stderr.write(proc.stderr)
+        raise RuntimeError(f'link failed with exit code {proc.returncode}')
     STAMP_PATH.write_text(source_digest() + '\n')
     return LIB_PATH
 

@@ -111,8 +111,17 @@ __device__ __forceinline__ float grad(float x, float p) {
     return 1.0f - t * t;
   }
   if constexpr (A == ACT_RELU) return x <= 0.0f ? 0.0f : 1.0f;
-  if constexpr (A == ACT_GELU)
-    return 0.5f * (1.0f + erf_fast(kRsqrt2 * x)) + x * kRsqrt2Pi * __expf(-0.5f * x * x);
+  if constexpr (A == ACT_GELU) {
+    // Phi(x) + x * phi(x).  erf(x / sqrt 2) and phi(x) need the same exponential, exp(-x^2 / 2).
+    const float e = __expf(-0.5f * x * x);
+    const float t = __fdividef(1.0f, fmaf(0.3275911f * kRsqrt2, fabsf(x), 1.0f));
+    float poly = fmaf(1.061405429f, t, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    const float half_erf = 0.5f - 0.5f * poly * t * e;        // erf(|x| / sqrt 2) / 2
+    return fmaf(x * kRsqrt2Pi, e, 0.5f + copysignf(half_erf, x));
+  }
   if constexpr (A == ACT_GELUAPPROX) {
     const float t = tanh_(kSqrt2OverPi * x * (1.0f + 0.044715f * x * x));
     return 0.5f * ((1.0f + t) +

@@ -5,11 +5,12 @@
 
 #include <atomic>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/attorch_b200.h"
 #include "common.cuh"
-#include "gemm_tcgen05.cuh"
+#include "gemm_launch.cuh"
 #include "kernels_misc.cuh"
 
 namespace ab200 {
@@ -17,62 +18,6 @@ namespace {
 
 thread_local int g_last_path = 0;
 std::atomic<int64_t> g_launches{0};   // all host threads: backward runs on autograd's threads
-
-// ------------------------------------------------------------------------------------------------
-// Driver entry point for tensor-map encoding, resolved through the runtime so that the library
-// does not link against libcuda.
-// ------------------------------------------------------------------------------------------------
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                   CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = []() -> EncodeTiledFn {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
-// 2-D map over a row-major matrix: `inner` contiguous elements per row, `outer` rows, row pitch in
-// bytes; box = box_inner x box_outer elements; 128-byte swizzle (of 32-byte units if `atom32`, the
-// layout MN-major tf32 operands need); out-of-range elements read as zero.
-int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
-              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32 = false) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (fn == nullptr) return ERR_DRIVER;
-  const CUtensorMapDataType dt = dtype == DT_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                 : dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                                   : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {pitch_bytes};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? OK : ERR_TENSOR_MAP;
-}
-
-int sm_count() {
-  static thread_local int cached_dev = -1;
-  static thread_local int cached = 0;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-  if (dev != cached_dev) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached = n;
-    cached_dev = dev;
-  }
-  return cached;
-}
 
 bool valid_dtype(int dt) { return dt == DT_F32 || dt == DT_F16 || dt == DT_BF16; }
 bool valid_act(int act) { return act >= 0 && act < ACT_COUNT; }
@@ -83,90 +28,6 @@ bool tma_ok(const void* p, long long pitch_elems, long long unit_stride, int elt
   if (reinterpret_cast<uintptr_t>(p) & 15) return false;
   if (pitch_elems <= 0 || (pitch_elems * elt) % 16 != 0) return false;
   return true;
-}
-
-// ------------------------------------------------------------------------------------------------
-// tcgen05 launch
-// ------------------------------------------------------------------------------------------------
-struct TcProblem {
-  const void* a; bool a_mn; long long a_pitch;   // pitch (elements) of the strided dimension
-  const void* b; bool b_mn; long long b_pitch;
-  int op_dtype;
-  GemmArgs g;     // M, N, K and epilogue filled by the caller
-};
-
-template <class Cfg>
-int launch_cfg(const TcProblem& p, cudaStream_t stream) {
-  CUtensorMap ta, tb;
-  const uint64_t elt = Cfg::ELT;
-  int rc;
-  // K-major: inner = K, outer = M (or N); box = one 128-byte row of K x tile rows.
-  // MN-major: inner = M (or N), outer = K; box = 128 bytes of M/N x BKE rows of K.
-  if (Cfg::A_MN)
-    rc = encode_2d(&ta, p.op_dtype, p.a, p.g.M, p.g.K, p.a_pitch * elt, Cfg::MN_ATOM, Cfg::BKE, Cfg::MN_BASE32);
-  else
-    rc = encode_2d(&ta, p.op_dtype, p.a, p.g.K, p.g.M, p.a_pitch * elt, Cfg::BKE, Cfg::BM);
-  if (rc != OK) return rc;
-  if (Cfg::B_MN)
-    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.N, p.g.K, p.b_pitch * elt, Cfg::MN_ATOM, Cfg::BKE, Cfg::MN_BASE32);
-  else
-    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.K, p.g.N, p.b_pitch * elt, Cfg::BKE, Cfg::BN);
-  if (rc != OK) return rc;
-
-  GemmArgs g = p.g;
-  g.tiles_m = (g.M + Cfg::BM - 1) / Cfg::BM;
-  g.tiles_n = (g.N + Cfg::BN - 1) / Cfg::BN;
-  g.k_blocks = (g.K + Cfg::BKE - 1) / Cfg::BKE;
-  g.group_m = 8;
-  const uint32_t fmt = p.op_dtype == DT_F32 ? 2u : (p.op_dtype == DT_BF16 ? 1u : 0u);
-  g.idesc = ptx::make_idesc(fmt, Cfg::A_MN ? 1u : 0u, Cfg::B_MN ? 1u : 0u, Cfg::BM, Cfg::BN);
-
-  static thread_local bool attr_set[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg::SMEM_BYTES) != cudaSuccess)
-      return ERR_LAUNCH;
-    attr_set[dev] = true;
-  }
-  const long long tiles = static_cast<long long>(g.tiles_m) * g.tiles_n;
-  const long long work = g.stream_k ? tiles * g.k_blocks : tiles;
-  const int sms = sm_count();
-  const int grid = static_cast<int>(work < sms ? work : sms);
-  if (grid <= 0) return OK;
-  gemm_tcgen05_kernel<Cfg><<<grid, Cfg::kThreads, Cfg::SMEM_BYTES, stream>>>(ta, tb, g);
-  ++g_launches;
-  return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
-}
-
-template <bool A_MN, bool B_MN>
-int launch_bn(const TcProblem& p, int bn, cudaStream_t stream) {
-  // A 32-wide tile is narrower than one 128-byte row of an MN-major 16-bit B operand, so it
-  // exists only for K-major B (the swap-AB kernel, whose B is the skinny activation matrix).
-  if (p.op_dtype == DT_F32) {
-    switch (bn) {
-      case 32: return launch_cfg<GemmCfg<32, 4, A_MN, B_MN>>(p, stream);
-      case 64: return launch_cfg<GemmCfg<64, 4, A_MN, B_MN>>(p, stream);
-      case 128: return launch_cfg<GemmCfg<128, 4, A_MN, B_MN>>(p, stream);
-      default: return launch_cfg<GemmCfg<256, 4, A_MN, B_MN>>(p, stream);
-    }
-  }
-  switch (bn) {
-    case 32:
-      if constexpr (!B_MN) return launch_cfg<GemmCfg<32, 2, A_MN, B_MN>>(p, stream);
-      [[fallthrough]];
-    case 64: return launch_cfg<GemmCfg<64, 2, A_MN, B_MN>>(p, stream);
-    case 128: return launch_cfg<GemmCfg<128, 2, A_MN, B_MN>>(p, stream);
-    default: return launch_cfg<GemmCfg<256, 2, A_MN, B_MN>>(p, stream);
-  }
-}
-
-int launch_tc(const TcProblem& p, int bn, cudaStream_t stream) {
-  if (!p.a_mn && p.b_mn) return launch_bn<false, true>(p, bn, stream);
-  if (!p.a_mn && !p.b_mn) return launch_bn<false, false>(p, bn, stream);
-  if (p.a_mn && p.b_mn) return launch_bn<true, true>(p, bn, stream);
-  return launch_bn<true, false>(p, bn, stream);
 }
 
 // Widest tile that still gives every SM work; otherwise the narrowest that covers N.
@@ -190,6 +51,21 @@ int launch_any(const AnyGemmArgs& a, cudaStream_t stream) {
 }
 
 bool fits_int(int64_t v) { return v >= 0 && v < (1ll << 31); }
+
+// CTA pairs (cta_group::2) are used unless the call's flags or AB200_CTA_PAIR=0 say otherwise.
+bool pair_allowed(int flags) {
+  static const bool env_on = []() {
+    const char* e = std::getenv("AB200_CTA_PAIR");
+    return e == nullptr || e[0] != '0';
+  }();
+  return env_on && !(flags & AB200_FLAG_NO_PAIR);
+}
+
+int launch_tc_counted(const TcProblem& p, int bn, cudaStream_t stream) {
+  const int rc = launch_tc(p, bn, stream);
+  if (rc == OK) ++g_launches;
+  return rc;
+}
 
 int launch_finish(float* partial, const GemmArgs& e, long long M, long long N, cudaStream_t stream) {
   const long long total = M * N;
@@ -217,8 +93,10 @@ bool want_split(long long rows, long long cols, long long reduction, int elt) {
 // Runs p as whole tiles with the fused epilogue, or, if the shape calls for it and the caller
 // supplied enough workspace, as stream-K partial sums plus the finishing kernel.  p.g holds the
 // epilogue in both cases.
-int run_tiles_or_split(TcProblem& p, void* workspace, int64_t workspace_bytes, cudaStream_t stream) {
+int run_tiles_or_split(TcProblem& p, void* workspace, int64_t workspace_bytes, cudaStream_t stream,
+                       int flags) {
   GemmArgs& g = p.g;
+  p.allow_pair = pair_allowed(flags);
   const int bn = pick_bn(g.M, g.N);
   const int64_t need = static_cast<int64_t>(g.M) * g.N * 4;
   if (want_split(g.M, g.N, g.K, dtype_size(p.op_dtype)) && workspace != nullptr && workspace_bytes >= need) {
@@ -228,13 +106,13 @@ int run_tiles_or_split(TcProblem& p, void* workspace, int64_t workspace_bytes, c
     g.ld_partial = g.N;
     g.partial_transposed = 0;
     g_last_path = AB200_PATH_STREAMK;
-    const int rc = launch_tc(p, bn, stream);
+    const int rc = launch_tc_counted(p, bn, stream);
     if (rc != OK) return rc;
     return launch_finish(g.partial, g, g.M, g.N, stream);
   }
   g.stream_k = 0;
   g_last_path = AB200_PATH_TCGEN05;
-  return launch_tc(p, bn, stream);
+  return launch_tc_counted(p, bn, stream);
 }
 
 }  // namespace
@@ -338,7 +216,7 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
     g.partial_transposed = 1;
     const int bn = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
     g_last_path = AB200_PATH_STREAMK;
-    int rc = launch_tc(p, bn, stream);
+    int rc = launch_tc_counted(p, bn, stream);
     if (rc != OK) return rc;
     GemmArgs e{};
     e.bias = bias; e.bias_dtype = bias_dtype; e.aux = pre_act; e.ld_aux = ld_pre;
@@ -353,7 +231,7 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
   g.aux = pre_act; g.ld_aux = ld_pre;
   g.bias = bias; g.bias_dtype = bias_dtype;
   g.act = act; g.act_param = act_param;
-  return run_tiles_or_split(p, workspace, workspace_bytes, stream);
+  return run_tiles_or_split(p, workspace, workspace_bytes, stream, flags);
 }
 
 int64_t ab200_act_backward_workspace_bytes(int64_t M, int64_t N) {
@@ -441,7 +319,7 @@ int ab200_linear_backward_input(const void* dz, const void* w, void* dx, int64_t
     g.M = static_cast<int>(M); g.N = static_cast<int>(K); g.K = static_cast<int>(N);
     g.out = dx; g.ld_out = ld_dx; g.out_dtype = dx_dtype;
     g.act = ACT_NONE;
-    return run_tiles_or_split(p, workspace, workspace_bytes, stream);
+    return run_tiles_or_split(p, workspace, workspace_bytes, stream, flags);
   }
   AnyGemmArgs a{};
   a.a = dz; a.sam = dz_stride_m; a.sak = dz_stride_n; a.a_dtype = op_dtype;
@@ -480,7 +358,7 @@ int ab200_linear_backward_weight(const void* x, const void* dz, void* dw, int64_
     g.M = static_cast<int>(K); g.N = static_cast<int>(N); g.K = static_cast<int>(M);
     g.out = dw; g.ld_out = ld_dw; g.out_dtype = dw_dtype;
     g.act = ACT_NONE;
-    return run_tiles_or_split(p, workspace, workspace_bytes, stream);
+    return run_tiles_or_split(p, workspace, workspace_bytes, stream, flags);
   }
   AnyGemmArgs a{};
   a.a = x; a.sam = x_stride_k; a.sak = x_stride_m; a.a_dtype = op_dtype;   // A[k_feat, m] = X[m, k_feat]

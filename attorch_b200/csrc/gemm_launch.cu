@@ -1,0 +1,72 @@
+// Non-template parts of the tcgen05 GEMM host side: the tensor-map encoder (resolved through the
+// runtime so that the library does not link against libcuda), the SM count and the family dispatch.
+#include "gemm_launch.cuh"
+
+namespace ab200 {
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+}  // namespace
+
+int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
+              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return ERR_DRIVER;
+  const CUtensorMapDataType dt = dtype == DT_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                   : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? OK : ERR_TENSOR_MAP;
+}
+
+int sm_count() {
+  static thread_local int cached_dev = -1;
+  static thread_local int cached = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev != cached_dev) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached = n;
+    cached_dev = dev;
+  }
+  return cached;
+}
+
+int launch_tc(const TcProblem& p, int bn, cudaStream_t stream) {
+  if (p.op_dtype == DT_F32) {
+    if (!p.a_mn && p.b_mn) return launch_tc_4_km(p, bn, stream);
+    if (!p.a_mn && !p.b_mn) return launch_tc_4_kk(p, bn, stream);
+    if (p.a_mn && p.b_mn) return launch_tc_4_mm(p, bn, stream);
+    return launch_tc_4_mk(p, bn, stream);
+  }
+  if (!p.a_mn && p.b_mn) return launch_tc_2_km(p, bn, stream);
+  if (!p.a_mn && !p.b_mn) return launch_tc_2_kk(p, bn, stream);
+  if (p.a_mn && p.b_mn) return launch_tc_2_mm(p, bn, stream);
+  return launch_tc_2_mk(p, bn, stream);
+}
+
+}  // namespace ab200

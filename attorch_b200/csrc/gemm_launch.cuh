@@ -1,0 +1,148 @@
+// Host side of the tcgen05 GEMM: TMA tensor-map construction and the launch of one kernel
+// configuration.  The configurations are instantiated in gemm_inst_*.cu, one translation unit per
+// (element size, operand majorness) so that they compile in parallel; api.cu picks one through
+// launch_tc().
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "common.cuh"
+#include "gemm_tcgen05.cuh"
+
+namespace ab200 {
+
+// One GEMM for the tensor-core kernel: operands with their majorness and the pitch (in elements)
+// of their strided dimension, the element type, and GemmArgs with M, N, K and the epilogue filled in.
+struct TcProblem {
+  const void* a; bool a_mn; long long a_pitch;
+  const void* b; bool b_mn; long long b_pitch;
+  int op_dtype;
+  bool allow_pair;   // may run as CTA pairs (cta_group::2) where a configuration for it exists
+  GemmArgs g;
+};
+
+// Number of SMs of the current device (148 if it cannot be queried).
+int sm_count();
+
+// Launches p with a BN-wide tile on the kernel family given by p.a_mn / p.b_mn / p.op_dtype.
+int launch_tc(const TcProblem& p, int bn, cudaStream_t stream);
+
+// Per-family launchers, defined in gemm_inst_*.cu.  Suffix: element bytes, then the majorness of
+// A and B (k = K-major, m = MN-major).
+int launch_tc_2_km(const TcProblem& p, int bn, cudaStream_t stream);
+int launch_tc_2_kk(const TcProblem& p, int bn, cudaStream_t stream);
+int launch_tc_2_mm(const TcProblem& p, int bn, cudaStream_t stream);
+int launch_tc_2_mk(const TcProblem& p, int bn, cudaStream_t stream);
+int launch_tc_4_km(const TcProblem& p, int bn, cudaStream_t stream);
+int launch_tc_4_kk(const TcProblem& p, int bn, cudaStream_t stream);
+int launch_tc_4_mm(const TcProblem& p, int bn, cudaStream_t stream);
+int launch_tc_4_mk(const TcProblem& p, int bn, cudaStream_t stream);
+
+// 2-D map over a row-major matrix: `inner` contiguous elements per row, `outer` rows, row pitch in
+// bytes; box = box_inner x box_outer elements; 128-byte swizzle (of 32-byte units if `atom32`, the
+// layout MN-major tf32 operands need); out-of-range elements read as zero.
+int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
+              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32 = false);
+
+template <class Cfg>
+int launch_cfg(const TcProblem& p, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  const uint64_t elt = Cfg::ELT;
+  int rc;
+  // K-major: inner = K, outer = M (or N); box = one 128-byte row of K x the rows one CTA loads.
+  // MN-major: inner = M (or N), outer = K; box = 128 bytes of M/N x BKE rows of K.
+  if (Cfg::A_MN)
+    rc = encode_2d(&ta, p.op_dtype, p.a, p.g.M, p.g.K, p.a_pitch * elt, Cfg::MN_ATOM, Cfg::BKE, Cfg::MN_BASE32);
+  else
+    rc = encode_2d(&ta, p.op_dtype, p.a, p.g.K, p.g.M, p.a_pitch * elt, Cfg::BKE, Cfg::BM);
+  if (rc != OK) return rc;
+  if (Cfg::B_MN)
+    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.N, p.g.K, p.b_pitch * elt, Cfg::MN_ATOM, Cfg::BKE, Cfg::MN_BASE32);
+  else
+    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.K, p.g.N, p.b_pitch * elt, Cfg::BKE, Cfg::BN_CTA);
+  if (rc != OK) return rc;
+
+  GemmArgs g = p.g;
+  g.tiles_m = (g.M + Cfg::TILE_M - 1) / Cfg::TILE_M;
+  g.tiles_n = (g.N + Cfg::BN - 1) / Cfg::BN;
+  g.k_blocks = (g.K + Cfg::BKE - 1) / Cfg::BKE;
+  g.group_m = 8 / Cfg::CTAS;
+  const uint32_t fmt = p.op_dtype == DT_F32 ? 2u : (p.op_dtype == DT_BF16 ? 1u : 0u);
+  g.idesc = ptx::make_idesc(fmt, Cfg::A_MN ? 1u : 0u, Cfg::B_MN ? 1u : 0u, Cfg::TILE_M, Cfg::BN);
+
+  // Per device: opt in to the large dynamic shared memory and, for CTA pairs, find out how many
+  // pairs the device can hold at once.
+  static thread_local bool attr_set[64] = {};
+  static thread_local int max_workers[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return ERR_LAUNCH;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::SMEM_BYTES) != cudaSuccess)
+      return ERR_LAUNCH;
+    max_workers[dev] = sm_count() / Cfg::CTAS;
+    if (Cfg::CTAS > 1) {
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = dim3(sm_count() / Cfg::CTAS * Cfg::CTAS);
+      probe.blockDim = dim3(Cfg::kThreads);
+      probe.dynamicSmemBytes = Cfg::SMEM_BYTES;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = Cfg::CTAS;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      probe.attrs = &attr;
+      probe.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_kernel<Cfg>, &probe) == cudaSuccess && clusters > 0)
+        max_workers[dev] = clusters < max_workers[dev] ? clusters : max_workers[dev];
+    }
+    attr_set[dev] = true;
+  }
+  const long long tiles = static_cast<long long>(g.tiles_m) * g.tiles_n;
+  const long long work = g.stream_k ? tiles * g.k_blocks : tiles;
+  const int workers = static_cast<int>(work < max_workers[dev] ? work : max_workers[dev]);
+  if (workers <= 0) return OK;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(workers * Cfg::CTAS);
+  cfg.blockDim = dim3(Cfg::kThreads);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  if (Cfg::CTAS > 1) {
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = Cfg::CTAS;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<Cfg>, ta, tb, g);
+  return err == cudaSuccess ? OK : ERR_LAUNCH;
+}
+
+// All tile widths of one (element size, majorness) family.  A 32-wide tile is narrower than one
+// 128-byte row of an MN-major 16-bit B operand, so it exists only where B is K-major or 4-byte.
+// CTA pairs exist for the 256-wide tile-parallel case.
+template <int ELT, bool A_MN, bool B_MN>
+int launch_family(const TcProblem& p, int bn, cudaStream_t stream) {
+  switch (bn) {
+    case 32:
+      if constexpr (!(B_MN && ELT == 2)) return launch_cfg<GemmCfg<32, ELT, A_MN, B_MN>>(p, stream);
+      [[fallthrough]];
+    case 64: return launch_cfg<GemmCfg<64, ELT, A_MN, B_MN>>(p, stream);
+    case 128: return launch_cfg<GemmCfg<128, ELT, A_MN, B_MN>>(p, stream);
+    default:
+      if constexpr (!(A_MN && !B_MN)) {
+        if (p.allow_pair && !p.g.stream_k && p.g.M > 128)
+          return launch_cfg<GemmCfg<256, ELT, A_MN, B_MN, 2>>(p, stream);
+      }
+      return launch_cfg<GemmCfg<256, ELT, A_MN, B_MN>>(p, stream);
+  }
+}
+
+}  // namespace ab200

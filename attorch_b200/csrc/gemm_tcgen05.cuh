@@ -28,6 +28,14 @@
 // Work is either whole output tiles (tile-parallel, direct epilogue) or equal contiguous ranges of
 // (tile, k-block) units (stream-K, fp32 atomic accumulation into a zeroed workspace that a small
 // finishing kernel turns into the output).
+//
+// With kCtas = 2 two CTAs on the two SMs of a TPC (a cluster of 2) share one 256 x BN tile: each
+// loads its own 128 rows of A and its own half of the columns of B, and the leader CTA (cluster
+// rank 0) issues tcgen05.mma.cta_group::2, which reads both CTAs' shared memory and writes 128
+// accumulator rows into each CTA's tensor memory.  Per SM that halves the B bytes pulled through L2
+// and read from shared memory.  Both CTAs' TMA loads complete on the leader's "full" barrier; the
+// leader's tcgen05.commit signals "empty" and "accumulator full" in both CTAs; both CTAs' epilogue
+// warps arrive on the leader's "accumulator empty" barrier.  No load is multicast.
 #pragma once
 #include "act_math.cuh"
 #include "common.cuh"
@@ -59,17 +67,20 @@ struct GemmArgs {
   int* status;            // device word; a bounded wait that runs out stores a DeviceStatus here
 };
 
-template <int BN_, int ELT_, bool A_MN_, bool B_MN_>
+template <int BN_, int ELT_, bool A_MN_, bool B_MN_, int CTAS_ = 1>
 struct GemmCfg {
-  static constexpr int BM = 128;
+  static constexpr int CTAS = CTAS_;             // CTAs sharing one tile (1, or 2 with cta_group::2)
+  static constexpr int BM = 128;                 // accumulator rows per CTA
+  static constexpr int TILE_M = BM * CTAS;       // output rows per tile
   static constexpr int BN = BN_;
+  static constexpr int BN_CTA = BN_ / CTAS_;     // columns of B each CTA loads
   static constexpr int ELT = ELT_;               // bytes per operand element (2: f16/bf16, 4: tf32)
   static constexpr bool A_MN = A_MN_;
   static constexpr bool B_MN = B_MN_;
   static constexpr int BKE = 128 / ELT;          // K elements per stage (one 128-byte swizzle row)
   static constexpr int UMMA_K = 32 / ELT;        // K elements per tcgen05.mma
   static constexpr int A_BYTES = BM * 128;
-  static constexpr int B_BYTES = BN * 128;
+  static constexpr int B_BYTES = BN_CTA * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int kMaxSmem = 227 * 1024;
   static constexpr int kBarrierBytes = 512;
@@ -88,7 +99,8 @@ struct GemmCfg {
   static constexpr int kThreads = 32 * (2 + kEpilogueWarps);
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be 32, 64, 128 or 256");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM allocation must be a power of two");
-  static_assert(!B_MN_ || BN_ % (128 / ELT_) == 0, "an MN-major B tile is made of 128-byte wide boxes");
+  static_assert(!B_MN_ || BN_CTA % (128 / ELT_) == 0, "an MN-major B tile is made of 128-byte wide boxes");
+  static_assert(CTAS_ == 1 || CTAS_ == 2, "one CTA or a pair");
 };
 
 struct Segment {
@@ -100,17 +112,20 @@ struct Segment {
 struct SegmentIter {
   long long unit, unit_end;   // stream-K: position in (tile, k-block) units
   int tile;                   // tile-parallel: next tile
-  __device__ __forceinline__ SegmentIter(const GemmArgs& a) {
+  int stride;                 // number of workers (CTAs, or CTA pairs)
+  // worker / workers: index and count of the CTAs (or CTA pairs) that share the work.
+  __device__ __forceinline__ SegmentIter(const GemmArgs& a, int worker, int workers) {
     const long long tiles = static_cast<long long>(a.tiles_m) * a.tiles_n;
+    stride = workers;
     if (a.stream_k) {
       const long long total = tiles * a.k_blocks;
-      unit = total * blockIdx.x / gridDim.x;
-      unit_end = total * (blockIdx.x + 1) / gridDim.x;
+      unit = total * worker / workers;
+      unit_end = total * (worker + 1) / workers;
       tile = 0;
     } else {
       unit = 0;
       unit_end = tiles;
-      tile = blockIdx.x;
+      tile = worker;
     }
   }
   __device__ __forceinline__ bool next(const GemmArgs& a, Segment& s) {
@@ -125,7 +140,7 @@ struct SegmentIter {
     } else {
       if (tile >= unit_end) return false;
       t = tile;
-      tile += gridDim.x;
+      tile += stride;
       s.kb0 = 0;
       s.kb1 = a.k_blocks;
     }
@@ -220,7 +235,9 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BKE = Cfg::BKE, STAGES = Cfg::STAGES;
+  constexpr int CTAS = Cfg::CTAS;
   constexpr bool kTf32 = (Cfg::ELT == 4);
+  constexpr bool kPair = (CTAS == 2);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -239,15 +256,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // Rank of this CTA in its pair (0 = leader, which issues the MMAs) and the pair's place among
+  // the workers that share the tiles.
+  const uint32_t cta = kPair ? ptx::cluster_ctarank() : 0u;
+  const int worker = static_cast<int>(blockIdx.x) / CTAS;
+  const int workers = static_cast<int>(gridDim.x) / CTAS;
 
   if (warp == 0 && lane == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      ptx::mbar_init(full_bar(s), 1);
-      ptx::mbar_init(empty_bar(s), 1);
+      ptx::mbar_init(full_bar(s), 1);        // the leader's arrive.expect_tx
+      ptx::mbar_init(empty_bar(s), 1);       // one tcgen05.commit
     }
     for (int b = 0; b < 2; ++b) {
-      ptx::mbar_init(acc_full_bar(b), 1);
-      ptx::mbar_init(acc_empty_bar(b), Cfg::kEpilogueWarps);   // one arrival per epilogue warp
+      ptx::mbar_init(acc_full_bar(b), 1);    // one tcgen05.commit
+      ptx::mbar_init(acc_empty_bar(b), Cfg::kEpilogueWarps * CTAS);   // one arrival per epilogue warp
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -255,11 +277,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::prefetch_tmap(&tmap_b);
   }
   if (warp == 1) {
-    ptx::tmem_alloc<1>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
-    ptx::tmem_relinquish<1>();
+    ptx::tmem_alloc<CTAS>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+    ptx::tmem_relinquish<CTAS>();
   }
   ptx::tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kPair) {
+    // The peer's barriers must be initialised before anything here signals them.
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  } else {
+    __syncthreads();
+  }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -267,7 +295,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   auto wait = [&](uint32_t bar, uint32_t parity, int code) -> bool {
     uint32_t spins = 0;
     uint64_t t0 = 0;
-    while (!ptx::mbar_try_wait(bar, parity)) {
+    while (!(kPair ? ptx::mbar_try_wait_cluster(bar, parity) : ptx::mbar_try_wait(bar, parity))) {
       if ((++spins & 0x3FFu) == 0) {
         if (*abort_flag) return false;
         const uint64_t now = ptx::globaltimer_ns();
@@ -286,44 +314,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      SegmentIter it(args);
+      SegmentIter it(args, worker, workers);
       Segment seg;
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
       while (ok && it.next(args, seg)) {
-        const int m0 = seg.m_blk * BM;
-        const int n0 = seg.n_blk * BN;
+        const int m0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM;      // this CTA's rows of A
+        const int n0 = seg.n_blk * BN + static_cast<int>(cta) * Cfg::BN_CTA;      // this CTA's columns of B
         for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
           if (!wait(empty_bar(s), ph ^ 1u, DEV_TIMEOUT_PRODUCER)) { ok = false; break; }
-          ptx::mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+          // The pair's loads all complete on the leader's barrier, which expects both CTAs' bytes.
+          uint32_t full = full_bar(s);
+          if constexpr (kPair) {
+            if (cta == 0) ptx::mbar_arrive_expect_tx(full, Cfg::STAGE_BYTES * CTAS);
+            full = ptx::map_to_cta(full, 0);
+          } else {
+            ptx::mbar_arrive_expect_tx(full, Cfg::STAGE_BYTES);
+          }
           const uint32_t a_dst = smem_base + s * Cfg::STAGE_BYTES;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
           const int k0 = kb * BKE;
           if constexpr (Cfg::A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / Cfg::MN_ATOM; ++j)
-              ptx::tma_load_2d(a_dst + j * Cfg::MN_BOX_BYTES, &tmap_a, full_bar(s),
-                               m0 + j * Cfg::MN_ATOM, k0);
+              ptx::tma_load_2d<kPair>(a_dst + j * Cfg::MN_BOX_BYTES, &tmap_a, full, m0 + j * Cfg::MN_ATOM, k0);
           } else {
-            ptx::tma_load_2d(a_dst, &tmap_a, full_bar(s), k0, m0);
+            ptx::tma_load_2d<kPair>(a_dst, &tmap_a, full, k0, m0);
           }
           if constexpr (Cfg::B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / Cfg::MN_ATOM; ++j)
-              ptx::tma_load_2d(b_dst + j * Cfg::MN_BOX_BYTES, &tmap_b, full_bar(s),
-                               n0 + j * Cfg::MN_ATOM, k0);
+            for (int j = 0; j < Cfg::BN_CTA / Cfg::MN_ATOM; ++j)
+              ptx::tma_load_2d<kPair>(b_dst + j * Cfg::MN_BOX_BYTES, &tmap_b, full, n0 + j * Cfg::MN_ATOM, k0);
           } else {
-            ptx::tma_load_2d(b_dst, &tmap_b, full_bar(s), k0, n0);
+            ptx::tma_load_2d<kPair>(b_dst, &tmap_b, full, k0, n0);
           }
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      SegmentIter it(args);
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && cta == 0) {
+      SegmentIter it(args, worker, workers);
       Segment seg;
       int s = 0;
       uint32_t ph = 0;
@@ -351,14 +384,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 Cfg::B_MN ? ptx::make_smem_desc(b_addr + k * Cfg::UMMA_K * 128, Cfg::MN_BOX_BYTES,
                                                 Cfg::MN_SBO, Cfg::MN_LAYOUT)
                           : ptx::make_smem_desc(b_addr + k * 32, 16, 1024);
-            ptx::umma<1, kTf32>(d_tmem, a_desc, b_desc, args.idesc,
-                                (kb > seg.kb0 || k > 0) ? 1u : 0u);
+            ptx::umma<CTAS, kTf32>(d_tmem, a_desc, b_desc, args.idesc, (kb > seg.kb0 || k > 0) ? 1u : 0u);
           }
-          ptx::umma_commit(empty_bar(s));      // stage reusable once these MMAs have read it
+          // The stage is reusable (in both CTAs) once these MMAs have read it.
+          if constexpr (kPair) ptx::umma_commit_pair(empty_bar(s), 3);
+          else ptx::umma_commit(empty_bar(s));
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
         if (!ok) break;
-        ptx::umma_commit(acc_full_bar(b));     // accumulator complete
+        // Accumulator complete (in both CTAs' tensor memory).
+        if constexpr (kPair) ptx::umma_commit_pair(acc_full_bar(b), 3);
+        else ptx::umma_commit(acc_full_bar(b));
         ++n_acc;
       }
     }
@@ -366,7 +402,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int q = warp & 3;                    // TMEM lane quarter this warp may access
     const int half = (warp - 2) >> 2;          // which of the quarter's two warps: chunks half, half + 2, ...
-    SegmentIter it(args);
+    SegmentIter it(args, worker, workers);
     Segment seg;
     uint32_t n_acc = 0;
     bool ok = true;
@@ -375,7 +411,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t acc_ph = (n_acc >> 1) & 1u;
       if (!wait(acc_full_bar(b), acc_ph, DEV_TIMEOUT_EPILOGUE)) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      const int row = seg.m_blk * BM + q * 32 + lane;
+      const int row = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32 + lane;
       const bool row_ok = row < args.M;
 #pragma unroll 1
       for (int c = half; c < BN / 32; c += 2) {
@@ -416,18 +452,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             store_row_chunk(args.out, args.out_dtype, static_cast<long long>(row) * args.ld_out + col0, v, valid);
         }
       }
+      // This warp has read its share of the accumulator: tell the (leader's) MMA issuer.
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(acc_empty_bar(b));
+      if (lane == 0) {
+        if constexpr (kPair) ptx::mbar_arrive_cluster(acc_empty_bar(b), 0);
+        else ptx::mbar_arrive(acc_empty_bar(b));
+      }
       ++n_acc;
     }
   }
 
   ptx::tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kPair) {
+    // Neither CTA may free tensor memory or exit while the other can still signal its barriers
+    // or while the leader's MMAs still write the peer's accumulators.
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  } else {
+    __syncthreads();
+  }
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc<1>(tmem_base, Cfg::TMEM_COLS);
+    ptx::tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
   }
 }
 

@@ -30,59 +30,70 @@ act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restri
   const int col0 = blockIdx.x * 256 + cg * 8;
   const int row_begin = blockIdx.y * kActRows;
   const int row_end = min(M, row_begin + kActRows);
+  constexpr int kWords = sizeof(T) * 8 / 16;   // 16-byte words per 8 elements
   float sum[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
 
   if (col0 < N) {
-    for (int r = row_begin + rl; r < row_end; r += 8) {
-      float g[8], zz[8];
-      if constexpr (kVec) {
-        // 8 elements: one 16-byte load for 2-byte types, two for fp32.
-        constexpr int kWords = sizeof(T) * 8 / 16;
-        uint4 gq[kWords], zq[kWords];
-        const uint4* gp = reinterpret_cast<const uint4*>(dy + r * ld_dy + col0);
+    // Two rows per iteration: twice the loads in flight per thread.
+    for (int r0 = row_begin + rl; r0 < row_end; r0 += 16) {
+      uint4 gq[2][kWords], zq[2][kWords];
+      float g[2][8], zz[2][8];
 #pragma unroll
-        for (int w = 0; w < kWords; ++w) gq[w] = __ldg(gp + w);
-        if (z != nullptr) {
-          const uint4* zp = reinterpret_cast<const uint4*>(z + r * ld_z + col0);
-#pragma unroll
-          for (int w = 0; w < kWords; ++w) zq[w] = __ldg(zp + w);
-        }
-        const T* ge = reinterpret_cast<const T*>(gq);
-        const T* ze = reinterpret_cast<const T*>(zq);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          g[i] = to_f32<T>(ge[i]);
-          zz[i] = (z != nullptr) ? to_f32<T>(ze[i]) : 0.0f;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const bool in = col0 + i < N;
-          g[i] = in ? to_f32<T>(dy[r * ld_dy + col0 + i]) : 0.0f;
-          zz[i] = (in && z != nullptr) ? to_f32<T>(z[r * ld_z + col0 + i]) : 0.0f;
-        }
-      }
-      act_grad_mul(g, zz, act, act_param);
-      // The stored dZ is rounded to the element type; the column sums use the rounded values,
-      // as a sum over the stored dZ would.
-      T o[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        o[i] = from_f32<T>(g[i]);
-        sum[i] += to_f32<T>(o[i]);
-      }
-      if (dz != nullptr) {
+      for (int u = 0; u < 2; ++u) {
+        const int r = r0 + 8 * u;
+        if (r >= row_end) continue;
         if constexpr (kVec) {
-          constexpr int kWords = sizeof(T) * 8 / 16;
-          uint4* op = reinterpret_cast<uint4*>(dz + r * ld_dz + col0);
+          const uint4* gp = reinterpret_cast<const uint4*>(dy + r * ld_dy + col0);
 #pragma unroll
-          for (int w = 0; w < kWords; ++w) op[w] = reinterpret_cast<const uint4*>(o)[w];
+          for (int w = 0; w < kWords; ++w) gq[u][w] = __ldg(gp + w);
+          if (z != nullptr) {
+            const uint4* zp = reinterpret_cast<const uint4*>(z + r * ld_z + col0);
+#pragma unroll
+            for (int w = 0; w < kWords; ++w) zq[u][w] = __ldg(zp + w);
+          }
         } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (col0 + i < N) dz[r * ld_dz + col0 + i] = o[i];
+          for (int i = 0; i < 8; ++i) {
+            const bool in = col0 + i < N;
+            g[u][i] = in ? to_f32<T>(dy[r * ld_dy + col0 + i]) : 0.0f;
+            zz[u][i] = (in && z != nullptr) ? to_f32<T>(z[r * ld_z + col0 + i]) : 0.0f;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int r = r0 + 8 * u;
+        if (r >= row_end) continue;
+        if constexpr (kVec) {
+          const T* ge = reinterpret_cast<const T*>(gq[u]);
+          const T* ze = reinterpret_cast<const T*>(zq[u]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            g[u][i] = to_f32<T>(ge[i]);
+            zz[u][i] = (z != nullptr) ? to_f32<T>(ze[i]) : 0.0f;
+          }
+        }
+        act_grad_mul(g[u], zz[u], act, act_param);
+        // The stored dZ is rounded to the element type; the column sums use the rounded values,
+        // as a sum over the stored dZ would.
+        alignas(16) T o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          o[i] = from_f32<T>(g[u][i]);
+          if (partial != nullptr) sum[i] += to_f32<T>(o[i]);
+        }
+        if (dz != nullptr) {
+          if constexpr (kVec) {
+            uint4* op = reinterpret_cast<uint4*>(dz + r * ld_dz + col0);
+#pragma unroll
+            for (int w = 0; w < kWords; ++w) op[w] = reinterpret_cast<const uint4*>(o)[w];
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (col0 + i < N) dz[r * ld_dz + col0 + i] = o[i];
+          }
         }
       }
     }

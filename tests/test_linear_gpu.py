@@ -190,6 +190,7 @@ def seeded(shape, out_dim, dtype, seed=0, bias=True, scale=1.0):
 
 
 SHAPES = [
+    ((1536, 320), 768),      # several 256-row tiles (CTA pairs), ragged k-blocks
     ((128, 64), 256),        # exactly one tile, one k-block
     ((256, 512), 512),       # several tiles and k-blocks
     ((300, 264), 520),       # ragged in M, K and N
@@ -198,6 +199,7 @@ SHAPES = [
     ((129, 2048), 136),      # long K
 ]
 FAMILIES = [('tcgen05', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK),
+            ('tcgen05-1cta', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK | _lib.FLAG_NO_PAIR),
             ('streamk', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_FORCE_STREAMK),
             ('generic', _lib.FLAG_FORCE_GENERIC)]
 
