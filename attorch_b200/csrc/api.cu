@@ -267,20 +267,24 @@ int ab200_act_backward(const void* dy, const void* z, void* dz, void* db, int64_
     return p == nullptr || ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * elt) % 16 == 0);
   };
   const bool vec = (N % 8 == 0) && aligned(dy, ld_dy) && aligned(z, ld_z) && aligned(dz, ld_dz);
-  dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(chunks));
+  const bool wide = N >= 1024;     // 256 threads side by side on a row, else 32
+  const int cols_per_block = wide ? 2048 : 256;
+  dim3 grid(static_cast<unsigned>((N + cols_per_block - 1) / cols_per_block), static_cast<unsigned>(chunks));
   const int Mi = static_cast<int>(M), Ni = static_cast<int>(N);
-#define AB200_LAUNCH_ACT(T)                                                                              \
-  do {                                                                                                   \
-    if (vec)                                                                                             \
-      act_backward_kernel<T, true><<<grid, 256, 0, stream>>>(static_cast<const T*>(dy), ld_dy,          \
-          static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param); \
-    else                                                                                                 \
-      act_backward_kernel<T, false><<<grid, 256, 0, stream>>>(static_cast<const T*>(dy), ld_dy,         \
-          static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param); \
+#define AB200_LAUNCH_ACT_V(T, V, C)                                                                  \
+  act_backward_kernel<T, V, C><<<grid, 256, 0, stream>>>(static_cast<const T*>(dy), ld_dy,           \
+      static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param)
+#define AB200_LAUNCH_ACT(T)                                                  \
+  do {                                                                       \
+    if (vec && wide) AB200_LAUNCH_ACT_V(T, true, 256);                       \
+    else if (vec) AB200_LAUNCH_ACT_V(T, true, 32);                           \
+    else if (wide) AB200_LAUNCH_ACT_V(T, false, 256);                        \
+    else AB200_LAUNCH_ACT_V(T, false, 32);                                   \
   } while (0)
   if (dtype == DT_F32) AB200_LAUNCH_ACT(float);
   else if (dtype == DT_F16) AB200_LAUNCH_ACT(__half);
   else AB200_LAUNCH_ACT(__nv_bfloat16);
+#undef AB200_LAUNCH_ACT_V
 #undef AB200_LAUNCH_ACT
   ++g_launches;
   if (cudaGetLastError() != cudaSuccess) return ERR_LAUNCH;

@@ -15,34 +15,39 @@ namespace ab200 {
 
 // ------------------------------------------------------------------------------------------------
 // dZ = dY * act'(Z), plus per-row-block column sums of dZ.
-// Block: 256 threads = 32 column groups (8 columns each) x 8 row lanes; covers 256 columns x
-// kActRows rows.  partial is [gridDim.y][N] fp32.
+// A block of 256 threads covers kColThreads * 8 columns and kActRows rows; kColThreads threads sit
+// side by side on one row and 256 / kColThreads row lanes take alternate rows.  With
+// kColThreads = 256 (wide matrices) every row pass reads 4 KB (2-byte types) of one row
+// contiguously, which keeps DRAM pages open, and a thread owns its 8 columns for all rows of the
+// block, so the column sums need no exchange; with kColThreads = 32 (narrow matrices) the row
+// lanes' sums meet in shared memory.  partial is [gridDim.y][N] fp32.
 // ------------------------------------------------------------------------------------------------
-constexpr int kActRows = 128;
+constexpr int kActRows = 64;
 
-template <class T, bool kVec>
+template <class T, bool kVec, int kColThreads>
 __global__ void __launch_bounds__(256)
 act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restrict__ z, long long ld_z,
                     T* __restrict__ dz, long long ld_dz, float* __restrict__ partial, int M, int N,
                     int act, float act_param) {
-  const int cg = threadIdx.x & 31;
-  const int rl = threadIdx.x >> 5;
-  const int col0 = blockIdx.x * 256 + cg * 8;
+  constexpr int kRowLanes = 256 / kColThreads;
+  constexpr int kUnroll = 4;                   // rows in flight per thread
+  constexpr int kWords = sizeof(T) * 8 / 16;   // 16-byte words per 8 elements
+  const int ct = threadIdx.x % kColThreads;
+  const int rl = threadIdx.x / kColThreads;
+  const int col0 = (blockIdx.x * kColThreads + ct) * 8;
   const int row_begin = blockIdx.y * kActRows;
   const int row_end = min(M, row_begin + kActRows);
-  constexpr int kWords = sizeof(T) * 8 / 16;   // 16-byte words per 8 elements
   float sum[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
 
   if (col0 < N) {
-    // Two rows per iteration: twice the loads in flight per thread.
-    for (int r0 = row_begin + rl; r0 < row_end; r0 += 16) {
-      uint4 gq[2][kWords], zq[2][kWords];
-      float g[2][8], zz[2][8];
+    for (int r0 = row_begin + rl; r0 < row_end; r0 += kRowLanes * kUnroll) {
+      uint4 gq[kUnroll][kWords], zq[kUnroll][kWords];
+      float g[kUnroll][8], zz[kUnroll][8];
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int r = r0 + 8 * u;
+      for (int u = 0; u < kUnroll; ++u) {
+        const int r = r0 + kRowLanes * u;
         if (r >= row_end) continue;
         if constexpr (kVec) {
           const uint4* gp = reinterpret_cast<const uint4*>(dy + r * ld_dy + col0);
@@ -63,8 +68,8 @@ act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restri
         }
       }
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int r = r0 + 8 * u;
+      for (int u = 0; u < kUnroll; ++u) {
+        const int r = r0 + kRowLanes * u;
         if (r >= row_end) continue;
         if constexpr (kVec) {
           const T* ge = reinterpret_cast<const T*>(gq[u]);
@@ -100,16 +105,24 @@ act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restri
   }
 
   if (partial != nullptr) {
-    __shared__ float red[8][256 + 8];
+    float* dst = partial + static_cast<long long>(blockIdx.y) * N;
+    if constexpr (kRowLanes == 1) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) red[rl][cg * 8 + i] = sum[i];
-    __syncthreads();
-    const int c = threadIdx.x;   // one column per thread
-    float s = 0.0f;
+      for (int i = 0; i < 8; ++i)
+        if (col0 + i < N) dst[col0 + i] = sum[i];
+    } else {
+      __shared__ float red[kRowLanes][kColThreads * 8 + 8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) s += red[j][c];
-    const int col = blockIdx.x * 256 + c;
-    if (col < N) partial[static_cast<long long>(blockIdx.y) * N + col] = s;
+      for (int i = 0; i < 8; ++i) red[rl][ct * 8 + i] = sum[i];
+      __syncthreads();
+      for (int c = threadIdx.x; c < kColThreads * 8; c += 256) {
+        float s = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kRowLanes; ++j) s += red[j][c];
+        const int col = blockIdx.x * kColThreads * 8 + c;
+        if (col < N) dst[col] = s;
+      }
+    }
   }
 }
 

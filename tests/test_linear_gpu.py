@@ -210,7 +210,8 @@ FAMILIES = [('tcgen05', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK),
 @pytest.mark.parametrize('act_func', [None, 'gelu', 'relu'])
 def test_oracle_parity(family, flags, dtype, shape, out_dim, act_func):
     x, w, b, dy = seeded(shape, out_dim, dtype)
-    tol = 1e-4 if (family == 'generic' and dtype is torch.float32) else TOL
+    # Exact fp32 products on the generic kernel; what is left is fp32 summation order.
+    tol = 5e-4 if (family == 'generic' and dtype is torch.float32) else TOL
     check_layer(x, w, b, act_func, dy, tol=tol, flags=flags)
 
 
