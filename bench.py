@@ -147,41 +147,76 @@ def run_reference(args, spec, world_size, rank):
     print(json.dumps(line), flush=True)
 
 
-def forward_kernel_launcher(spec, tokens, device, lib):
+def kernel_launcher(spec, tokens, device, lib, which='fwd'):
     """
-    Returns (launch, flops): `launch()` enqueues the forward tcgen05 GEMM of the workload's first
-    layer through the C ABI exactly as the layer launches it (X[M, K] * W[K, N] with bias,
-    activation and the pre-activation store), on the current stream.
+    Returns (launch, work, unit): `launch()` enqueues one kernel of the workload's first layer through
+    the C ABI exactly as the layer launches it, on the current stream.  `which`:
+      fwd      forward tcgen05 GEMM, X[M, K] * W[K, N] with bias, activation, pre-activation store
+      dx       backward tcgen05 GEMM dX = dZ * W^T
+      dw       backward tcgen05 GEMM dW = X^T * dZ
+      act_bwd  dZ = dY * act'(Z) with the bias-gradient column sums
+    `work` is the algorithmic work of one launch: floating-point operations for the GEMMs, bytes
+    (dY and Z read, dZ written) for act_bwd.
     """
     from attorch_b200 import _lib
     from attorch_b200.acts import act_id, parse_act_func
     k0, n0, act0, _ = spec['layers'][0]
     op_dtype = spec['autocast'] or spec['param_dtype']
+    grad_dtype = spec['param_dtype']
+    ids = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
     xo = torch.randn(tokens, k0, device=device).to(op_dtype)
     wo = (torch.randn(k0, n0, device=device) / k0 ** 0.5).to(op_dtype)
     bo = torch.randn(n0, device=device).to(op_dtype)
     yo = torch.empty(tokens, n0, device=device, dtype=op_dtype)
-    zo = torch.empty(tokens, n0, device=device, dtype=op_dtype)
+    zo = torch.randn(tokens, n0, device=device).to(op_dtype)
+    dyo = (torch.randn(tokens, n0, device=device) * 0.01).to(op_dtype)
+    dzo = torch.randn(tokens, n0, device=device).to(op_dtype)
+    dxo = torch.empty(tokens, k0, device=device, dtype=spec['input_dtype'])
+    dwo = torch.empty(k0, n0, device=device, dtype=grad_dtype)
+    dbo = torch.empty(n0, device=device, dtype=grad_dtype)
+    ws = torch.empty(max(lib.ab200_act_backward_workspace_bytes(tokens, n0), 16), dtype=torch.uint8, device=device)
     status = torch.zeros(1, dtype=torch.int32, device=device)
-    dt_id = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[op_dtype]
+    dt_id = ids[op_dtype]
     name, param = parse_act_func(act0)
     stream = torch.cuda.current_stream().cuda_stream
-    keep = (xo, wo, bo, yo, zo, status)
+    keep = (xo, wo, bo, yo, zo, dyo, dzo, dxo, dwo, dbo, ws, status)
+    flags = _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK
+    gemm_flops = 2.0 * tokens * k0 * n0
 
-    def launch():
-        rc = lib.ab200_linear_forward(xo.data_ptr(), wo.data_ptr(), bo.data_ptr(), zo.data_ptr(), yo.data_ptr(),
-                                      tokens, k0, n0, k0, 1, n0, 1, n0, n0, dt_id, dt_id, dt_id,
-                                      act_id(name), param or 0.0, None, 0, status.data_ptr(), stream,
-                                      _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK)
-        _lib.check(rc, 'ab200_linear_forward')
+    def fwd():
+        _lib.check(lib.ab200_linear_forward(
+            xo.data_ptr(), wo.data_ptr(), bo.data_ptr(), zo.data_ptr(), yo.data_ptr(), tokens, k0, n0,
+            k0, 1, n0, 1, n0, n0, dt_id, dt_id, dt_id, act_id(name), param or 0.0, None, 0,
+            status.data_ptr(), stream, flags), 'ab200_linear_forward')
         return keep
 
-    return launch, 2.0 * tokens * k0 * n0
+    def dx():
+        _lib.check(lib.ab200_linear_backward_input(
+            dzo.data_ptr(), wo.data_ptr(), dxo.data_ptr(), tokens, k0, n0, n0, 1, n0, 1, k0, dt_id,
+            ids[dxo.dtype], None, 0, status.data_ptr(), stream, flags), 'ab200_linear_backward_input')
+        return keep
+
+    def dw():
+        _lib.check(lib.ab200_linear_backward_weight(
+            xo.data_ptr(), dzo.data_ptr(), dwo.data_ptr(), tokens, k0, n0, k0, 1, n0, 1, n0, dt_id,
+            ids[dwo.dtype], None, 0, status.data_ptr(), stream, flags), 'ab200_linear_backward_weight')
+        return keep
+
+    def act_bwd():
+        _lib.check(lib.ab200_act_backward(
+            dyo.data_ptr(), zo.data_ptr(), dzo.data_ptr(), dbo.data_ptr(), tokens, n0, n0, n0, n0, dt_id,
+            ids[dbo.dtype], act_id(name), param or 0.0, ws.data_ptr(), ws.numel(), stream),
+            'ab200_act_backward')
+        return keep
+
+    if which == 'act_bwd':
+        return act_bwd, 3.0 * tokens * n0 * dyo.element_size(), 'bytes'
+    return {'fwd': fwd, 'dx': dx, 'dw': dw}[which], gemm_flops, 'flops'
 
 
 def kernel_only(args, spec, tokens, device, lib):
-    """A few launches of the dominant kernel and nothing else: the target of ncu captures."""
-    launch, flops = forward_kernel_launcher(spec, tokens, device, lib)
+    """A few launches of one kernel and nothing else: the target of ncu captures."""
+    launch, work, unit = kernel_launcher(spec, tokens, device, lib, args.kernel_only)
     for _ in range(max(args.warmup, 1)):
         launch()
     torch.cuda.synchronize()
@@ -192,8 +227,8 @@ def kernel_only(args, spec, tokens, device, lib):
     r1.record()
     torch.cuda.synchronize()
     ms = r0.elapsed_time(r1) / args.steps
-    print(json.dumps({'kernel_only': True, 'tokens': tokens, 'kernel_ms': ms,
-                      'tflops': flops / (ms * 1e-3) / 1e12}), flush=True)
+    rate = {'tflops': work / (ms * 1e-3) / 1e12} if unit == 'flops' else {'gbs': work / (ms * 1e-3) / 1e9}
+    print(json.dumps({'kernel_only': args.kernel_only, 'tokens': tokens, 'kernel_ms': ms, **rate}), flush=True)
 
 
 def main():
@@ -206,8 +241,8 @@ def main():
     parser.add_argument('--no-cpu-baseline', action='store_true')
     parser.add_argument('--no-graph', action='store_true',
                         help='launch every step eagerly instead of replaying one captured CUDA graph')
-    parser.add_argument('--kernel-only', action='store_true',
-                        help='launch only the dominant kernel (for ncu captures of a small case)')
+    parser.add_argument('--kernel-only', choices=['fwd', 'dx', 'dw', 'act_bwd'], default=None,
+                        help='launch only this kernel of the first layer (for ncu captures)')
     parser.add_argument('--tokens', type=int, default=None,
                         help='override the tokens per GPU (profiling of reduced cases)')
     args = parser.parse_args()
@@ -377,7 +412,7 @@ def main():
     # the launching stream.
     peaks, peak_source = measured_peaks()
     k0, n0 = spec['layers'][0][0], spec['layers'][0][1]
-    launch_fwd, _ = forward_kernel_launcher(spec, tokens, device, lib)
+    launch_fwd, _, _ = kernel_launcher(spec, tokens, device, lib, 'fwd')
 
     for _ in range(5):
         launch_fwd()
