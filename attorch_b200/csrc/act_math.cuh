@@ -48,12 +48,12 @@ __device__ __forceinline__ float tanh_(float x) { return 2.0f * sigmoid(2.0f * x
 // instruction count of the activation is what decides whether it hides behind the main loop.
 __device__ __forceinline__ float erf_fast(float x) {
   const float ax = fabsf(x);
-  const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+  const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.0f));
   float poly = fmaf(1.061405429f, t, -1.453152027f);
   poly = fmaf(poly, t, 1.421413741f);
   poly = fmaf(poly, t, -0.284496736f);
   poly = fmaf(poly, t, 0.254829592f);
-  const float r = 1.0f - poly * t * __expf(-ax * ax);
+  const float r = 1.0f - poly * t * exp2f(-1.44269504f * ax * ax);
   return copysignf(r, x);
 }
 // log(1 + e^x) without overflow.
@@ -113,8 +113,8 @@ __device__ __forceinline__ float grad(float x, float p) {
   if constexpr (A == ACT_RELU) return x <= 0.0f ? 0.0f : 1.0f;
   if constexpr (A == ACT_GELU) {
     // Phi(x) + x * phi(x).  erf(x / sqrt 2) and phi(x) need the same exponential, exp(-x^2 / 2).
-    const float e = __expf(-0.5f * x * x);
-    const float t = __fdividef(1.0f, fmaf(0.3275911f * kRsqrt2, fabsf(x), 1.0f));
+    const float e = exp2f(-0.72134752f * x * x);               // exp(-x^2 / 2)
+    const float t = __frcp_rn(fmaf(0.3275911f * kRsqrt2, fabsf(x), 1.0f));
     float poly = fmaf(1.061405429f, t, -1.453152027f);
     poly = fmaf(poly, t, 1.421413741f);
     poly = fmaf(poly, t, -0.284496736f);

@@ -1,6 +1,7 @@
 // Types shared by the kernels and the C-ABI layer.
 #pragma once
 #include <cstdint>
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -77,6 +78,23 @@ __device__ __forceinline__ float round_through(float v, int dt) {
   if (dt == DT_F16) return __half2float(__float2half_rn(v));
   if (dt == DT_BF16) return __bfloat162float(__float2bfloat16_rn(v));
   return v;
+}
+
+// Rounds eight fp32 values to T, packed in order into 16 (2-byte T) or 32 (fp32) bytes; two values
+// per conversion instruction for the 2-byte types.
+template <class T>
+__device__ __forceinline__ void pack8(const float (&v)[8], T (&o)[8]) {
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = v[i];
+  } else if constexpr (sizeof(T) == 2 && std::is_same<T, __half>::value) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) reinterpret_cast<__half2*>(o)[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      reinterpret_cast<__nv_bfloat162*>(o)[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  }
 }
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, int dt) {

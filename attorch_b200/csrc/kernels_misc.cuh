@@ -22,7 +22,7 @@ namespace ab200 {
 // block, so the column sums need no exchange; with kColThreads = 32 (narrow matrices) the row
 // lanes' sums meet in shared memory.  partial is [gridDim.y][N] fp32.
 // ------------------------------------------------------------------------------------------------
-constexpr int kActRows = 64;
+constexpr int kActRows = 16;
 
 template <class T, bool kVec, int kColThreads>
 __global__ void __launch_bounds__(256)
@@ -30,7 +30,7 @@ act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restri
                     T* __restrict__ dz, long long ld_dz, float* __restrict__ partial, int M, int N,
                     int act, float act_param) {
   constexpr int kRowLanes = 256 / kColThreads;
-  constexpr int kUnroll = 4;                   // rows in flight per thread
+  constexpr int kUnroll = kRowLanes == 1 ? 4 : 2;   // rows in flight per thread
   constexpr int kWords = sizeof(T) * 8 / 16;   // 16-byte words per 8 elements
   const int ct = threadIdx.x % kColThreads;
   const int rl = threadIdx.x / kColThreads;
@@ -84,10 +84,10 @@ act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restri
         // The stored dZ is rounded to the element type; the column sums use the rounded values,
         // as a sum over the stored dZ would.
         alignas(16) T o[8];
+        pack8<T>(g[u], o);
+        if (partial != nullptr) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          o[i] = from_f32<T>(g[u][i]);
-          if (partial != nullptr) sum[i] += to_f32<T>(o[i]);
+          for (int i = 0; i < 8; ++i) sum[i] += to_f32<T>(o[i]);
         }
         if (dz != nullptr) {
           if constexpr (kVec) {
