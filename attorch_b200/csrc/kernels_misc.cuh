@@ -22,7 +22,7 @@ namespace ab200 {
 // block, so the column sums need no exchange; with kColThreads = 32 (narrow matrices) the row
 // lanes' sums meet in shared memory.  partial is [gridDim.y][N] fp32.
 // ------------------------------------------------------------------------------------------------
-constexpr int kActRows = 16;
+constexpr int kActRows = 128;
 
 template <class T, bool kVec, int kColThreads>
 __global__ void __launch_bounds__(256)
@@ -126,14 +126,27 @@ act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restri
   }
 }
 
-// db[n] = sum over row blocks, in block order (deterministic), rounded once to the output type.
-__global__ void colsum_finish_kernel(const float* __restrict__ partial, int chunks, int N, void* db,
-                                     int db_dtype) {
-  const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  if (n >= N) return;
+// db[n] = sum over row blocks of partial[c][n], rounded once to the output type.  A block of 256
+// threads handles 32 columns with 8 lanes per column; lane j adds blocks j, j + 8, ... in order and
+// the 8 lane sums are added in lane order, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256)
+colsum_finish_kernel(const float* __restrict__ partial, int chunks, int N, void* db, int db_dtype) {
+  __shared__ float red[8][33];
+  const int cl = threadIdx.x & 31;
+  const int lane = threadIdx.x >> 5;
+  const int n = blockIdx.x * 32 + cl;
   float s = 0.0f;
-  for (int c = 0; c < chunks; ++c) s += partial[static_cast<long long>(c) * N + n];
-  store_from_f32(db, db_dtype, n, s);
+  if (n < N) {
+    for (int c = lane; c < chunks; c += 8) s += partial[static_cast<long long>(c) * N + n];
+  }
+  red[lane][cl] = s;
+  __syncthreads();
+  if (lane == 0 && n < N) {
+    float t = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t += red[j][cl];
+    store_from_f32(db, db_dtype, n, t);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
