@@ -42,6 +42,9 @@ SIGNATURES = {
     'ab200_act_backward_workspace_bytes': (_i64, [_i64, _i64]),
     'ab200_act_backward': (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64,
                                   _int, _int, _int, _f32, _ptr, _i64, _ptr]),
+    'ab200_act_backward_static': (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64,
+                                         _int, _int, _int, _f32, _ptr]),
+    'ab200_act_backward_static_max_floats': (_i64, []),
     'ab200_linear_backward_input': (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64,
                                            _i64, _i64, _i64, _i64, _i64,
                                            _int, _int, _ptr, _i64, _ptr, _ptr, _int]),

@@ -136,7 +136,9 @@ const char* ab200_error_string(int code) {
     case ERR_TENSOR_MAP: return "cuTensorMapEncodeTiled rejected the operand";
     case ERR_LAUNCH: return "kernel launch failed";
     case ERR_TOO_LARGE: return "a dimension exceeds 2^31 - 1";
-    case ERR_DRIVER: return "CUDA driver entry point unavailable";
+    case ERR_DRIVER: return "CUDA driver entry point or symbol address unavailable";
+    case ERR_STATIC_SCRATCH_TOO_SMALL:
+      return "shape needs more scratch than the built-in array of ab200_act_backward_static holds";
     case DEV_TIMEOUT_PRODUCER: return "device: TMA producer gave up waiting for a free stage";
     case DEV_TIMEOUT_MMA: return "device: MMA issuer gave up waiting for operands or an accumulator";
     case DEV_TIMEOUT_EPILOGUE: return "device: epilogue gave up waiting for an accumulator";
@@ -292,6 +294,101 @@ int ab200_act_backward(const void* dy, const void* z, void* dz, void* db, int64_
   if (cudaGetLastError() != cudaSuccess) return ERR_LAUNCH;
   if (db != nullptr) {
     colsum_finish_kernel<<<(Ni + 31) / 32, 256, 0, stream>>>(partial, chunks, Ni, db, db_dtype);
+    ++g_launches;
+    if (cudaGetLastError() != cudaSuccess) return ERR_LAUNCH;
+  }
+  return OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Activation backward for callers that must not allocate.
+//
+// The column-sum partials live in this file-scope device array instead of a caller-supplied
+// workspace.  Every GPU that loads the library holds these 4 MiB until the process exits.  In host
+// code the array's name is only a handle for cudaGetSymbolAddress; the address a kernel needs is
+// looked up once per device (with that device current) and cached.
+// ------------------------------------------------------------------------------------------------
+constexpr int64_t kStaticScratchFloats = 1 << 20;
+static __device__ __align__(256) float g_static_colsum_scratch[kStaticScratchFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::atomic<float*> g_static_scratch_ptr[kMaxDevices];
+
+// Device address of g_static_colsum_scratch on the current device, or nullptr with *rc set.
+float* static_scratch_for_current_device(int* rc) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    *rc = ERR_LAUNCH;
+    return nullptr;
+  }
+  float* ptr = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
+    void* sym = nullptr;
+    if (cudaGetSymbolAddress(&sym, g_static_colsum_scratch) != cudaSuccess || sym == nullptr) {
+      *rc = ERR_DRIVER;
+      return nullptr;
+    }
+    ptr = static_cast<float*>(sym);
+    g_static_scratch_ptr[dev].store(ptr, std::memory_order_release);
+  }
+  return ptr;
+}
+}  // namespace
+
+int64_t ab200_act_backward_static_max_floats(void) { return kStaticScratchFloats; }
+
+int ab200_act_backward_static(const void* dy, const void* z, void* dz, void* db, int64_t M, int64_t N,
+                              int64_t ld_dy, int64_t ld_z, int64_t ld_dz, int dtype, int db_dtype,
+                              int act, float act_param, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || N < 0) return ERR_BAD_SHAPE;
+  if (!fits_int(M) || !fits_int(N)) return ERR_TOO_LARGE;
+  if (!valid_dtype(dtype) || (db && !valid_dtype(db_dtype))) return ERR_BAD_DTYPE;
+  if (!valid_act(act)) return ERR_BAD_ACT;
+  if (N == 0) return OK;
+  if (M > 0 && (!dy || (act != ACT_NONE && !z))) return ERR_NULL_POINTER;
+  if (dz == nullptr && db == nullptr) return OK;
+  if (ld_dy < N || (z && ld_z < N) || (dz && ld_dz < N)) return ERR_BAD_STRIDE;
+  const int64_t chunks = (M + kActRows - 1) / kActRows;
+  // One fp32 per (row block, column): reject shapes the built-in array cannot hold.
+  if (db != nullptr && chunks * N > kStaticScratchFloats) return ERR_STATIC_SCRATCH_TOO_SMALL;
+  if (M == 0) {
+    if (db == nullptr) return OK;
+    return cudaMemsetAsync(db, 0, N * dtype_size(db_dtype), stream) == cudaSuccess ? OK : ERR_LAUNCH;
+  }
+  float* partial = nullptr;
+  if (db != nullptr) {
+    int rc = OK;
+    partial = static_scratch_for_current_device(&rc);
+    if (partial == nullptr) return rc;
+  }
+  const int elt = dtype_size(dtype);
+  auto aligned = [&](const void* p, long long ld) {
+    return p == nullptr || ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && (ld * elt) % 16 == 0);
+  };
+  const bool vec = (N % 8 == 0) && aligned(dy, ld_dy) && aligned(z, ld_z) && aligned(dz, ld_dz);
+  dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(chunks));
+  const int Mi = static_cast<int>(M), Ni = static_cast<int>(N);
+  // Each block overwrites its own row of partials for every column below N, and the finishing
+  // kernel reads only those, so nothing left in the array by an earlier call is ever read.
+#define AB200_LAUNCH_ACT_STATIC(T)                                                                     \
+  do {                                                                                                 \
+    if (vec)                                                                                           \
+      act_backward_kernel<T, true, 32><<<grid, 256, 0, stream>>>(static_cast<const T*>(dy), ld_dy,     \
+          static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param); \
+    else                                                                                               \
+      act_backward_kernel<T, false, 32><<<grid, 256, 0, stream>>>(static_cast<const T*>(dy), ld_dy,    \
+          static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param); \
+  } while (0)
+  if (dtype == DT_F32) AB200_LAUNCH_ACT_STATIC(float);
+  else if (dtype == DT_F16) AB200_LAUNCH_ACT_STATIC(__half);
+  else AB200_LAUNCH_ACT_STATIC(__nv_bfloat16);
+#undef AB200_LAUNCH_ACT_STATIC
+  ++g_launches;
+  if (cudaGetLastError() != cudaSuccess) return ERR_LAUNCH;
+  if (db != nullptr) {
+    colsum_finish_kernel<<<(Ni + 31) / 32, 256, 0, stream>>>(partial, static_cast<int>(chunks), Ni, db, db_dtype);
     ++g_launches;
     if (cudaGetLastError() != cudaSuccess) return ERR_LAUNCH;
   }

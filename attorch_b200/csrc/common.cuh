@@ -26,6 +26,7 @@ enum Status : int {
   ERR_LAUNCH = -8,
   ERR_TOO_LARGE = -9,
   ERR_DRIVER = -10,
+  ERR_STATIC_SCRATCH_TOO_SMALL = -11,
 };
 
 // Codes a kernel writes to the caller's device status word when a bounded wait runs out.

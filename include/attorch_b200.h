@@ -44,6 +44,7 @@ extern "C" {
 #define AB200_ERR_LAUNCH (-8)
 #define AB200_ERR_TOO_LARGE (-9)
 #define AB200_ERR_DRIVER (-10)
+#define AB200_ERR_STATIC_SCRATCH_TOO_SMALL (-11)
 
 /* Device-side status codes (written to *status). */
 #define AB200_DEV_OK 0
@@ -154,6 +155,34 @@ int ab200_act_backward(const void* dy, const void* z, void* dz, void* db, int64_
                        float act_param, void* workspace, int64_t workspace_bytes, void* stream);
 
 int64_t ab200_act_backward_workspace_bytes(int64_t M, int64_t N);
+
+/*
+ * Backward, step 1, for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: it allocates freely through PyTorch.)
+ *
+ * Same computation and same results as ab200_act_backward, but the scratch for the bias-gradient
+ * column sums is a fixed 4 MiB array inside the library, so the caller passes only inputs and
+ * outputs and the call never runs cudaMalloc, cudaFree or any allocating routine.  It is meant for
+ * code that runs where allocation is forbidden or impossible: inside a memory pool that has been
+ * frozen for the step, in a latency-critical serving loop that must not touch the allocator, or in
+ * a host thread that owns no allocator at all (for instance a plain C or Go caller of this ABI).
+ *
+ *   - Limit: ceil(M / 128) * N must not exceed ab200_act_backward_static_max_floats() (1 Mi fp32),
+ *     e.g. M = 8192 with N up to 16384; larger shapes return AB200_ERR_STATIC_SCRATCH_TOO_SMALL and
+ *     launch nothing.  The limit applies only when db is wanted; without db no scratch is used.
+ *   - The first call on each device looks up the array's device address (with that device current)
+ *     and remembers it; make that first call before any stream capture begins.
+ *   - Every call on a device shares the one array.  Calls that may overlap on the GPU (different
+ *     streams, or different processes' threads on one context) race on it: serialise them.
+ *     Nothing has to be zeroed between calls; each call overwrites every entry it later reads.
+ *   - Every GPU that loads the library keeps the 4 MiB reserved until the process exits.
+ */
+int ab200_act_backward_static(const void* dy, const void* z, void* dz, void* db, int64_t M, int64_t N,
+                              int64_t ld_dy, int64_t ld_z, int64_t ld_dz, int dtype, int db_dtype,
+                              int act, float act_param, void* stream);
+
+/* Capacity of the built-in scratch of ab200_act_backward_static, in fp32 elements. */
+int64_t ab200_act_backward_static_max_floats(void);
 
 /*
  * Backward, step 2:  dX[M, K] = dZ[M, N] * W^T.   Replaces `pre_act_grad @ weight.T`
