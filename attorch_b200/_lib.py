@@ -33,6 +33,7 @@ SIGNATURES = {
     'ab200_error_string': (ctypes.c_char_p, [_int]),
     'ab200_last_path': (_int, []),
     'ab200_launch_count': (_i64, []),
+    'ab200_set_gemm_cta_limit': (_int, [_int]),
     'ab200_forward_workspace_bytes': (_i64, [_i64, _i64, _i64, _int]),
     'ab200_gemm_workspace_bytes': (_i64, [_i64, _i64, _i64]),
     'ab200_linear_forward': (_int, [_ptr, _ptr, _ptr, _ptr, _ptr,

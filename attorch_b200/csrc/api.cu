@@ -148,6 +148,11 @@ const char* ab200_error_string(int code) {
 }
 
 int ab200_last_path(void) { return g_last_path; }
+int ab200_set_gemm_cta_limit(int ctas) {
+  const int previous = gemm_cta_limit();
+  set_gemm_cta_limit(ctas);
+  return previous;
+}
 int64_t ab200_launch_count(void) { return g_launches.load(); }
 
 int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N, int flags) {

@@ -2,6 +2,8 @@
 // runtime so that the library does not link against libcuda), the SM count and the family dispatch.
 #include "gemm_launch.cuh"
 
+#include <atomic>
+
 namespace ab200 {
 namespace {
 
@@ -55,6 +57,12 @@ int sm_count() {
   }
   return cached;
 }
+
+namespace {
+std::atomic<int> g_cta_limit{0};
+}
+int gemm_cta_limit() { return g_cta_limit.load(std::memory_order_relaxed); }
+void set_gemm_cta_limit(int ctas) { g_cta_limit.store(ctas < 0 ? 0 : ctas, std::memory_order_relaxed); }
 
 int launch_tc(const TcProblem& p, int bn, cudaStream_t stream) {
   if (p.op_dtype == DT_F32) {

@@ -26,6 +26,11 @@ struct TcProblem {
 // Number of SMs of the current device (148 if it cannot be queried).
 int sm_count();
 
+// Upper bound on the CTAs a GEMM launch may use (0 = every SM).  A persistent GEMM that takes every
+// SM leaves none for a collective running beside it; a caller that overlaps the two lowers this.
+int gemm_cta_limit();
+void set_gemm_cta_limit(int ctas);
+
 // Launches p with a BN-wide tile on the kernel family given by p.a_mn / p.b_mn / p.op_dtype.
 int launch_tc(const TcProblem& p, int bn, cudaStream_t stream);
 
@@ -104,7 +109,10 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   }
   const long long tiles = static_cast<long long>(g.tiles_m) * g.tiles_n;
   const long long work = g.stream_k ? tiles * g.k_blocks : tiles;
-  const int workers = static_cast<int>(work < max_workers[dev] ? work : max_workers[dev]);
+  int cap = max_workers[dev];
+  const int limit = gemm_cta_limit();
+  if (limit > 0 && limit / Cfg::CTAS < cap) cap = limit / Cfg::CTAS > 0 ? limit / Cfg::CTAS : 1;
+  const int workers = static_cast<int>(work < cap ? work : cap);
   if (workers <= 0) return OK;
 
   cudaLaunchConfig_t cfg = {};

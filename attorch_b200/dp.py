@@ -19,6 +19,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
+from . import _lib
 from .linear_layer import Linear
 
 
@@ -42,8 +43,12 @@ class GradientBuckets:
             (or torch.distributed not initialised) no collective is issued.
         overlap: Issue each layer's all-reduce on a side stream as soon as its gradients are
             enqueued (CUDA only); otherwise reduce everything in ``finish``.
+        comm_sms: SMs left free for the collective while it overlaps the remaining GEMMs of
+            backward: the persistent GEMM kernels would otherwise hold every SM and the all-reduce
+            would only start once they end.
     """
-    def __init__(self, layers: Iterable[Linear], process_group=None, overlap: bool = True) -> None:
+    def __init__(self, layers: Iterable[Linear], process_group=None, overlap: bool = True,
+                 comm_sms: int = 16) -> None:
         self.layers: List[Linear] = list(layers)
         self.group = process_group
         self.world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -57,6 +62,10 @@ class GradientBuckets:
         self.overlap = overlap and self.device.type == 'cuda' and self.world_size > 1
         self.comm_stream = torch.cuda.Stream(self.device) if self.overlap else None
         self._pending: List[torch.cuda.Event] = []
+        self._gemm_ctas = 0
+        if self.overlap:
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            self._gemm_ctas = max(2, sms - comm_sms)
         offset = 0
         for index, layer in enumerate(self.layers):
             if layer.weight.dtype is not self.dtype:
@@ -87,6 +96,8 @@ class GradientBuckets:
             done = torch.cuda.Event()
             done.record(self.comm_stream)
         self._pending.append(done)
+        # The GEMMs enqueued from here to finish() run beside the collective.
+        _lib.load().ab200_set_gemm_cta_limit(self._gemm_ctas)
 
     def finish(self) -> None:
         """
@@ -100,6 +111,7 @@ class GradientBuckets:
             for done in self._pending:
                 current.wait_event(done)
             self._pending.clear()
+            _lib.load().ab200_set_gemm_cta_limit(0)
         else:
             dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
 

@@ -269,6 +269,7 @@ def main():
     device = torch.device('cuda', local_rank)
     if world_size > 1:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        os.environ.setdefault('NCCL_MAX_CTAS', '16')    # the SMs GradientBuckets leaves free
         dist.init_process_group('nccl', device_id=device)
 
     tokens = args.tokens or spec['tokens_per_gpu'] or spec['global_tokens'] // world_size

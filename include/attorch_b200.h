@@ -101,6 +101,13 @@ const char* ab200_error_string(int code);
 /* Kernel chosen by the last GEMM entry point called on this host thread (AB200_PATH_*). */
 int ab200_last_path(void);
 
+/*
+ * Limits the CTAs (= SMs) the persistent GEMM kernels launch with, process-wide; 0 restores "all".
+ * Returns the previous limit.  For callers that overlap a GEMM with a collective (NCCL needs SMs of
+ * its own, and a GEMM that already holds every SM would make it wait until the GEMM ends).
+ */
+int ab200_set_gemm_cta_limit(int ctas);
+
 /* Number of kernels this library has launched (all host threads) since it was loaded. */
 int64_t ab200_launch_count(void);
 
