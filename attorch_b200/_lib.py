@@ -19,6 +19,7 @@ FLAG_FORCE_TCGEN05 = 2
 FLAG_FORCE_STREAMK = 4
 FLAG_NO_STREAMK = 8
 FLAG_NO_PAIR = 16
+FLAG_NO_TMA_STORE = 32
 
 PATH_TCGEN05, PATH_STREAMK, PATH_GENERIC = 1, 2, 3
 

@@ -27,7 +27,7 @@ EncodeTiledFn get_encode_fn() {
 }  // namespace
 
 int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
-              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32) {
+              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32, bool swizzle64) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return ERR_DRIVER;
   const CUtensorMapDataType dt = dtype == DT_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
@@ -39,9 +39,17 @@ int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uin
   cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                  : (atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B),
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? OK : ERR_TENSOR_MAP;
+}
+
+bool encode_store_map(CUtensorMap* map, int dtype, void* base, uint64_t rows, uint64_t cols, long long ld) {
+  const int elt = dtype_size(dtype);
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || ld <= 0 || (ld * elt) % 16 != 0) return false;
+  // 32 columns: 64 bytes (64-byte swizzle) for 2-byte elements, 128 bytes (128-byte swizzle) for fp32.
+  return encode_2d(map, dtype, base, cols, rows, static_cast<uint64_t>(ld) * elt, 32, 32, false, elt == 2) == OK;
 }
 
 int sm_count() {

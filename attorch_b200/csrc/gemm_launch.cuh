@@ -20,6 +20,7 @@ struct TcProblem {
   const void* b; bool b_mn; long long b_pitch;
   int op_dtype;
   bool allow_pair;   // may run as CTA pairs (cta_group::2) where a configuration for it exists
+  bool allow_tma_store;   // the epilogue may write its outputs with TMA stores
   GemmArgs g;
 };
 
@@ -49,7 +50,12 @@ int launch_tc_4_mk(const TcProblem& p, int bn, cudaStream_t stream);
 // bytes; box = box_inner x box_outer elements; 128-byte swizzle (of 32-byte units if `atom32`, the
 // layout MN-major tf32 operands need); out-of-range elements read as zero.
 int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
-              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32 = false);
+              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32 = false,
+              bool swizzle64 = false);
+
+// Map for the epilogue's TMA stores of 32 x 32 chunks into a row-major [rows, cols] matrix, or false
+// if TMA cannot address it (base or row pitch not 16-byte aligned).
+bool encode_store_map(CUtensorMap* map, int dtype, void* base, uint64_t rows, uint64_t cols, long long ld);
 
 template <class Cfg>
 int launch_cfg(const TcProblem& p, cudaStream_t stream) {
@@ -70,6 +76,14 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   if (rc != OK) return rc;
 
   GemmArgs g = p.g;
+  // Outputs of the direct epilogue go through shared memory and TMA stores where TMA can address
+  // them; otherwise (and for stream-K partial sums) the epilogue stores from registers.
+  CUtensorMap tout = ta, taux = ta;
+  g.tma_store = 0;
+  if (!g.stream_k && p.allow_tma_store) {
+    if (g.out != nullptr && encode_store_map(&tout, g.out_dtype, g.out, g.M, g.N, g.ld_out)) g.tma_store |= 1;
+    if (g.aux != nullptr && encode_store_map(&taux, g.out_dtype, g.aux, g.M, g.N, g.ld_aux)) g.tma_store |= 2;
+  }
   g.tiles_m = (g.M + Cfg::TILE_M - 1) / Cfg::TILE_M;
   g.tiles_n = (g.N + Cfg::BN - 1) / Cfg::BN;
   g.k_blocks = (g.K + Cfg::BKE - 1) / Cfg::BKE;
@@ -129,7 +143,7 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
   }
-  const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<Cfg>, ta, tb, g);
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<Cfg>, ta, tb, tout, taux, g);
   return err == cudaSuccess ? OK : ERR_LAUNCH;
 }
 

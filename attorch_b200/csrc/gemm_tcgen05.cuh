@@ -65,6 +65,7 @@ struct GemmArgs {
   long long ld_partial;
   int partial_transposed;
   int* status;            // device word; a bounded wait that runs out stores a DeviceStatus here
+  int tma_store;          // bit 0: `out` goes through shared memory and a TMA store; bit 1: `aux` too
 };
 
 template <int BN_, int ELT_, bool A_MN_, bool B_MN_, int CTAS_ = 1>
@@ -84,9 +85,13 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int kMaxSmem = 227 * 1024;
   static constexpr int kBarrierBytes = 512;
-  static constexpr int kStagesFit = (kMaxSmem - 1024 - kBarrierBytes) / STAGE_BYTES;
+  static constexpr int kEpilogueWarps = 8;
+  // Each epilogue warp stages one 32 x 32 chunk (up to 4 bytes per element) for its TMA stores.
+  static constexpr int kStageOutBytes = 32 * 32 * 4;
+  static constexpr int kStoreBytes = kEpilogueWarps * kStageOutBytes;
+  static constexpr int kStagesFit = (kMaxSmem - 1024 - kBarrierBytes - kStoreBytes) / STAGE_BYTES;
   static constexpr int STAGES = kStagesFit > 8 ? 8 : kStagesFit;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + kBarrierBytes;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + kStoreBytes + 1024 + kBarrierBytes;
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;   // power of two for BN in {16..256}
   static constexpr int MN_ATOM = 128 / ELT;      // elements in one 128-byte row of an MN-major tile
   static constexpr int MN_BOX_BYTES = BKE * 128; // one TMA box of an MN-major tile
@@ -95,7 +100,6 @@ struct GemmCfg {
   static constexpr bool MN_BASE32 = (ELT == 4);
   static constexpr uint32_t MN_LAYOUT = MN_BASE32 ? ptx::kLayoutSw128Base32 : ptx::kLayoutSw128;
   static constexpr uint32_t MN_SBO = MN_BASE32 ? 512 : 1024;
-  static constexpr int kEpilogueWarps = 8;
   static constexpr int kThreads = 32 * (2 + kEpilogueWarps);
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be 32, 64, 128 or 256");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM allocation must be a power of two");
@@ -190,6 +194,27 @@ __device__ __forceinline__ void store_row_chunk(void* base, int dt, long long of
   }
 }
 
+// Writes this lane's row of a 32 x 32 chunk (lane = row, v = its 32 columns, rounded to dt) into the
+// warp's staging buffer in the layout a swizzled TMA store expects: rows of 64 bytes with the
+// 64-byte swizzle for 2-byte elements, rows of 128 bytes with the 128-byte swizzle for fp32 (16-byte
+// unit j of row r sits at unit j ^ ((r >> 1) & 3), resp. j ^ (r & 7)); conflict-free per quarter warp.
+__device__ __forceinline__ void stage_row_chunk(uint32_t buf, int lane, int dt, const float (&v)[32]) {
+  if (dt == DT_F32) {
+    const uint32_t row = buf + lane * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      ptx::st_shared_v4(row + ((j ^ (lane & 7)) << 4), __float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                        __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
+  } else {
+    const uint32_t row = buf + lane * 64;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      ptx::st_shared_v4(row + ((j ^ ((lane >> 1) & 3)) << 4), pack2(v[8 * j], v[8 * j + 1], dt),
+                        pack2(v[8 * j + 2], v[8 * j + 3], dt), pack2(v[8 * j + 4], v[8 * j + 5], dt),
+                        pack2(v[8 * j + 6], v[8 * j + 7], dt));
+  }
+}
+
 // v[i] += bias[col0 + i] for the valid columns of a 32-column chunk (same addresses in every lane:
 // the loads are warp-wide broadcasts, 16 bytes at a time when the chunk is whole and aligned).
 __device__ __forceinline__ void add_bias_chunk(float (&v)[32], const void* bias, int dt, int col0,
@@ -233,7 +258,9 @@ __device__ __forceinline__ void add_bias_chunk(float (&v)[32], const void* bias,
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
+                    const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_out,
+                    const __grid_constant__ CUtensorMap tmap_aux, const GemmArgs args) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BKE = Cfg::BKE, STAGES = Cfg::STAGES;
   constexpr int CTAS = Cfg::CTAS;
   constexpr bool kTf32 = (Cfg::ELT == 4);
@@ -244,8 +271,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
   uint8_t* smem = smem_raw + pad;              // 1024-byte aligned: required by the 128-byte swizzle
   const uint32_t smem_base = raw_addr + pad;
-  uint8_t* bar_region = smem + STAGES * Cfg::STAGE_BYTES;
-  const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+  const uint32_t store_base = smem_base + STAGES * Cfg::STAGE_BYTES;   // 1024-byte aligned
+  uint8_t* bar_region = smem + STAGES * Cfg::STAGE_BYTES + Cfg::kStoreBytes;
+  const uint32_t bar_base = store_base + Cfg::kStoreBytes;
   // Barrier layout (8 bytes each): full[STAGES], empty[STAGES], acc_full[2], acc_empty[2].
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
@@ -402,6 +430,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int q = warp & 3;                    // TMEM lane quarter this warp may access
     const int half = (warp - 2) >> 2;          // which of the quarter's two warps: chunks half, half + 2, ...
+    const uint32_t stage_buf = store_base + (warp - 2) * Cfg::kStageOutBytes;
     SegmentIter it(args, worker, workers);
     Segment seg;
     uint32_t n_acc = 0;
@@ -445,11 +474,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         } else {
           if (args.bias != nullptr) add_bias_chunk(v, args.bias, args.bias_dtype, col0, valid);
-          if (args.aux != nullptr && row_ok)
-            store_row_chunk(args.aux, args.out_dtype, static_cast<long long>(row) * args.ld_aux + col0, v, valid);
+          const int row0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32;   // chunk's first row
+          if (args.aux != nullptr) {
+            if (args.tma_store & 2) {
+              // One staging buffer per warp: the previous store must have read it out first.
+              if (lane == 0) ptx::tma_store_wait_read();
+              __syncwarp();
+              stage_row_chunk(stage_buf, lane, args.out_dtype, v);
+              ptx::fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0 && row0 < args.M) {
+                ptx::tma_store_2d(&tmap_aux, stage_buf, col0, row0);
+                ptx::tma_store_commit();
+              }
+            } else if (row_ok) {
+              store_row_chunk(args.aux, args.out_dtype, static_cast<long long>(row) * args.ld_aux + col0, v, valid);
+            }
+          }
           act_fwd_inplace(v, args.act, args.act_param);
-          if (row_ok)
+          if (args.tma_store & 1) {
+            if (lane == 0) ptx::tma_store_wait_read();
+            __syncwarp();
+            stage_row_chunk(stage_buf, lane, args.out_dtype, v);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && row0 < args.M) {
+              ptx::tma_store_2d(&tmap_out, stage_buf, col0, row0);
+              ptx::tma_store_commit();
+            }
+          } else if (row_ok) {
             store_row_chunk(args.out, args.out_dtype, static_cast<long long>(row) * args.ld_out + col0, v, valid);
+          }
         }
       }
       // This warp has read its share of the accumulator: tell the (leader's) MMA issuer.
@@ -461,6 +516,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       ++n_acc;
     }
+    // Shared memory must outlive the TMA stores that read it.
+    if (lane == 0) ptx::tma_store_wait_all();
   }
 
   ptx::tc_fence_before_sync();

@@ -269,7 +269,6 @@ def main():
     device = torch.device('cuda', local_rank)
     if world_size > 1:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
-        os.environ.setdefault('NCCL_MAX_CTAS', '16')    # the SMs GradientBuckets leaves free
         dist.init_process_group('nccl', device_id=device)
 
     tokens = args.tokens or spec['tokens_per_gpu'] or spec['global_tokens'] // world_size
@@ -278,7 +277,7 @@ def main():
     layers = [attorch_b200.Linear(k, n, bias=bias, act_func=act, device=device,
                                   dtype=spec['param_dtype'])
               for (k, n, act, bias) in spec['layers']]
-    buckets = GradientBuckets(layers)
+    buckets = GradientBuckets(layers, comm_sms=int(os.environ.get('AB200_COMM_SMS', '16')))
     k_in, n_out = spec['layers'][0][0], spec['layers'][-1][1]
     gen = torch.Generator(device=device).manual_seed(1 + rank)
     x_dev = torch.randn(tokens, k_in, device=device, generator=gen).to(spec['input_dtype'])

@@ -85,6 +85,7 @@ extern "C" {
 #define AB200_FLAG_FORCE_STREAMK 4  /* forward only: use the swap-AB stream-K kernel            */
 #define AB200_FLAG_NO_STREAMK 8     /* forward only: never use the swap-AB stream-K kernel      */
 #define AB200_FLAG_NO_PAIR 16       /* one CTA per tile: no cta_group::2 kernels                */
+#define AB200_FLAG_NO_TMA_STORE 32  /* epilogue stores from registers, not through TMA           */
 
 /* Which kernel the last call on this host thread chose: 1 tcgen05 tile-parallel, 2 tcgen05
  * swap-AB stream-K, 3 generic CUDA-core.  For tests and benchmarks. */

@@ -52,6 +52,7 @@ def test_header_constants_match_python():
     assert int(defines['AB200_FLAG_FORCE_STREAMK']) == _lib.FLAG_FORCE_STREAMK
     assert int(defines['AB200_FLAG_NO_STREAMK']) == _lib.FLAG_NO_STREAMK
     assert int(defines['AB200_FLAG_NO_PAIR']) == _lib.FLAG_NO_PAIR
+    assert int(defines['AB200_FLAG_NO_TMA_STORE']) == _lib.FLAG_NO_TMA_STORE
 
 
 def test_version_and_error_strings(lib):

@@ -200,6 +200,7 @@ SHAPES = [
 ]
 FAMILIES = [('tcgen05', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK),
             ('tcgen05-1cta', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK | _lib.FLAG_NO_PAIR),
+            ('tcgen05-regstore', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK | _lib.FLAG_NO_TMA_STORE),
             ('streamk', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_FORCE_STREAMK),
             ('generic', _lib.FLAG_FORCE_GENERIC)]
 
