@@ -8,6 +8,8 @@ Public surface (mirrors the reference's for this path, attorch/__init__.py:7-22)
     check_status      raise if a kernel reported a device-side time-out
 """
 
-from .linear_layer import Linear, LinearAutoGrad, check_status, get_output_dtype, set_gemm_flags
+from .linear_layer import (Linear, LinearAutoGrad, check_status, get_output_dtype, set_gemm_flags,
+                           set_save_derivative)
 
-__all__ = ['Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags']
+__all__ = ['Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags',
+           'set_save_derivative']

@@ -34,7 +34,10 @@ enum Act : int {
   ACT_CELU = 19,
   ACT_HARDSHRINK = 20,
   ACT_SOFTSHRINK = 21,
-  ACT_COUNT = 22
+  ACT_COUNT = 22,
+  // Backward only: the saved tensor already holds act'(Z) (written by a forward pass that was asked
+  // to save the derivative), so dZ = dY * saved.
+  ACT_SAVED_DERIVATIVE = 22
 };
 
 namespace actm {
@@ -158,6 +161,31 @@ __device__ __forceinline__ float grad(float x, float p) {
   return 1.0f;
 }
 
+// y = act(v) and g = act'(zr) in one go, for a forward pass that saves the derivative instead of the
+// pre-activation.  zr is v rounded to the storage type, i.e. the pre-activation the reference would
+// have stored and differentiated through (attorch/linear_layer.py:104-105, 143-146).  gelu, whose
+// forward value and derivative need the same exponential, evaluates it once at v and carries the
+// derivative over to zr with its own derivative, gelu''(v) = phi(v) (2 - v^2): the neglected term is
+// of order (v - zr)^2, four orders of magnitude below the resolution g is stored with.
+template <int A>
+__device__ __forceinline__ void fwd_grad(float v, float zr, float p, float& y, float& g) {
+  if constexpr (A == ACT_GELU) {
+    const float e = exp2f(-0.72134752f * v * v);               // exp(-v^2 / 2)
+    const float t = __frcp_rn(fmaf(0.3275911f * kRsqrt2, fabsf(v), 1.0f));
+    float poly = fmaf(1.061405429f, t, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    const float cdf = 0.5f + copysignf(0.5f - 0.5f * poly * t * e, v);
+    const float pdf = kRsqrt2Pi * e;
+    y = v * cdf;
+    g = fmaf(v, pdf, cdf) + pdf * fmaf(-v, v, 2.0f) * (zr - v);
+  } else {
+    y = fwd<A>(v, p);
+    g = grad<A>(zr, p);
+  }
+}
+
 }  // namespace actm
 
 // Calls f.template operator()<A>() with the runtime id turned into a compile-time constant,
@@ -207,10 +235,28 @@ __device__ __forceinline__ void act_fwd_inplace(float (&v)[N], int act, float p)
   });
 }
 
+// v[i] <- act(v[i]) and g[i] <- act'(.), see actm::fwd_grad; zr[i] is v[i] rounded to storage.
+template <int N>
+__device__ __forceinline__ void act_fwd_grad(float (&v)[N], const float (&zr)[N], float (&g)[N], int act, float p) {
+  dispatch_act(act, [&]<int A>() {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      float y;
+      actm::fwd_grad<A>(v[i], zr[i], p, y, g[i]);
+      v[i] = y;
+    }
+  });
+}
+
 // g[i] *= act'(z[i]).
 template <int N>
 __device__ __forceinline__ void act_grad_mul(float (&g)[N], const float (&z)[N], int act, float p) {
   if (act == ACT_NONE) return;
+  if (act == ACT_SAVED_DERIVATIVE) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) g[i] *= z[i];
+    return;
+  }
   dispatch_act(act, [&]<int A>() {
 #pragma unroll
     for (int i = 0; i < N; ++i) g[i] *= actm::grad<A>(z[i], p);

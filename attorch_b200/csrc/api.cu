@@ -21,6 +21,7 @@ std::atomic<int64_t> g_launches{0};   // all host threads: backward runs on auto
 
 bool valid_dtype(int dt) { return dt == DT_F32 || dt == DT_F16 || dt == DT_BF16; }
 bool valid_act(int act) { return act >= 0 && act < ACT_COUNT; }
+bool valid_backward_act(int act) { return valid_act(act) || act == ACT_SAVED_DERIVATIVE; }
 
 // Can TMA address this matrix: unit inner stride, 16-byte aligned base and row pitch?
 bool tma_ok(const void* p, long long pitch_elems, long long unit_stride, int elt) {
@@ -74,7 +75,7 @@ int launch_finish(float* partial, const GemmArgs& e, long long M, long long N, c
   if (blocks > cap) blocks = cap;
   streamk_finish_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
       partial, N, static_cast<int>(M), static_cast<int>(N), e.bias, e.bias_dtype, e.aux, e.ld_aux, e.out,
-      e.ld_out, e.out_dtype, e.act, e.act_param);
+      e.ld_out, e.out_dtype, e.act, e.act_param, e.save_grad);
   ++g_launches;
   return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
 }
@@ -183,6 +184,7 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
   if (M == 0 || N == 0) return OK;
   if (!out || (K > 0 && (!x || !w))) return ERR_NULL_POINTER;
   if (ld_out < N || (pre_act && ld_pre < N)) return ERR_BAD_STRIDE;
+  const int save_grad = (flags & AB200_FLAG_SAVE_DERIVATIVE) && act != ACT_NONE ? 1 : 0;
 
   const int elt = dtype_size(op_dtype);
   const bool tc_ok = K > 0 && tma_ok(x, x_stride_m, x_stride_k, elt) && tma_ok(w, w_stride_k, w_stride_n, elt) &&
@@ -199,6 +201,7 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
     a.aux = pre_act; a.ld_aux = ld_pre;
     a.bias = bias; a.bias_dtype = bias_dtype;
     a.act = act; a.act_param = act_param;
+    a.save_grad = save_grad;
     g_last_path = AB200_PATH_GENERIC;
     return launch_any(a, stream);
   }
@@ -229,6 +232,7 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
     GemmArgs e{};
     e.bias = bias; e.bias_dtype = bias_dtype; e.aux = pre_act; e.ld_aux = ld_pre;
     e.out = out; e.ld_out = ld_out; e.out_dtype = out_dtype; e.act = act; e.act_param = act_param;
+    e.save_grad = save_grad;
     return launch_finish(static_cast<float*>(workspace), e, M, N, stream);
   }
 
@@ -239,6 +243,7 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
   g.aux = pre_act; g.ld_aux = ld_pre;
   g.bias = bias; g.bias_dtype = bias_dtype;
   g.act = act; g.act_param = act_param;
+  g.save_grad = save_grad;
   return run_tiles_or_split(p, workspace, workspace_bytes, stream, flags);
 }
 
@@ -254,7 +259,7 @@ int ab200_act_backward(const void* dy, const void* z, void* dz, void* db, int64_
   if (M < 0 || N < 0) return ERR_BAD_SHAPE;
   if (!fits_int(M) || !fits_int(N)) return ERR_TOO_LARGE;
   if (!valid_dtype(dtype) || (db && !valid_dtype(db_dtype))) return ERR_BAD_DTYPE;
-  if (!valid_act(act)) return ERR_BAD_ACT;
+  if (!valid_backward_act(act)) return ERR_BAD_ACT;
   if (N == 0) return OK;
   if (M > 0 && (!dy || (act != ACT_NONE && !z))) return ERR_NULL_POINTER;
   if (dz == nullptr && db == nullptr) return OK;
@@ -351,7 +356,7 @@ int ab200_act_backward_static(const void* dy, const void* z, void* dz, void* db,
   if (M < 0 || N < 0) return ERR_BAD_SHAPE;
   if (!fits_int(M) || !fits_int(N)) return ERR_TOO_LARGE;
   if (!valid_dtype(dtype) || (db && !valid_dtype(db_dtype))) return ERR_BAD_DTYPE;
-  if (!valid_act(act)) return ERR_BAD_ACT;
+  if (!valid_backward_act(act)) return ERR_BAD_ACT;
   if (N == 0) return OK;
   if (M > 0 && (!dy || (act != ACT_NONE && !z))) return ERR_NULL_POINTER;
   if (dz == nullptr && db == nullptr) return OK;

@@ -65,6 +65,7 @@ struct GemmArgs {
   long long ld_partial;
   int partial_transposed;
   int* status;            // device word; a bounded wait that runs out stores a DeviceStatus here
+  int save_grad;          // aux receives act'(Z) instead of Z (see actm::fwd_grad)
   int tma_store;          // bit 0: `out` goes through shared memory and a TMA store; bit 1: `aux` too
 };
 
@@ -475,36 +476,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         } else {
           if (args.bias != nullptr) add_bias_chunk(v, args.bias, args.bias_dtype, col0, valid);
           const int row0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32;   // chunk's first row
-          if (args.aux != nullptr) {
-            if (args.tma_store & 2) {
+          // Writes one 32 x 32 chunk of an output: through the warp's staging buffer and a TMA
+          // store, or straight from registers where TMA cannot address the output.
+          auto emit = [&](const CUtensorMap* map, void* base, long long ld, bool by_tma, const float (&w)[32]) {
+            if (by_tma) {
               // One staging buffer per warp: the previous store must have read it out first.
               if (lane == 0) ptx::tma_store_wait_read();
               __syncwarp();
-              stage_row_chunk(stage_buf, lane, args.out_dtype, v);
+              stage_row_chunk(stage_buf, lane, args.out_dtype, w);
               ptx::fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0 && row0 < args.M) {
-                ptx::tma_store_2d(&tmap_aux, stage_buf, col0, row0);
+                ptx::tma_store_2d(map, stage_buf, col0, row0);
                 ptx::tma_store_commit();
               }
             } else if (row_ok) {
-              store_row_chunk(args.aux, args.out_dtype, static_cast<long long>(row) * args.ld_aux + col0, v, valid);
+              store_row_chunk(base, args.out_dtype, static_cast<long long>(row) * ld + col0, w, valid);
             }
+          };
+          if (args.aux != nullptr && args.save_grad) {
+            // Save act'(Z) instead of Z: backward then needs one multiply per element.
+            float zr[32], g[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) zr[i] = round_through(v[i], args.out_dtype);
+            act_fwd_grad(v, zr, g, args.act, args.act_param);
+            emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, g);
+          } else {
+            if (args.aux != nullptr) emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, v);
+            act_fwd_inplace(v, args.act, args.act_param);
           }
-          act_fwd_inplace(v, args.act, args.act_param);
-          if (args.tma_store & 1) {
-            if (lane == 0) ptx::tma_store_wait_read();
-            __syncwarp();
-            stage_row_chunk(stage_buf, lane, args.out_dtype, v);
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0 && row0 < args.M) {
-              ptx::tma_store_2d(&tmap_out, stage_buf, col0, row0);
-              ptx::tma_store_commit();
-            }
-          } else if (row_ok) {
-            store_row_chunk(args.out, args.out_dtype, static_cast<long long>(row) * args.ld_out + col0, v, valid);
-          }
+          emit(&tmap_out, args.out, args.ld_out, (args.tma_store & 1) != 0, v);
         }
       }
       // This warp has read its share of the accumulator: tell the (leader's) MMA issuer.

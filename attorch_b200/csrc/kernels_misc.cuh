@@ -156,7 +156,7 @@ colsum_finish_kernel(const float* __restrict__ partial, int chunks, int N, void*
 __global__ void streamk_finish_kernel(float* __restrict__ partial, long long ld_partial, int M, int N,
                                       const void* bias, int bias_dtype, void* aux, long long ld_aux,
                                       void* out, long long ld_out, int out_dtype, int act,
-                                      float act_param) {
+                                      float act_param, int save_grad) {
   const long long total = static_cast<long long>(M) * N;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -166,8 +166,14 @@ __global__ void streamk_finish_kernel(float* __restrict__ partial, long long ld_
     float v[1] = {*pp};
     *pp = 0.0f;
     if (bias != nullptr) v[0] += load_as_f32(bias, bias_dtype, n);
-    if (aux != nullptr) store_from_f32(aux, out_dtype, m * ld_aux + n, v[0]);
-    act_fwd_inplace(v, act, act_param);
+    if (aux != nullptr && save_grad) {
+      float zr[1] = {round_through(v[0], out_dtype)}, g[1];
+      act_fwd_grad(v, zr, g, act, act_param);
+      store_from_f32(aux, out_dtype, m * ld_aux + n, g[0]);
+    } else {
+      if (aux != nullptr) store_from_f32(aux, out_dtype, m * ld_aux + n, v[0]);
+      act_fwd_inplace(v, act, act_param);
+    }
     store_from_f32(out, out_dtype, m * ld_out + n, v[0]);
   }
 }
@@ -223,6 +229,7 @@ struct AnyGemmArgs {
   void* aux; long long ld_aux;
   const void* bias; int bias_dtype;
   int act; float act_param;
+  int save_grad;          // aux receives act'(Z) instead of Z
 };
 
 __global__ void __launch_bounds__(256) gemm_any_kernel(const AnyGemmArgs g) {
@@ -287,8 +294,14 @@ __global__ void __launch_bounds__(256) gemm_any_kernel(const AnyGemmArgs g) {
       if (n >= g.N) continue;
       float v[1] = {acc[i][j]};
       if (g.bias != nullptr) v[0] += load_as_f32(g.bias, g.bias_dtype, n);
-      if (g.aux != nullptr) store_from_f32(g.aux, g.out_dtype, m * g.ld_aux + n, v[0]);
-      act_fwd_inplace(v, g.act, g.act_param);
+      if (g.aux != nullptr && g.save_grad) {
+        float zr[1] = {round_through(v[0], g.out_dtype)}, d[1];
+        act_fwd_grad(v, zr, d, g.act, g.act_param);
+        store_from_f32(g.aux, g.out_dtype, m * g.ld_aux + n, d[0]);
+      } else {
+        if (g.aux != nullptr) store_from_f32(g.aux, g.out_dtype, m * g.ld_aux + n, v[0]);
+        act_fwd_inplace(v, g.act, g.act_param);
+      }
       store_from_f32(g.out, g.out_dtype, m * g.ld_out + n, v[0]);
     }
   }

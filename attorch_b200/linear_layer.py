@@ -26,6 +26,20 @@ _scratch: Dict[Tuple[int, int], Dict[str, Tensor]] = {}
 # Flags forwarded to every GEMM entry point (tests use them to pin a kernel family).
 _gemm_flags = 0
 
+# What forward keeps for backward when there is an activation: the pre-activation Z, as the
+# reference does (attorch/linear_layer.py:104-105), or act'(Z) computed in the same epilogue.  The
+# second makes the activation backward one multiply per element instead of a second evaluation of
+# the activation's transcendental functions; it costs one extra rounding of the derivative to the
+# 16-bit storage type.
+_save_derivative = True
+
+
+def set_save_derivative(enabled: bool) -> bool:
+    """Chooses what forward saves for backward (see above); returns the previous setting."""
+    global _save_derivative
+    previous, _save_derivative = _save_derivative, bool(enabled)
+    return previous
+
 
 def set_gemm_flags(flags: int) -> int:
     """Sets the AB200_FLAG_* bits passed to the GEMM entry points; returns the previous value."""
@@ -179,6 +193,7 @@ class LinearAutoGrad(torch.autograd.Function):
             if bias_op is not None and not bias_op.is_contiguous():
                 bias_op = bias_op.contiguous()
 
+            saves_derivative = save_pre_act and _save_derivative
             output = torch.empty((batch_dim, out_feat_dim), device=input.device, dtype=output_dtype)
             pre_act = torch.empty_like(output) if save_pre_act else None
 
@@ -192,7 +207,8 @@ class LinearAutoGrad(torch.autograd.Function):
                 _dtype_id(op_dtype), _dtype_id(output_dtype),
                 _dtype_id(bias_op.dtype) if bias_op is not None else 0,
                 act_id(name), 0.0 if param is None else param,
-                _ptr(workspace), ws_bytes, _ptr(scratch['status']), stream, _gemm_flags),
+                _ptr(workspace), ws_bytes, _ptr(scratch['status']), stream,
+                _gemm_flags | (_lib.FLAG_SAVE_DERIVATIVE if saves_derivative else 0)),
                 'ab200_linear_forward')
 
         ctx.param = param
@@ -208,6 +224,7 @@ class LinearAutoGrad(torch.autograd.Function):
         ctx.weight_shape = weight.shape
         ctx.has_grad_out = (weight_grad_out is not None, bias_grad_out is not None)
         ctx.grad_ready = grad_ready
+        ctx.saved_derivative = requires_grad and name is not None and _save_derivative
         if requires_grad:
             # Backward multiplies in the output dtype, so the converted operands are what it
             # needs; keeping them avoids converting X and W a second time.
@@ -263,7 +280,8 @@ class LinearAutoGrad(torch.autograd.Function):
                     pre_act.stride(0) if pre_act is not None else out_feat_dim,
                     pre_act_grad.stride(0), _dtype_id(op_dtype),
                     _dtype_id(bias_grad.dtype) if need_db else 0,
-                    act_id(ctx.act_func), 0.0 if ctx.param is None else ctx.param,
+                    _lib.ACT_SAVED_DERIVATIVE if ctx.saved_derivative else act_id(ctx.act_func),
+                    0.0 if ctx.param is None else ctx.param,
                     _ptr(workspace), ws_bytes, stream), 'ab200_act_backward')
 
             # dW before dX: in a data-parallel step the all-reduce of dW can then start while

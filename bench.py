@@ -12,6 +12,8 @@ Workloads (synthetic, seeded; shapes of BASELINE.json's configs):
       (dX, dW, db); with N > 1 the fp32 dW / db are SUM-all-reduced every step, overlapped with dX.
   c5  two layers 8192 -> 8192 (gelu + bias, then bias), bf16 parameters, global batch 65536 tokens
       split over the N GPUs (strong scaling), same all-reduce.
+  c3  transformer MLP pair 4096 -> 14336 (silu) -> 4096, no biases, bf16, 16384 tokens per GPU.
+  c4  skinny forward only, fp16, 8192 -> 28672, M in {1, 8, 32, 128}: prints weight-read GB/s.
 
 One "step" is one forward + backward of the workload on one batch.  ``value`` is the whole-job
 TFLOP/s at 6 * M * K * N floating-point operations per layer and step with the inputs resident in
@@ -48,7 +50,11 @@ WORKLOADS = {
     'c5': dict(layers=[(8192, 8192, 'gelu', True), (8192, 8192, None, True)], tokens_per_gpu=None,
                global_tokens=65536, param_dtype=torch.bfloat16, input_dtype=torch.bfloat16,
                autocast=None, scaling='strong'),
+    'c3': dict(layers=[(4096, 14336, 'silu', False), (14336, 4096, None, False)], tokens_per_gpu=16384,
+               global_tokens=None, param_dtype=torch.bfloat16, input_dtype=torch.bfloat16,
+               autocast=None, scaling='weak'),
 }
+# Workload c4 (BASELINE config 4) is forward only and HBM-bound: see skinny_forward().
 
 
 def measured_peaks():
@@ -231,12 +237,54 @@ def kernel_only(args, spec, tokens, device, lib):
     print(json.dumps({'kernel_only': args.kernel_only, 'tokens': tokens, 'kernel_ms': ms, **rate}), flush=True)
 
 
+def skinny_forward(args, device, lib):
+    """
+    BASELINE config 4: y = x @ W for fp16 x [M, 8192], W [8192, 28672], no bias, no activation, under
+    torch.no_grad(), through the module.  HBM-bound: the score is algorithmic bytes
+    2 * (K * N + M * K + M * N) over the CUDA-event time, in GB/s.  W (448 MiB) exceeds the L2, so
+    back-to-back launches are cold.
+    """
+    import attorch_b200
+    K, N = 8192, 28672
+    peaks, peak_source = measured_peaks()
+    layer = attorch_b200.Linear(K, N, bias=False, device=device, dtype=torch.float16)
+    with torch.no_grad():
+        layer.weight.normal_(0, 0.02)
+    rows = []
+    for m in (1, 8, 32, 128):
+        x = torch.randn(m, K, device=device, dtype=torch.float16)
+        with torch.no_grad():
+            for _ in range(max(args.warmup, 3)):
+                layer(x)
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(args.steps):
+                layer(x)
+            t1.record()
+            torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / args.steps
+        nbytes = 2.0 * (K * N + m * K + m * N)
+        rows.append({'M': m, 'us': ms * 1e3, 'gbs': nbytes / (ms * 1e-3) / 1e9,
+                     'frac_of_measured_hbm': nbytes / (ms * 1e-3) / 1e9 / peaks['hbm_gbs'],
+                     'frac_of_nominal_8000': nbytes / (ms * 1e-3) / 1e9 / 8000.0})
+    attorch_b200.check_status()
+    best = max(r['gbs'] for r in rows)
+    print(json.dumps({'metric': 'skinny_forward_weight_read_gbs', 'value': best, 'unit': 'GB/s', 'n_gpus': 1,
+                      'steps': args.steps, 'warmup': args.warmup, 'higher_is_better': True, 'dtype': 'f16',
+                      'data': 'synthetic', 'config': {'workload': 'c4', 'K': K, 'N': N, 'rows': rows,
+                                                      'path': 'module call: memset + swap-AB stream-K tcgen05 + finish'},
+                      'roofline': {'bound': 'hbm', 'achieved': best, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
+                                   'frac': best / peaks['hbm_gbs'], 'traffic': None,
+                                   'peak_source': peak_source}}), flush=True)
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     parser.add_argument('--gpus', type=int, default=1)
     parser.add_argument('--steps', type=int, default=200)
     parser.add_argument('--warmup', type=int, default=10)
-    parser.add_argument('--workload', choices=sorted(WORKLOADS), default='c2')
+    parser.add_argument('--workload', choices=sorted(WORKLOADS) + ['c4'], default='c2')
     parser.add_argument('--impl', choices=['b200', 'reference'], default='b200')
     parser.add_argument('--no-cpu-baseline', action='store_true')
     parser.add_argument('--no-graph', action='store_true',
@@ -247,6 +295,14 @@ def main():
                         help='override the tokens per GPU (profiling of reduced cases)')
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.workload == 'c4':
+        if args.impl == 'reference':
+            print(json.dumps({'impl': 'reference', 'unavailable': 'c4 has no CPU arm; use c2'}))
+            return
+        from attorch_b200 import _lib
+        torch.cuda.set_device(0)
+        skinny_forward(args, torch.device('cuda', 0), _lib.load())
+        return
     spec = WORKLOADS[args.workload]
 
     world_size = int(os.environ.get('WORLD_SIZE', '1'))
@@ -370,6 +426,11 @@ def main():
     # ---------------------------------------------------------------- end to end with host buffers
     host_x = [torch.randn(tokens, k_in).to(spec['input_dtype']).pin_memory() for _ in range(2)]
     dev_x = [torch.empty_like(x_dev).requires_grad_(True) for _ in range(2)]
+    # The step's result that is read back: the last layer's bias gradient, or, for a layer without
+    # bias, the first row of its weight gradient.
+    def result_tensor():
+        last = layers[-1]
+        return last.bias.grad if last.bias is not None else last.weight.grad[0]
     bias_grad_host = torch.empty(n_out, dtype=spec['param_dtype']).pin_memory()
     copy_stream = torch.cuda.Stream(device)
     copied = [torch.cuda.Event() for _ in range(2)]
@@ -391,7 +452,7 @@ def main():
             compute.wait_event(copied[cur])
             step(dev_x[cur])
             consumed[cur].record(compute)
-            bias_grad_host.copy_(layers[-1].bias.grad, non_blocking=True)
+            bias_grad_host.copy_(result_tensor(), non_blocking=True)
         compute.synchronize()
 
     e2e_loop(3)

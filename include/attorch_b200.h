@@ -78,6 +78,9 @@ extern "C" {
 #define AB200_ACT_HARDSHRINK 20
 #define AB200_ACT_SOFTSHRINK 21
 #define AB200_ACT_COUNT 22
+/* ab200_act_backward only: `z` already holds act'(Z), written by a forward call that had
+ * AB200_FLAG_SAVE_DERIVATIVE set; dZ = dY * z. */
+#define AB200_ACT_SAVED_DERIVATIVE 22
 
 /* Flags (bit set) accepted by the GEMM entry points. */
 #define AB200_FLAG_FORCE_GENERIC 1  /* use the any-shape CUDA-core kernel                      */
@@ -86,6 +89,7 @@ extern "C" {
 #define AB200_FLAG_NO_STREAMK 8     /* forward only: never use the swap-AB stream-K kernel      */
 #define AB200_FLAG_NO_PAIR 16       /* one CTA per tile: no cta_group::2 kernels                */
 #define AB200_FLAG_NO_TMA_STORE 32  /* epilogue stores from registers, not through TMA           */
+#define AB200_FLAG_SAVE_DERIVATIVE 64 /* forward: pre_act receives act'(Z) instead of Z            */
 
 /* Which kernel the last call on this host thread chose: 1 tcgen05 tile-parallel, 2 tcgen05
  * swap-AB stream-K, 3 generic CUDA-core.  For tests and benchmarks. */
@@ -120,7 +124,11 @@ int64_t ab200_launch_count(void);
  *   w        [K, N], element strides (w_stride_k, w_stride_n), type op_dtype
  *   bias     [N] of bias_dtype, or NULL
  *   pre_act  [M, N] of out_dtype, row pitch ld_pre, or NULL: the value before the activation,
- *            rounded to out_dtype (what backward differentiates through)
+ *            rounded to out_dtype (what backward differentiates through).  With
+ *            AB200_FLAG_SAVE_DERIVATIVE it receives act'(Z) instead (piecewise derivatives taken at
+ *            the rounded Z, exactly where the reference takes them), which turns the activation
+ *            backward into one multiply per element: pass it to ab200_act_backward as `z` with
+ *            act = AB200_ACT_SAVED_DERIVATIVE
  *   out      [M, N] of out_dtype, row pitch ld_out
  * Accumulation is fp32; fp32 operands are multiplied as TF32 on the tensor cores
  * (attorch/linear_kernels.py:57,165).  The activation is evaluated on the unrounded fp32 value

@@ -234,7 +234,8 @@ def linear_forward(x: Tensor, weight: Tensor, bias: Optional[Tensor], act_func: 
 def linear_backward(output_grad: Tensor, x: Tensor, pre_act: Optional[Tensor], weight: Tensor,
                     act_func: Optional[str], out_dtype: torch.dtype,
                     bias: Optional[Tensor] = None, tf32: Optional[str] = None,
-                    derivative_in_fp32: bool = False, round_to_out_dtype: bool = True
+                    derivative_in_fp32: bool = False, round_to_out_dtype: bool = True,
+                    derivative_rounded: bool = False, stored_derivative: Optional[Tensor] = None
                     ) -> Tuple[Tensor, Tensor, Optional[Tensor]]:
     """
     Returns (dX, dW, db) following attorch/linear_layer.py:125-161.
@@ -252,16 +253,24 @@ def linear_backward(output_grad: Tensor, x: Tensor, pre_act: Optional[Tensor], w
     backward uses true fp32 products, its forward TF32); ``derivative_in_fp32`` evaluates every
     activation derivative in fp32 instead of Z's 16-bit dtype; ``round_to_out_dtype=False`` skips
     the intermediate rounding of dX / dW to the output dtype when the destination is wider (the
-    CUDA kernels write the fp32 accumulator straight into fp32 gradients under autocast).
+    CUDA kernels write the fp32 accumulator straight into fp32 gradients under autocast);
+    ``derivative_rounded`` rounds act'(Z) to Z's dtype before it multiplies dY (the CUDA forward can
+    save the derivative in place of Z); ``stored_derivative`` supplies that saved act'(Z) itself, so
+    that backward is checked through the tensor it actually reads.
     """
     name, param = parse_act_func(act_func)
     dy = output_grad.flatten(0, -2)
     x2 = x.flatten(0, -2)
     if name is None:
         dz = dy
+    elif stored_derivative is not None:
+        dz = (dy.float() * stored_derivative.flatten(0, -2).float()).to(stored_derivative.dtype)
     else:
         z = pre_act.float() if (name in FP32_ACTS or derivative_in_fp32) else pre_act
-        dz = (dy * act_grad(name, z, param)).to(pre_act.dtype)
+        grad = act_grad(name, z, param)
+        if derivative_rounded:
+            grad = grad.to(pre_act.dtype).float()
+        dz = (dy * grad).to(pre_act.dtype)
 
     def mm(a: Tensor, b: Tensor) -> Tensor:
         a, b = a.to(out_dtype), b.to(out_dtype)

@@ -53,6 +53,8 @@ def test_header_constants_match_python():
     assert int(defines['AB200_FLAG_NO_STREAMK']) == _lib.FLAG_NO_STREAMK
     assert int(defines['AB200_FLAG_NO_PAIR']) == _lib.FLAG_NO_PAIR
     assert int(defines['AB200_FLAG_NO_TMA_STORE']) == _lib.FLAG_NO_TMA_STORE
+    assert int(defines['AB200_FLAG_SAVE_DERIVATIVE']) == _lib.FLAG_SAVE_DERIVATIVE
+    assert int(defines['AB200_ACT_SAVED_DERIVATIVE']) == _lib.ACT_SAVED_DERIVATIVE
 
 
 def test_version_and_error_strings(lib):

@@ -50,6 +50,8 @@ def make_layer(w, b, act_func, dtype):
 
 
 LAST_PATH = {'path': None}
+SAVE_DERIVATIVE = {'on': True}      # the layer's default: forward saves act'(Z)
+SAVED = {'tensor': None}
 
 
 def run_layer(x, w, b, act_func, dy, autocast_dtype=None, flags=0, param_dtype=None):
@@ -66,6 +68,8 @@ def run_layer(x, w, b, act_func, dy, autocast_dtype=None, flags=0, param_dtype=N
                             enabled=autocast_dtype is not None):
             y = layer(xg)
             LAST_PATH['path'] = _lib.load().ab200_last_path()
+            # What forward kept for backward: Z, or act'(Z) in the default save-derivative mode.
+            SAVED['tensor'] = y.grad_fn.saved_tensors[1].cpu() if act_func is not None else None
             z = None
             if act_func is not None:
                 with torch.no_grad():
@@ -87,13 +91,23 @@ def expected_from_oracle(x, w, b, act_func, dy, z_gpu, autocast_dtype=None):
     if z_gpu is not None:
         assert_close(z_gpu.view_as(z), z, TOL, 'pre-activation')
         z = z_gpu.view_as(z)
+    name, param = oracle.parse_act_func(act_func)
+    stored = None
+    if name is not None and SAVE_DERIVATIVE['on']:
+        # The saved derivative against the oracle's act'(stored Z), then backward through it: two
+        # correct evaluations can round act'(Z) to neighbouring 16-bit values, and backward reads
+        # the stored one.
+        stored = SAVED['tensor'].view_as(z)
+        assert_close(stored, oracle.act_grad(name, z.float(), param).to(out_dtype), TOL, 'saved derivative')
     dx, dw, db = oracle.linear_backward(dy.to(out_dtype), x, z, w, act_func, out_dtype, b, tf32=tf32,
-                                        derivative_in_fp32=True, round_to_out_dtype=False)
+                                        derivative_in_fp32=True, round_to_out_dtype=False,
+                                        stored_derivative=stored)
     if b is not None:
         # db: fp32 sum of the stored dZ, rounded once to the bias dtype.
-        name, param = oracle.parse_act_func(act_func)
         dz = dy.to(out_dtype).flatten(0, -2)
-        if name is not None:
+        if stored is not None:
+            dz = (dz.float() * stored.float()).to(out_dtype)
+        elif name is not None:
             dz = (dz * oracle.act_grad(name, z.float(), param)).to(out_dtype)
         db = dz.float().sum(0).to(b.dtype)
     return y, dx, dw, db
@@ -218,9 +232,17 @@ def test_oracle_parity(family, flags, dtype, shape, out_dim, act_func):
 
 @pytest.mark.parametrize('act_func', oracle.ALL_ACT_FUNCS)
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
-def test_every_activation(act_func, dtype):
+@pytest.mark.parametrize('save_derivative', [True, False])
+def test_every_activation(act_func, dtype, save_derivative):
+    """Every activation, with forward saving act'(Z) (default) and saving Z as the reference does."""
     x, w, b, dy = seeded((200, 192), 320, dtype, seed=3)
-    check_layer(x, w, b, act_func, dy)
+    previous = attorch_b200.set_save_derivative(save_derivative)
+    SAVE_DERIVATIVE['on'] = save_derivative
+    try:
+        check_layer(x, w, b, act_func, dy)
+    finally:
+        attorch_b200.set_save_derivative(previous)
+        SAVE_DERIVATIVE['on'] = True
 
 
 @pytest.mark.parametrize('autocast_dtype', [torch.float16, torch.bfloat16])
@@ -347,12 +369,13 @@ def test_config2_full_size_bf16():
     e_y, e_z = oracle.linear_forward(x[rows], w, b, 'gelu')
     assert_close(y[rows], e_y, TOL, 'output rows')
     assert_close(z[rows], e_z, TOL, 'pre-activation rows')
-    e_dx, _, _ = oracle.linear_backward(dy[rows], x[rows], z[rows], w, 'gelu', torch.bfloat16, b)
+    e_dx, _, _ = oracle.linear_backward(dy[rows], x[rows], z[rows], w, 'gelu', torch.bfloat16, b,
+                                        derivative_rounded=True)
     assert_close(dx[rows], e_dx, TOL, 'dX rows')
     # dW and db sum over all 8192 rows.  With dZ from the oracle's activation backward on the full
     # stored pre-activation (elementwise, cheap), 48 sampled input features of dW and all of db are
     # checked with float64 products.
-    dz = (dy.float() * oracle.act_grad('gelu', z.float())).bfloat16()
+    dz = (dy.float() * oracle.act_grad('gelu', z.float()).bfloat16().float()).bfloat16()
     feats = torch.randperm(K)[:48]
     e_dw = (x[:, feats].double().T @ dz.double()).float().bfloat16()
     assert_close(dw[feats], e_dw, TOL, 'dW rows')
