@@ -3,6 +3,8 @@
 #include "gemm_launch.cuh"
 
 #include <atomic>
+#include <cstdio>
+#include <cstdlib>
 
 namespace ab200 {
 namespace {
@@ -30,6 +32,15 @@ int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uin
               uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32, bool swizzle64) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return ERR_DRIVER;
+  // The encoder is a driver-API call and needs the device's primary context current on this host
+  // thread.  A thread that has only ever made runtime calls that do not touch the device (an
+  // autograd worker before its first launch, say) has none yet; cudaFree(0) binds it.
+  static thread_local int bound_device = -1;
+  int dev = -1;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev != bound_device) {
+    cudaFree(nullptr);
+    bound_device = dev;
+  }
   const CUtensorMapDataType dt = dtype == DT_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                  : dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                    : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -42,6 +53,11 @@ int encode_2d(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uin
                         swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B
                                   : (atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B),
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS && std::getenv("AB200_DEBUG") != nullptr)
+    std::fprintf(stderr, "ab200: cuTensorMapEncodeTiled error %d: base %p dims {%llu, %llu} pitch %llu box {%u, %u} "
+                 "dtype %d atom32 %d swizzle64 %d\n", static_cast<int>(r), base,
+                 static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
+                 static_cast<unsigned long long>(pitch_bytes), box_inner, box_outer, dtype, atom32, swizzle64);
   return r == CUDA_SUCCESS ? OK : ERR_TENSOR_MAP;
 }
 
