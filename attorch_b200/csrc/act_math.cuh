@@ -42,7 +42,18 @@ enum Act : int {
 
 namespace actm {
 
-__device__ __forceinline__ float sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+// Single-instruction approximations (MUFU): 2^x and 1/x to about 2 ulp and 1 ulp.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float sigmoid(float x) { return rcp_approx(1.0f + ex2_approx(-1.44269504f * x)); }
 // tanh as 2*sigmoid(2x) - 1 (act_kernels.py:71-81).
 __device__ __forceinline__ float tanh_(float x) { return 2.0f * sigmoid(2.0f * x) - 1.0f; }
 // erf(x) by Abramowitz & Stegun 7.1.26: 1 - (a1 t + ... + a5 t^5) exp(-x^2), t = 1 / (1 + p |x|);
@@ -51,12 +62,12 @@ __device__ __forceinline__ float tanh_(float x) { return 2.0f * sigmoid(2.0f * x
 // instruction count of the activation is what decides whether it hides behind the main loop.
 __device__ __forceinline__ float erf_fast(float x) {
   const float ax = fabsf(x);
-  const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.0f));
+  const float t = rcp_approx(fmaf(0.3275911f, ax, 1.0f));
   float poly = fmaf(1.061405429f, t, -1.453152027f);
   poly = fmaf(poly, t, 1.421413741f);
   poly = fmaf(poly, t, -0.284496736f);
   poly = fmaf(poly, t, 0.254829592f);
-  const float r = 1.0f - poly * t * exp2f(-1.44269504f * ax * ax);
+  const float r = 1.0f - poly * t * ex2_approx(-1.44269504f * ax * ax);
   return copysignf(r, x);
 }
 // log(1 + e^x) without overflow.
@@ -116,8 +127,8 @@ __device__ __forceinline__ float grad(float x, float p) {
   if constexpr (A == ACT_RELU) return x <= 0.0f ? 0.0f : 1.0f;
   if constexpr (A == ACT_GELU) {
     // Phi(x) + x * phi(x).  erf(x / sqrt 2) and phi(x) need the same exponential, exp(-x^2 / 2).
-    const float e = exp2f(-0.72134752f * x * x);               // exp(-x^2 / 2)
-    const float t = __frcp_rn(fmaf(0.3275911f * kRsqrt2, fabsf(x), 1.0f));
+    const float e = ex2_approx(-0.72134752f * x * x);               // exp(-x^2 / 2)
+    const float t = rcp_approx(fmaf(0.3275911f * kRsqrt2, fabsf(x), 1.0f));
     float poly = fmaf(1.061405429f, t, -1.453152027f);
     poly = fmaf(poly, t, 1.421413741f);
     poly = fmaf(poly, t, -0.284496736f);
@@ -170,8 +181,8 @@ __device__ __forceinline__ float grad(float x, float p) {
 template <int A>
 __device__ __forceinline__ void fwd_grad(float v, float zr, float p, float& y, float& g) {
   if constexpr (A == ACT_GELU) {
-    const float e = exp2f(-0.72134752f * v * v);               // exp(-v^2 / 2)
-    const float t = __frcp_rn(fmaf(0.3275911f * kRsqrt2, fabsf(v), 1.0f));
+    const float e = ex2_approx(-0.72134752f * v * v);               // exp(-v^2 / 2)
+    const float t = rcp_approx(fmaf(0.3275911f * kRsqrt2, fabsf(v), 1.0f));
     float poly = fmaf(1.061405429f, t, -1.453152027f);
     poly = fmaf(poly, t, 1.421413741f);
     poly = fmaf(poly, t, -0.284496736f);

@@ -218,8 +218,10 @@ __device__ __forceinline__ void stage_row_chunk(uint32_t buf, int lane, int dt, 
 
 // v[i] += bias[col0 + i] for the valid columns of a 32-column chunk (same addresses in every lane:
 // the loads are warp-wide broadcasts, 16 bytes at a time when the chunk is whole and aligned).
+// A bias wider than the output type is first rounded to it (round_dt), as the reference does when
+// the output is 16-bit (attorch/linear_kernels.py:171-172).
 __device__ __forceinline__ void add_bias_chunk(float (&v)[32], const void* bias, int dt, int col0,
-                                               int valid) {
+                                               int valid, int round_dt) {
   const int elt = dt == DT_F32 ? 4 : 2;
   const char* p = static_cast<const char*>(bias) + static_cast<long long>(col0) * elt;
   if (valid == 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
@@ -227,7 +229,10 @@ __device__ __forceinline__ void add_bias_chunk(float (&v)[32], const void* bias,
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float4 b = __ldg(reinterpret_cast<const float4*>(p) + i);
-        v[4 * i] += b.x; v[4 * i + 1] += b.y; v[4 * i + 2] += b.z; v[4 * i + 3] += b.w;
+        v[4 * i] += round_through(b.x, round_dt);
+        v[4 * i + 1] += round_through(b.y, round_dt);
+        v[4 * i + 2] += round_through(b.z, round_dt);
+        v[4 * i + 3] += round_through(b.w, round_dt);
       }
     } else {
 #pragma unroll
@@ -252,7 +257,7 @@ __device__ __forceinline__ void add_bias_chunk(float (&v)[32], const void* bias,
   } else {
 #pragma unroll
     for (int i = 0; i < 32; ++i)
-      if (i < valid) v[i] += load_as_f32(bias, dt, col0 + i);
+      if (i < valid) v[i] += round_through(load_as_f32(bias, dt, col0 + i), round_dt);
   }
 }
 
@@ -474,7 +479,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
         } else {
-          if (args.bias != nullptr) add_bias_chunk(v, args.bias, args.bias_dtype, col0, valid);
+          if (args.bias != nullptr) add_bias_chunk(v, args.bias, args.bias_dtype, col0, valid, args.out_dtype);
           const int row0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32;   // chunk's first row
           // Writes one 32 x 32 chunk of an output: through the warp's staging buffer and a TMA
           // store, or straight from registers where TMA cannot address the output.

@@ -165,7 +165,7 @@ __global__ void streamk_finish_kernel(float* __restrict__ partial, long long ld_
     float* pp = partial + m * ld_partial + n;
     float v[1] = {*pp};
     *pp = 0.0f;
-    if (bias != nullptr) v[0] += load_as_f32(bias, bias_dtype, n);
+    if (bias != nullptr) v[0] += round_through(load_as_f32(bias, bias_dtype, n), out_dtype);
     if (aux != nullptr && save_grad) {
       float zr[1] = {round_through(v[0], out_dtype)}, g[1];
       act_fwd_grad(v, zr, g, act, act_param);
@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(256) gemm_any_kernel(const AnyGemmArgs g) {
       const int n = n0 + tx * 4 + j;
       if (n >= g.N) continue;
       float v[1] = {acc[i][j]};
-      if (g.bias != nullptr) v[0] += load_as_f32(g.bias, g.bias_dtype, n);
+      if (g.bias != nullptr) v[0] += round_through(load_as_f32(g.bias, g.bias_dtype, n), g.out_dtype);
       if (g.aux != nullptr && g.save_grad) {
         float zr[1] = {round_through(v[0], g.out_dtype)}, d[1];
         act_fwd_grad(v, zr, d, g.act, g.act_param);

@@ -185,11 +185,9 @@ class LinearAutoGrad(torch.autograd.Function):
             scratch = _stream_scratch(input.device)
             x_op = _as_operand(flattened_input, op_dtype, stream)
             w_op = _as_operand(weight, op_dtype, stream)
-            # With a 16-bit output the reference rounds the bias to that dtype before adding it
-            # to the fp32 accumulator (attorch/linear_kernels.py:171-172).
+            # With a 16-bit output the reference rounds the bias to that dtype before adding it to
+            # the fp32 accumulator (attorch/linear_kernels.py:171-172); the kernels do that themselves.
             bias_op = bias
-            if bias is not None and bias.dtype is not op_dtype and op_dtype is not torch.float32:
-                bias_op = _as_operand(bias.view(1, -1), op_dtype, stream).view(-1)
             if bias_op is not None and not bias_op.is_contiguous():
                 bias_op = bias_op.contiguous()
 

@@ -157,10 +157,10 @@ def kernel_launcher(spec, tokens, device, lib, which='fwd'):
     """
     Returns (launch, work, unit): `launch()` enqueues one kernel of the workload's first layer through
     the C ABI exactly as the layer launches it, on the current stream.  `which`:
-      fwd      forward tcgen05 GEMM, X[M, K] * W[K, N] with bias, activation, pre-activation store
+      fwd      forward tcgen05 GEMM, X[M, K] * W[K, N] with bias, activation, saved act'(Z)
       dx       backward tcgen05 GEMM dX = dZ * W^T
       dw       backward tcgen05 GEMM dW = X^T * dZ
-      act_bwd  dZ = dY * act'(Z) with the bias-gradient column sums
+      act_bwd  dZ = dY * saved act'(Z) with the bias-gradient column sums
     `work` is the algorithmic work of one launch: floating-point operations for the GEMMs, bytes
     (dY and Z read, dZ written) for act_bwd.
     """
@@ -187,13 +187,16 @@ def kernel_launcher(spec, tokens, device, lib, which='fwd'):
     stream = torch.cuda.current_stream().cuda_stream
     keep = (xo, wo, bo, yo, zo, dyo, dzo, dxo, dwo, dbo, ws, status)
     flags = _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK
+    # As the layer does by default: forward saves act'(Z), backward multiplies by it.
+    fwd_flags = flags | (_lib.FLAG_SAVE_DERIVATIVE if name is not None else 0)
+    bwd_act = _lib.ACT_SAVED_DERIVATIVE if name is not None else 0
     gemm_flops = 2.0 * tokens * k0 * n0
 
     def fwd():
         _lib.check(lib.ab200_linear_forward(
             xo.data_ptr(), wo.data_ptr(), bo.data_ptr(), zo.data_ptr(), yo.data_ptr(), tokens, k0, n0,
             k0, 1, n0, 1, n0, n0, dt_id, dt_id, dt_id, act_id(name), param or 0.0, None, 0,
-            status.data_ptr(), stream, flags), 'ab200_linear_forward')
+            status.data_ptr(), stream, fwd_flags), 'ab200_linear_forward')
         return keep
 
     def dx():
@@ -211,7 +214,7 @@ def kernel_launcher(spec, tokens, device, lib, which='fwd'):
     def act_bwd():
         _lib.check(lib.ab200_act_backward(
             dyo.data_ptr(), zo.data_ptr(), dzo.data_ptr(), dbo.data_ptr(), tokens, n0, n0, n0, n0, dt_id,
-            ids[dbo.dtype], act_id(name), param or 0.0, ws.data_ptr(), ws.numel(), stream),
+            ids[dbo.dtype], bwd_act, param or 0.0, ws.data_ptr(), ws.numel(), stream),
             'ab200_act_backward')
         return keep
 
@@ -489,7 +492,7 @@ def main():
     achieved = 2.0 * tokens * k0 * n0 / (kernel_ms * 1e-3) / 1e12
     roofline = {'bound': 'tensor', 'achieved': achieved, 'peak': peaks['bf16_tflops'], 'unit': 'TFLOP/s',
                 'frac': achieved / peaks['bf16_tflops'], 'traffic': NCU_DRAM_BYTES_PER_LAUNCH,
-                'kernel': 'gemm_tcgen05_kernel (forward, bias + gelu + pre-activation epilogue)',
+                'kernel': 'gemm_tcgen05_kernel (forward: bias + gelu + saved-derivative epilogue)',
                 'kernel_ms': kernel_ms, 'peak_source': f'{peak_source} (cuBLAS bf16 burst)',
                 'frac_of_nominal_2250': achieved / 2250.0}
 

@@ -122,7 +122,8 @@ int64_t ab200_launch_count(void);
  * attorch/linear_layer.py:88-98.
  *   x        [M, K], element strides (x_stride_m, x_stride_k), type op_dtype
  *   w        [K, N], element strides (w_stride_k, w_stride_n), type op_dtype
- *   bias     [N] of bias_dtype, or NULL
+ *   bias     [N] of bias_dtype, or NULL; rounded to out_dtype before it is added when out_dtype is
+ *            16-bit (attorch/linear_kernels.py:171-172)
  *   pre_act  [M, N] of out_dtype, row pitch ld_pre, or NULL: the value before the activation,
  *            rounded to out_dtype (what backward differentiates through).  With
  *            AB200_FLAG_SAVE_DERIVATIVE it receives act'(Z) instead (piecewise derivatives taken at
