@@ -46,9 +46,11 @@ class GradientBuckets:
         comm_sms: SMs left free for the collective while it overlaps the remaining GEMMs of
             backward: the persistent GEMM kernels would otherwise hold every SM and the all-reduce
             would only start once they end.
+        dw_chunks: Each layer's dW is computed and exchanged in this many blocks of rows, which
+            widens the window the exchange can hide in from "dX" to "the rest of dW, then dX".
     """
     def __init__(self, layers: Iterable[Linear], process_group=None, overlap: bool = True,
-                 comm_sms: int = 16) -> None:
+                 comm_sms: int = 16, dw_chunks: int = 2) -> None:
         self.layers: List[Linear] = list(layers)
         self.group = process_group
         self.world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -80,19 +82,28 @@ class GradientBuckets:
                 offset += n
             self.slices.append(self.flat[begin:offset])
             layer.grad_ready = self._make_callback(index)
+            layer.dw_chunks = dw_chunks if self.overlap else 1
 
     def _make_callback(self, index: int):
-        def grad_ready() -> None:
-            if self.overlap:
-                self._reduce_async(index)
+        def grad_ready(block: int = 0, blocks: int = 1) -> None:
+            if not self.overlap:
+                return
+            # Block i of n covers rows [i K / n, (i + 1) K / n) of dW, contiguous in the bucket; the
+            # bias gradient, which follows dW in the bucket, travels with the last block.
+            layer = self.layers[index]
+            whole = self.slices[index]
+            per_block = layer.weight.numel() // blocks
+            begin = block * per_block
+            end = (block + 1) * per_block if block + 1 < blocks else whole.numel()
+            self._reduce_async(whole[begin:end])
         return grad_ready
 
-    def _reduce_async(self, index: int) -> None:
+    def _reduce_async(self, piece: Tensor) -> None:
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ready)
-            dist.all_reduce(self.slices[index], op=dist.ReduceOp.SUM, group=self.group)
+            dist.all_reduce(piece, op=dist.ReduceOp.SUM, group=self.group)
             done = torch.cuda.Event()
             done.record(self.comm_stream)
         self._pending.append(done)

@@ -147,14 +147,15 @@ class LinearAutoGrad(torch.autograd.Function):
     Autodiff for the fused linear layer; same call contract as the reference's
     ``LinearAutoGrad`` (attorch/linear_layer.py:19-161): ``apply(input, weight, bias, act_func)``.
     Three optional trailing arguments serve data-parallel training: the buffers ``dW`` and ``db``
-    are written into (e.g. views of a flat all-reduce bucket), and a callable that backward invokes
-    once the kernels producing ``dW`` and ``db`` are enqueued and before ``dX`` is, so that the
-    gradient exchange of this layer can overlap the remaining work.
+    are written into (e.g. views of a flat all-reduce bucket), and a callable ``grad_ready(i, n)``
+    that backward invokes each time block ``i`` of ``n`` row blocks of ``dW`` is enqueued (``db`` is
+    complete before block 0), before ``dX`` is, so that the gradient exchange of this layer can
+    overlap the remaining work; ``dw_chunks`` is ``n``.
     """
     @staticmethod
     def forward(ctx, input: Tensor, weight: Tensor, bias: Optional[Tensor] = None,
                 act_func: Optional[str] = None, weight_grad_out: Optional[Tensor] = None,
-                bias_grad_out: Optional[Tensor] = None, grad_ready=None) -> Tensor:
+                bias_grad_out: Optional[Tensor] = None, grad_ready=None, dw_chunks: int = 1) -> Tensor:
         assert weight.ndim == 2, \
             f'Weights must be 2D, received shape {weight.shape}'
         assert bias is None or bias.ndim == 1, \
@@ -222,6 +223,7 @@ class LinearAutoGrad(torch.autograd.Function):
         ctx.weight_shape = weight.shape
         ctx.has_grad_out = (weight_grad_out is not None, bias_grad_out is not None)
         ctx.grad_ready = grad_ready
+        ctx.dw_chunks = int(dw_chunks)
         ctx.saved_derivative = requires_grad and name is not None and _save_derivative
         if requires_grad:
             # Backward multiplies in the output dtype, so the converted operands are what it
@@ -287,17 +289,28 @@ class LinearAutoGrad(torch.autograd.Function):
             if ctx.weight_requires_grad:
                 weight_grad = (weight_grad_out if weight_grad_out is not None else
                                torch.empty(ctx.weight_shape, dtype=ctx.weight_dtype, device=device))
-                ws_bytes = lib.ab200_gemm_workspace_bytes(in_feat_dim, out_feat_dim, batch_dim)
+                # dW is computed in `chunks` blocks of rows (= input features).  With a gradient
+                # exchange attached, block i is handed to it as soon as it is enqueued, so that the
+                # exchange of block i overlaps the computation of block i + 1 and of dX.
+                chunks = ctx.dw_chunks if (ctx.grad_ready is not None and ctx.dw_chunks > 1 and
+                                           in_feat_dim % (ctx.dw_chunks * 8) == 0) else 1
+                rows = in_feat_dim // chunks
+                ws_bytes = lib.ab200_gemm_workspace_bytes(rows, out_feat_dim, batch_dim)
                 workspace = _workspace(device, ws_bytes) if ws_bytes else None
-                _lib.check(lib.ab200_linear_backward_weight(
-                    _ptr(x_op), _ptr(pre_act_grad), _ptr(weight_grad),
-                    batch_dim, in_feat_dim, out_feat_dim,
-                    x_op.stride(0), x_op.stride(1), pre_act_grad.stride(0), pre_act_grad.stride(1),
-                    weight_grad.stride(0), _dtype_id(op_dtype), _dtype_id(weight_grad.dtype),
-                    _ptr(workspace), ws_bytes, status, stream, _gemm_flags),
-                    'ab200_linear_backward_weight')
-            if ctx.grad_ready is not None:
-                ctx.grad_ready()
+                for c in range(chunks):
+                    x_part = x_op[:, c * rows:(c + 1) * rows]
+                    dw_part = weight_grad[c * rows:(c + 1) * rows]
+                    _lib.check(lib.ab200_linear_backward_weight(
+                        _ptr(x_part), _ptr(pre_act_grad), _ptr(dw_part),
+                        batch_dim, rows, out_feat_dim,
+                        x_part.stride(0), x_part.stride(1), pre_act_grad.stride(0), pre_act_grad.stride(1),
+                        dw_part.stride(0), _dtype_id(op_dtype), _dtype_id(weight_grad.dtype),
+                        _ptr(workspace), ws_bytes, status, stream, _gemm_flags),
+                        'ab200_linear_backward_weight')
+                    if ctx.grad_ready is not None:
+                        ctx.grad_ready(c, chunks)
+            elif ctx.grad_ready is not None:
+                ctx.grad_ready(0, 1)
             if ctx.input_requires_grad:
                 input_grad = torch.empty((batch_dim, in_feat_dim), dtype=ctx.input_dtype, device=device)
                 ws_bytes = lib.ab200_gemm_workspace_bytes(batch_dim, in_feat_dim, out_feat_dim)
@@ -312,7 +325,7 @@ class LinearAutoGrad(torch.autograd.Function):
                 input_grad = input_grad.view(ctx.input_shape)
 
         # One slot per forward argument (attorch/linear_layer.py:158-161 pads with None).
-        return input_grad, weight_grad, bias_grad, None, None, None, None
+        return input_grad, weight_grad, bias_grad, None, None, None, None, None
 
 
 class Linear(nn.Linear):
@@ -345,9 +358,11 @@ class Linear(nn.Linear):
         # Optional (dW, db) destination buffers, e.g. views into a gradient bucket.
         self.weight_grad_out: Optional[Tensor] = None
         self.bias_grad_out: Optional[Tensor] = None
-        # Optional callable run in backward once dW and db are enqueued (see LinearAutoGrad).
+        # Optional callable run in backward as blocks of dW are enqueued (see LinearAutoGrad).
         self.grad_ready = None
+        self.dw_chunks = 1
 
     def forward(self, input: Tensor) -> Tensor:
         return LinearAutoGrad.apply(input, self.weight, self.bias, self.act_func,
-                                    self.weight_grad_out, self.bias_grad_out, self.grad_ready)
+                                    self.weight_grad_out, self.bias_grad_out, self.grad_ready,
+                                    self.dw_chunks)

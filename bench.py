@@ -40,8 +40,8 @@ sys.path.insert(0, str(ROOT))
 PEAK_FALLBACK = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0}
 
 # DRAM bytes per launch of the dominant kernel (forward GEMM of c2) from the ncu capture summarised
-# in profiles/; None until a capture exists.
-NCU_DRAM_BYTES_PER_LAUNCH = None
+# in profiles/c2_kernel_fwd.md (algorithmic bytes: 224 MiB = 234.9e6).
+NCU_DRAM_BYTES_PER_LAUNCH = 286.3e6   # profiles/c2_kernel_fwd.md: 184.1 MB read + 102.2 MB written
 
 WORKLOADS = {
     'c2': dict(layers=[(4096, 4096, 'gelu', True)], tokens_per_gpu=8192, global_tokens=None,
@@ -336,7 +336,9 @@ def main():
     layers = [attorch_b200.Linear(k, n, bias=bias, act_func=act, device=device,
                                   dtype=spec['param_dtype'])
               for (k, n, act, bias) in spec['layers']]
-    buckets = GradientBuckets(layers, comm_sms=int(os.environ.get('AB200_COMM_SMS', '16')))
+    buckets = GradientBuckets(layers, comm_sms=int(os.environ.get('AB200_COMM_SMS', '16')),
+                              overlap=os.environ.get('AB200_DP_OVERLAP', '1') != '0',
+                              dw_chunks=int(os.environ.get('AB200_DW_CHUNKS', '2')))
     k_in, n_out = spec['layers'][0][0], spec['layers'][-1][1]
     gen = torch.Generator(device=device).manual_seed(1 + rank)
     x_dev = torch.randn(tokens, k_in, device=device, generator=gen).to(spec['input_dtype'])

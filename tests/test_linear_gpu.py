@@ -402,3 +402,21 @@ def test_config4_skinny_fp16(m):
     assert _lib.load().ab200_last_path() == _lib.PATH_STREAMK
     e_y, _ = oracle.linear_forward(x, w, None, None)
     assert_close(y.cpu(), e_y, TOL, 'output')
+
+
+def test_weight_gradient_in_row_blocks():
+    """dW computed in four row blocks (as the data-parallel harness asks for) equals dW in one piece."""
+    x, w, b, dy = seeded((512, 1024), 768, torch.bfloat16, seed=13)
+    calls = []
+    results = []
+    for chunks in (1, 4):
+        layer = make_layer(w, b, 'gelu', torch.bfloat16)
+        layer.grad_ready = lambda i, n: calls.append((i, n))
+        layer.dw_chunks = chunks
+        xg = x.to(DEV).requires_grad_(True)
+        layer(xg).backward(dy.to(DEV))
+        attorch_b200.check_status()
+        results.append((layer.weight.grad.cpu(), layer.bias.grad.cpu(), xg.grad.cpu()))
+    assert calls == [(0, 1), (0, 4), (1, 4), (2, 4), (3, 4)]
+    for a, c in zip(*results):
+        assert torch.equal(a, c)
