@@ -21,6 +21,9 @@ struct TcProblem {
   int op_dtype;
   bool allow_pair;   // may run as CTA pairs (cta_group::2) where a configuration for it exists
   bool allow_tma_store;   // the epilogue may write its outputs with TMA stores
+  // Optional scratch for sharing out a partial last round of tiles (hybrid scheduling).
+  void* tail_workspace;
+  long long tail_workspace_bytes;
   GemmArgs g;
 };
 
@@ -31,6 +34,10 @@ int sm_count();
 // SM leaves none for a collective running beside it; a caller that overlaps the two lowers this.
 int gemm_cta_limit();
 void set_gemm_cta_limit(int ctas);
+
+// Finishing pass of the hybrid schedule (defined next to the kernel, in api.cu): shared-out tiles
+// [first_tile, first_tile + count) of the launch described by g, tile_m x bn each.
+int launch_hybrid_finish(const GemmArgs& g, int first_tile, int count, int tile_m, int bn, cudaStream_t stream);
 
 // Launches p with a BN-wide tile on the kernel family given by p.a_mn / p.b_mn / p.op_dtype.
 int launch_tc(const TcProblem& p, int bn, cudaStream_t stream);
@@ -129,6 +136,21 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   const int workers = static_cast<int>(work < cap ? work : cap);
   if (workers <= 0) return OK;
 
+  // Hybrid schedule: when the last round of whole tiles would be mostly idle (at most 80 % of the
+  // workers busy), its tiles' reductions are shared out over all workers instead.
+  int tail_tiles = 0;
+  if (!g.stream_k && p.tail_workspace != nullptr && tiles > workers && g.k_blocks >= 16) {
+    const int rem = static_cast<int>(tiles % workers);
+    const long long need = static_cast<long long>(rem) * Cfg::TILE_M * Cfg::BN * 4;
+    if (rem > 0 && rem * 10 <= workers * 8 && need <= p.tail_workspace_bytes) {
+      if (cudaMemsetAsync(p.tail_workspace, 0, need, stream) != cudaSuccess) return ERR_LAUNCH;
+      tail_tiles = rem;
+      g.stream_k = 2;
+      g.dp_tiles = static_cast<int>(tiles) - rem;
+      g.partial = static_cast<float*>(p.tail_workspace);
+    }
+  }
+
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(workers * Cfg::CTAS);
   cfg.blockDim = dim3(Cfg::kThreads);
@@ -144,7 +166,9 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
     cfg.numAttrs = 1;
   }
   const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<Cfg>, ta, tb, tout, taux, g);
-  return err == cudaSuccess ? OK : ERR_LAUNCH;
+  if (err != cudaSuccess) return ERR_LAUNCH;
+  if (tail_tiles > 0) return launch_hybrid_finish(g, g.dp_tiles, tail_tiles, Cfg::TILE_M, Cfg::BN, stream);
+  return OK;
 }
 
 // All tile widths of one (element size, majorness) family.  A 32-wide tile is narrower than one

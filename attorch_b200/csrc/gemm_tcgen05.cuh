@@ -48,7 +48,8 @@ struct GemmArgs {
   int tiles_m, tiles_n;   // ceil(M / 128), ceil(N / BN)
   int group_m;            // row-blocks per rasterisation group
   int k_blocks;           // ceil(K / elements per stage)
-  int stream_k;           // 0: one CTA per whole tile; 1: equal (tile, k-block) ranges + atomics
+  int stream_k;           // 0: whole tiles; 1: equal (tile, k-block) shares + atomics; 2: hybrid
+  int dp_tiles;           // hybrid: tiles computed whole (a multiple of the worker count)
   uint32_t idesc;         // tcgen05 instruction descriptor (operand format, majorness, 128 x BN)
   // Direct epilogue
   void* out;              // [M, N], row pitch ld_out elements
@@ -61,7 +62,8 @@ struct GemmArgs {
   int act;
   float act_param;
   // Stream-K epilogue
-  float* partial;         // fp32, zero on entry; [M, N] (pitch ld_partial) or, if transposed, [N, M]
+  float* partial;         // fp32, zero on entry; mode 1: [M, N] (pitch ld_partial) or, if transposed,
+                          // [N, M]; mode 2: one dense TILE_M x BN block per shared-out tile
   long long ld_partial;
   int partial_transposed;
   int* status;            // device word; a bounded wait that runs out stores a DeviceStatus here
@@ -111,52 +113,66 @@ struct GemmCfg {
 struct Segment {
   int m_blk, n_blk;
   int kb0, kb1;     // k-block range [kb0, kb1)
+  int partial;      // 1: add the result to the fp32 partial sums; 0: whole tile, fused epilogue
+  int sk_index;     // hybrid mode: index of the tile among the shared-out tiles
 };
 
-// Every role of a CTA walks the same sequence of segments, computed from blockIdx alone.
+// Tile index -> (row block, column block).  Grouped rasterisation: group_m row blocks at a time,
+// row-block index fastest.
+__host__ __device__ __forceinline__ void tile_to_blocks(int t, int tiles_m, int tiles_n, int group_m,
+                                                        int& m_blk, int& n_blk) {
+  const int per_group = group_m * tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * group_m;
+  const int gsz = (tiles_m - first_m < group_m) ? tiles_m - first_m : group_m;
+  const int r = t - g * per_group;
+  m_blk = first_m + r % gsz;
+  n_blk = r / gsz;
+}
+
+// Every role of a CTA walks the same sequence of segments, computed from its worker index alone.
+//   stream_k = 0  whole tiles: worker, worker + workers, ...
+//   stream_k = 1  all (tile, k-block) units in equal contiguous shares
+//   stream_k = 2  hybrid: the first dp_tiles tiles whole, as in mode 0 (dp_tiles is a multiple of
+//                 the worker count, so these are full rounds); the (tile, k-block) units of the
+//                 remaining tiles in equal shares, which spreads a partial last round over all SMs
 struct SegmentIter {
-  long long unit, unit_end;   // stream-K: position in (tile, k-block) units
-  int tile;                   // tile-parallel: next tile
+  long long unit, unit_end;   // position in the shared-out (tile, k-block) units
+  int tile, tile_end;         // next whole tile
   int stride;                 // number of workers (CTAs, or CTA pairs)
+  int first_shared;           // first tile whose units are shared out
   // worker / workers: index and count of the CTAs (or CTA pairs) that share the work.
   __device__ __forceinline__ SegmentIter(const GemmArgs& a, int worker, int workers) {
-    const long long tiles = static_cast<long long>(a.tiles_m) * a.tiles_n;
+    const int tiles = a.tiles_m * a.tiles_n;
     stride = workers;
-    if (a.stream_k) {
-      const long long total = tiles * a.k_blocks;
-      unit = total * worker / workers;
-      unit_end = total * (worker + 1) / workers;
-      tile = 0;
-    } else {
-      unit = 0;
-      unit_end = tiles;
-      tile = worker;
-    }
+    tile = worker;
+    tile_end = a.stream_k == 0 ? tiles : (a.stream_k == 2 ? a.dp_tiles : 0);
+    first_shared = a.stream_k == 0 ? tiles : (a.stream_k == 2 ? a.dp_tiles : 0);
+    const long long total = static_cast<long long>(tiles - first_shared) * a.k_blocks;
+    unit = total * worker / workers;
+    unit_end = total * (worker + 1) / workers;
   }
   __device__ __forceinline__ bool next(const GemmArgs& a, Segment& s) {
     int t;
-    if (a.stream_k) {
-      if (unit >= unit_end) return false;
-      t = static_cast<int>(unit / a.k_blocks);
-      s.kb0 = static_cast<int>(unit - static_cast<long long>(t) * a.k_blocks);
-      const long long left = unit_end - unit;
-      s.kb1 = (a.k_blocks - s.kb0 < left) ? a.k_blocks : s.kb0 + static_cast<int>(left);
-      unit += s.kb1 - s.kb0;
-    } else {
-      if (tile >= unit_end) return false;
+    if (tile < tile_end) {
       t = tile;
       tile += stride;
       s.kb0 = 0;
       s.kb1 = a.k_blocks;
+      s.partial = 0;
+      s.sk_index = 0;
+    } else {
+      if (unit >= unit_end) return false;
+      const int ts = static_cast<int>(unit / a.k_blocks);
+      t = first_shared + ts;
+      s.kb0 = static_cast<int>(unit - static_cast<long long>(ts) * a.k_blocks);
+      const long long left = unit_end - unit;
+      s.kb1 = (a.k_blocks - s.kb0 < left) ? a.k_blocks : s.kb0 + static_cast<int>(left);
+      unit += s.kb1 - s.kb0;
+      s.partial = 1;
+      s.sk_index = ts;
     }
-    // Grouped rasterisation: group_m row-blocks at a time, row-block index fastest.
-    const int per_group = a.group_m * a.tiles_n;
-    const int g = t / per_group;
-    const int first_m = g * a.group_m;
-    const int gsz = (a.tiles_m - first_m < a.group_m) ? a.tiles_m - first_m : a.group_m;
-    const int r = t - g * per_group;
-    s.m_blk = first_m + r % gsz;
-    s.n_blk = r / gsz;
+    tile_to_blocks(t, a.tiles_m, a.tiles_n, a.group_m, s.m_blk, s.n_blk);
     return true;
   }
 };
@@ -459,8 +475,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
         const int valid = (args.N - col0 < 32) ? args.N - col0 : 32;
-        if (args.stream_k) {
-          if (row_ok) {
+        if (seg.partial) {
+          if (args.stream_k == 2) {
+            // Tile-local, dense and 16-byte aligned: rows beyond M add zeros to padding.
+            float* p = args.partial + (static_cast<long long>(seg.sk_index) * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32 + lane) * BN + c * 32;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              ptx::red_add_v4_f32(p + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          } else if (row_ok) {
             if (args.partial_transposed) {
 #pragma unroll
               for (int i = 0; i < 32; ++i)

@@ -10,6 +10,7 @@
 #pragma once
 #include "act_math.cuh"
 #include "common.cuh"
+#include "gemm_tcgen05.cuh"
 
 namespace ab200 {
 
@@ -175,6 +176,46 @@ __global__ void streamk_finish_kernel(float* __restrict__ partial, long long ld_
       act_fwd_inplace(v, act, act_param);
     }
     store_from_f32(out, out_dtype, m * ld_out + n, v[0]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Finishing pass of the hybrid GEMM: the tiles whose reduction was shared out sit as dense
+// tile_m x bn fp32 blocks in `partial`; block b of the grid turns shared-out tile b into output
+// (same epilogue as everywhere) and clears it.
+// ------------------------------------------------------------------------------------------------
+struct HybridFinishArgs {
+  float* partial;
+  int first_tile, tiles_m, tiles_n, group_m, tile_m, bn;
+  int M, N;
+  const void* bias; int bias_dtype;
+  void* aux; long long ld_aux;
+  void* out; long long ld_out; int out_dtype;
+  int act; float act_param; int save_grad;
+};
+
+__global__ void __launch_bounds__(256) hybrid_finish_kernel(const HybridFinishArgs a) {
+  int m_blk, n_blk;
+  tile_to_blocks(a.first_tile + blockIdx.x, a.tiles_m, a.tiles_n, a.group_m, m_blk, n_blk);
+  float* tile = a.partial + static_cast<long long>(blockIdx.x) * a.tile_m * a.bn;
+  const int elems = a.tile_m * a.bn;
+  for (int i = threadIdx.x; i < elems; i += blockDim.x) {
+    const int r = i / a.bn, c = i - r * a.bn;
+    float v[1] = {tile[i]};
+    tile[i] = 0.0f;
+    const long long m = static_cast<long long>(m_blk) * a.tile_m + r;
+    const long long n = static_cast<long long>(n_blk) * a.bn + c;
+    if (m >= a.M || n >= a.N) continue;
+    if (a.bias != nullptr) v[0] += round_through(load_as_f32(a.bias, a.bias_dtype, n), a.out_dtype);
+    if (a.aux != nullptr && a.save_grad) {
+      float zr[1] = {round_through(v[0], a.out_dtype)}, g[1];
+      act_fwd_grad(v, zr, g, a.act, a.act_param);
+      store_from_f32(a.aux, a.out_dtype, m * a.ld_aux + n, g[0]);
+    } else {
+      if (a.aux != nullptr) store_from_f32(a.aux, a.out_dtype, m * a.ld_aux + n, v[0]);
+      act_fwd_inplace(v, a.act, a.act_param);
+    }
+    store_from_f32(a.out, a.out_dtype, m * a.ld_out + n, v[0]);
   }
 }
 

@@ -181,11 +181,14 @@ def kernel_launcher(spec, tokens, device, lib, which='fwd'):
     dwo = torch.empty(k0, n0, device=device, dtype=grad_dtype)
     dbo = torch.empty(n0, device=device, dtype=grad_dtype)
     ws = torch.empty(max(lib.ab200_act_backward_workspace_bytes(tokens, n0), 16), dtype=torch.uint8, device=device)
+    gws_bytes = max(lib.ab200_gemm_workspace_bytes(tokens, n0, k0), lib.ab200_gemm_workspace_bytes(k0, n0, tokens),
+                    lib.ab200_gemm_workspace_bytes(tokens, k0, n0), 16)
+    gws = torch.empty(gws_bytes, dtype=torch.uint8, device=device)
     status = torch.zeros(1, dtype=torch.int32, device=device)
     dt_id = ids[op_dtype]
     name, param = parse_act_func(act0)
     stream = torch.cuda.current_stream().cuda_stream
-    keep = (xo, wo, bo, yo, zo, dyo, dzo, dxo, dwo, dbo, ws, status)
+    keep = (xo, wo, bo, yo, zo, dyo, dzo, dxo, dwo, dbo, ws, gws, status)
     flags = _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK
     # As the layer does by default: forward saves act'(Z), backward multiplies by it.
     fwd_flags = flags | (_lib.FLAG_SAVE_DERIVATIVE if name is not None else 0)
@@ -195,20 +198,22 @@ def kernel_launcher(spec, tokens, device, lib, which='fwd'):
     def fwd():
         _lib.check(lib.ab200_linear_forward(
             xo.data_ptr(), wo.data_ptr(), bo.data_ptr(), zo.data_ptr(), yo.data_ptr(), tokens, k0, n0,
-            k0, 1, n0, 1, n0, n0, dt_id, dt_id, dt_id, act_id(name), param or 0.0, None, 0,
+            k0, 1, n0, 1, n0, n0, dt_id, dt_id, dt_id, act_id(name), param or 0.0, gws.data_ptr(), gws_bytes,
             status.data_ptr(), stream, fwd_flags), 'ab200_linear_forward')
         return keep
 
     def dx():
         _lib.check(lib.ab200_linear_backward_input(
             dzo.data_ptr(), wo.data_ptr(), dxo.data_ptr(), tokens, k0, n0, n0, 1, n0, 1, k0, dt_id,
-            ids[dxo.dtype], None, 0, status.data_ptr(), stream, flags), 'ab200_linear_backward_input')
+            ids[dxo.dtype], gws.data_ptr(), gws_bytes, status.data_ptr(), stream, flags),
+            'ab200_linear_backward_input')
         return keep
 
     def dw():
         _lib.check(lib.ab200_linear_backward_weight(
             xo.data_ptr(), dzo.data_ptr(), dwo.data_ptr(), tokens, k0, n0, k0, 1, n0, 1, n0, dt_id,
-            ids[dwo.dtype], None, 0, status.data_ptr(), stream, flags), 'ab200_linear_backward_weight')
+            ids[dwo.dtype], gws.data_ptr(), gws_bytes, status.data_ptr(), stream, flags),
+            'ab200_linear_backward_weight')
         return keep
 
     def act_bwd():

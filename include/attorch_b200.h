@@ -90,6 +90,7 @@ extern "C" {
 #define AB200_FLAG_NO_PAIR 16       /* one CTA per tile: no cta_group::2 kernels                */
 #define AB200_FLAG_NO_TMA_STORE 32  /* epilogue stores from registers, not through TMA           */
 #define AB200_FLAG_SAVE_DERIVATIVE 64 /* forward: pre_act receives act'(Z) instead of Z            */
+#define AB200_FLAG_DETERMINISTIC 128 /* no atomically summed tile tails: bit-repeatable results    */
 
 /* Which kernel the last call on this host thread chose: 1 tcgen05 tile-parallel, 2 tcgen05
  * swap-AB stream-K, 3 generic CUDA-core.  For tests and benchmarks. */
@@ -154,7 +155,9 @@ int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N, int flags
  * length (0 when it needs none).  Outputs too small to occupy half of the SMs with whole tiles,
  * e.g. the weight gradient of a narrow layer over a long batch, are computed as equal shares of the
  * reduction on all SMs, accumulated in fp32 in the workspace and rounded by a finishing kernel.
- * Without the workspace the call still succeeds, on whole tiles.
+ * Large outputs whose last round of tiles would leave most SMs idle (256 tiles on 74 CTA pairs,
+ * say) share out just that round the same way.  Without the workspace the call still succeeds, on
+ * whole tiles.
  */
 int64_t ab200_gemm_workspace_bytes(int64_t rows, int64_t cols, int64_t reduction);
 
