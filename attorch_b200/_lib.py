@@ -21,7 +21,7 @@ FLAG_NO_STREAMK = 8
 FLAG_NO_PAIR = 16
 FLAG_NO_TMA_STORE = 32
 FLAG_SAVE_DERIVATIVE = 64
-FLAG_DETERMINISTIC = 128
+FLAG_WHOLE_TILES = 128
 ACT_SAVED_DERIVATIVE = 22
 
 PATH_TCGEN05, PATH_STREAMK, PATH_GENERIC = 1, 2, 3

@@ -15,17 +15,20 @@
 
 namespace ab200 {
 
-int launch_hybrid_finish(const GemmArgs& g, int first_tile, int count, int tile_m, int bn, cudaStream_t stream) {
+int launch_hybrid_finish(const GemmArgs& g, int first_tile, int count, int workers, int tile_m, int bn,
+                         cudaStream_t stream) {
   HybridFinishArgs a{};
   a.partial = g.partial;
-  a.first_tile = first_tile; a.tiles_m = g.tiles_m; a.tiles_n = g.tiles_n; a.group_m = g.group_m;
+  a.first_tile = first_tile; a.tail_tiles = count; a.workers = workers; a.k_blocks = g.k_blocks;
+  a.tiles_m = g.tiles_m; a.tiles_n = g.tiles_n; a.group_m = g.group_m;
   a.tile_m = tile_m; a.bn = bn;
   a.M = g.M; a.N = g.N;
   a.bias = g.bias; a.bias_dtype = g.bias_dtype;
   a.aux = g.aux; a.ld_aux = g.ld_aux;
   a.out = g.out; a.ld_out = g.ld_out; a.out_dtype = g.out_dtype;
   a.act = g.act; a.act_param = g.act_param; a.save_grad = g.save_grad;
-  hybrid_finish_kernel<<<count, 256, 0, stream>>>(a);
+  // 16 blocks per tile: enough parallelism for a handful of tiles.
+  hybrid_finish_kernel<<<dim3(count, 16), 256, 0, stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
 }
 
@@ -128,9 +131,8 @@ int run_tiles_or_split(TcProblem& p, void* workspace, int64_t workspace_bytes, c
     return launch_finish(g.partial, g, g.M, g.N, stream);
   }
   g.stream_k = 0;
-  // Scratch for sharing out a mostly idle last round of tiles; results are then summed with
-  // atomics, whose order is not fixed, so a caller that needs bit-repeatable sums opts out.
-  if (!(flags & AB200_FLAG_DETERMINISTIC)) {
+  // Scratch for sharing out a mostly idle last round of tiles (summed in a fixed order).
+  if (!(flags & AB200_FLAG_WHOLE_TILES)) {
     p.tail_workspace = workspace;
     p.tail_workspace_bytes = workspace_bytes;
   }
@@ -190,7 +192,7 @@ int64_t ab200_gemm_workspace_bytes(int64_t rows, int64_t cols, int64_t reduction
   int64_t need = (want_split(rows, cols, reduction, 2) || want_split(rows, cols, reduction, 4)) ? rows * cols * 4 : 0;
   // Sharing out a partial last round of 256 x 256 (pair) or 128 x 256 tiles: fewer tiles than workers.
   const int64_t tiles = ((rows + 127) / 128) * ((cols + 255) / 256);
-  const int64_t tail = static_cast<int64_t>(sm_count()) * 128 * 256 * 4;
+  const int64_t tail = 2 * static_cast<int64_t>(sm_count()) * 128 * 256 * 4;   // two slots per worker
   if (tiles > sm_count() / 2 && reduction >= 1024 && tail > need) need = tail;
   return need;
 }

@@ -37,7 +37,8 @@ void set_gemm_cta_limit(int ctas);
 
 // Finishing pass of the hybrid schedule (defined next to the kernel, in api.cu): shared-out tiles
 // [first_tile, first_tile + count) of the launch described by g, tile_m x bn each.
-int launch_hybrid_finish(const GemmArgs& g, int first_tile, int count, int tile_m, int bn, cudaStream_t stream);
+int launch_hybrid_finish(const GemmArgs& g, int first_tile, int count, int workers, int tile_m, int bn,
+                         cudaStream_t stream);
 
 // Launches p with a BN-wide tile on the kernel family given by p.a_mn / p.b_mn / p.op_dtype.
 int launch_tc(const TcProblem& p, int bn, cudaStream_t stream);
@@ -139,11 +140,14 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   // Hybrid schedule: when the last round of whole tiles would be mostly idle (at most 80 % of the
   // workers busy), its tiles' reductions are shared out over all workers instead.
   int tail_tiles = 0;
+  CUtensorMap tpartial = ta;
   if (!g.stream_k && p.tail_workspace != nullptr && tiles > workers && g.k_blocks >= 16) {
     const int rem = static_cast<int>(tiles % workers);
-    const long long need = static_cast<long long>(rem) * Cfg::TILE_M * Cfg::BN * 4;
-    if (rem > 0 && rem * 10 <= workers * 8 && need <= p.tail_workspace_bytes) {
-      if (cudaMemsetAsync(p.tail_workspace, 0, need, stream) != cudaSuccess) return ERR_LAUNCH;
+    // Two slots per worker (its share of the tail touches at most two tiles).
+    const long long need = 2ll * workers * Cfg::TILE_M * Cfg::BN * 4;
+    if (rem > 0 && rem * 10 <= workers * 8 && need <= p.tail_workspace_bytes &&
+        (reinterpret_cast<uintptr_t>(p.tail_workspace) & 15) == 0 &&
+        encode_2d(&tpartial, DT_F32, p.tail_workspace, Cfg::BN, 2ull * workers * Cfg::TILE_M, Cfg::BN * 4ull, 32, 32) == OK) {
       tail_tiles = rem;
       g.stream_k = 2;
       g.dp_tiles = static_cast<int>(tiles) - rem;
@@ -165,9 +169,10 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
   }
-  const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<Cfg>, ta, tb, tout, taux, g);
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<Cfg>, ta, tb, tout, taux, tpartial, g);
   if (err != cudaSuccess) return ERR_LAUNCH;
-  if (tail_tiles > 0) return launch_hybrid_finish(g, g.dp_tiles, tail_tiles, Cfg::TILE_M, Cfg::BN, stream);
+  if (tail_tiles > 0)
+    return launch_hybrid_finish(g, g.dp_tiles, tail_tiles, workers, Cfg::TILE_M, Cfg::BN, stream);
   return OK;
 }
 

@@ -62,8 +62,8 @@ struct GemmArgs {
   int act;
   float act_param;
   // Stream-K epilogue
-  float* partial;         // fp32, zero on entry; mode 1: [M, N] (pitch ld_partial) or, if transposed,
-                          // [N, M]; mode 2: one dense TILE_M x BN block per shared-out tile
+  float* partial;         // fp32; mode 1: zero on entry, [M, N] (pitch ld_partial) or, if transposed,
+                          // [N, M]; mode 2: 2 * workers dense TILE_M x BN slots, written through a map
   long long ld_partial;
   int partial_transposed;
   int* status;            // device word; a bounded wait that runs out stores a DeviceStatus here
@@ -114,7 +114,7 @@ struct Segment {
   int m_blk, n_blk;
   int kb0, kb1;     // k-block range [kb0, kb1)
   int partial;      // 1: add the result to the fp32 partial sums; 0: whole tile, fused epilogue
-  int sk_index;     // hybrid mode: index of the tile among the shared-out tiles
+  int sk_index;     // hybrid mode: slot of this worker's partial tile (2 * worker + 0 or 1)
 };
 
 // Tile index -> (row block, column block).  Grouped rasterisation: group_m row blocks at a time,
@@ -135,17 +135,23 @@ __host__ __device__ __forceinline__ void tile_to_blocks(int t, int tiles_m, int 
 //   stream_k = 1  all (tile, k-block) units in equal contiguous shares
 //   stream_k = 2  hybrid: the first dp_tiles tiles whole, as in mode 0 (dp_tiles is a multiple of
 //                 the worker count, so these are full rounds); the (tile, k-block) units of the
-//                 remaining tiles in equal shares, which spreads a partial last round over all SMs
+//                 remaining tiles in equal shares, which spreads a partial last round over all SMs.
+//                 A share is shorter than one tile's reduction, so it touches at most two tiles;
+//                 each piece is written, not added, to the worker's own slot (2 * worker, then
+//                 2 * worker + 1) and a finishing kernel sums the slots of a tile in worker order:
+//                 no atomics, no clearing, bit-repeatable.
 struct SegmentIter {
   long long unit, unit_end;   // position in the shared-out (tile, k-block) units
   int tile, tile_end;         // next whole tile
   int stride;                 // number of workers (CTAs, or CTA pairs)
   int first_shared;           // first tile whose units are shared out
+  int slot;                   // hybrid: next partial-tile slot of this worker
   // worker / workers: index and count of the CTAs (or CTA pairs) that share the work.
   __device__ __forceinline__ SegmentIter(const GemmArgs& a, int worker, int workers) {
     const int tiles = a.tiles_m * a.tiles_n;
     stride = workers;
     tile = worker;
+    slot = 2 * worker;
     tile_end = a.stream_k == 0 ? tiles : (a.stream_k == 2 ? a.dp_tiles : 0);
     first_shared = a.stream_k == 0 ? tiles : (a.stream_k == 2 ? a.dp_tiles : 0);
     const long long total = static_cast<long long>(tiles - first_shared) * a.k_blocks;
@@ -170,7 +176,7 @@ struct SegmentIter {
       s.kb1 = (a.k_blocks - s.kb0 < left) ? a.k_blocks : s.kb0 + static_cast<int>(left);
       unit += s.kb1 - s.kb0;
       s.partial = 1;
-      s.sk_index = ts;
+      s.sk_index = slot++;
     }
     tile_to_blocks(t, a.tiles_m, a.tiles_n, a.group_m, s.m_blk, s.n_blk);
     return true;
@@ -282,7 +288,8 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_out,
-                    const __grid_constant__ CUtensorMap tmap_aux, const GemmArgs args) {
+                    const __grid_constant__ CUtensorMap tmap_aux,
+                    const __grid_constant__ CUtensorMap tmap_partial, const GemmArgs args) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BKE = Cfg::BKE, STAGES = Cfg::STAGES;
   constexpr int CTAS = Cfg::CTAS;
   constexpr bool kTf32 = (Cfg::ELT == 4);
@@ -477,11 +484,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int valid = (args.N - col0 < 32) ? args.N - col0 : 32;
         if (seg.partial) {
           if (args.stream_k == 2) {
-            // Tile-local, dense and 16-byte aligned: rows beyond M add zeros to padding.
-            float* p = args.partial + (static_cast<long long>(seg.sk_index) * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32 + lane) * BN + c * 32;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              ptx::red_add_v4_f32(p + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            // This worker's own slot: a plain fp32 TMA store of the chunk.
+            if (lane == 0) ptx::tma_store_wait_read();
+            __syncwarp();
+            stage_row_chunk(stage_buf, lane, DT_F32, v);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_2d(&tmap_partial, stage_buf, c * 32,
+                                seg.sk_index * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32);
+              ptx::tma_store_commit();
+            }
           } else if (row_ok) {
             if (args.partial_transposed) {
 #pragma unroll

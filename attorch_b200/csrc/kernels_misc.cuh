@@ -180,13 +180,15 @@ __global__ void streamk_finish_kernel(float* __restrict__ partial, long long ld_
 }
 
 // ------------------------------------------------------------------------------------------------
-// Finishing pass of the hybrid GEMM: the tiles whose reduction was shared out sit as dense
-// tile_m x bn fp32 blocks in `partial`; block b of the grid turns shared-out tile b into output
-// (same epilogue as everywhere) and clears it.
+// Finishing pass of the hybrid GEMM.  Shared-out tile t (blockIdx.x) received pieces from the workers
+// whose share of the (tile, k-block) units overlaps it; worker w wrote them to slot 2w (if the tile
+// is the first its share touches) or 2w + 1.  The pieces are summed in worker order and go through
+// the same epilogue as everywhere.
 // ------------------------------------------------------------------------------------------------
 struct HybridFinishArgs {
-  float* partial;
-  int first_tile, tiles_m, tiles_n, group_m, tile_m, bn;
+  const float* partial;
+  int first_tile, tail_tiles, workers, k_blocks;
+  int tiles_m, tiles_n, group_m, tile_m, bn;
   int M, N;
   const void* bias; int bias_dtype;
   void* aux; long long ld_aux;
@@ -195,17 +197,38 @@ struct HybridFinishArgs {
 };
 
 __global__ void __launch_bounds__(256) hybrid_finish_kernel(const HybridFinishArgs a) {
+  // The workers whose shares overlap this tile's units form a contiguous range [w_lo, w_hi].
+  __shared__ int w_lo, w_hi;
+  const long long total = static_cast<long long>(a.tail_tiles) * a.k_blocks;
+  const long long t0 = static_cast<long long>(blockIdx.x) * a.k_blocks, t1 = t0 + a.k_blocks;
+  if (threadIdx.x == 0) {
+    int lo = a.workers, hi = -1;
+    for (int w = 0; w < a.workers; ++w) {
+      const long long u0 = total * w / a.workers, u1 = total * (w + 1) / a.workers;
+      if (u0 < t1 && u1 > t0 && u1 > u0) {
+        if (w < lo) lo = w;
+        hi = w;
+      }
+    }
+    w_lo = lo;
+    w_hi = hi;
+  }
+  __syncthreads();
   int m_blk, n_blk;
   tile_to_blocks(a.first_tile + blockIdx.x, a.tiles_m, a.tiles_n, a.group_m, m_blk, n_blk);
-  float* tile = a.partial + static_cast<long long>(blockIdx.x) * a.tile_m * a.bn;
   const int elems = a.tile_m * a.bn;
-  for (int i = threadIdx.x; i < elems; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < elems; i += gridDim.y * blockDim.x) {
     const int r = i / a.bn, c = i - r * a.bn;
-    float v[1] = {tile[i]};
-    tile[i] = 0.0f;
     const long long m = static_cast<long long>(m_blk) * a.tile_m + r;
     const long long n = static_cast<long long>(n_blk) * a.bn + c;
     if (m >= a.M || n >= a.N) continue;
+    float v[1] = {0.0f};
+    for (int w = w_lo; w <= w_hi; ++w) {
+      const long long u0 = total * w / a.workers, u1 = total * (w + 1) / a.workers;
+      if (u1 <= u0) continue;
+      const int slot = 2 * w + ((u0 / a.k_blocks == blockIdx.x) ? 0 : 1);
+      v[0] += a.partial[static_cast<long long>(slot) * elems + i];
+    }
     if (a.bias != nullptr) v[0] += round_through(load_as_f32(a.bias, a.bias_dtype, n), a.out_dtype);
     if (a.aux != nullptr && a.save_grad) {
       float zr[1] = {round_through(v[0], a.out_dtype)}, g[1];

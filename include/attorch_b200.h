@@ -90,7 +90,7 @@ extern "C" {
 #define AB200_FLAG_NO_PAIR 16       /* one CTA per tile: no cta_group::2 kernels                */
 #define AB200_FLAG_NO_TMA_STORE 32  /* epilogue stores from registers, not through TMA           */
 #define AB200_FLAG_SAVE_DERIVATIVE 64 /* forward: pre_act receives act'(Z) instead of Z            */
-#define AB200_FLAG_DETERMINISTIC 128 /* no atomically summed tile tails: bit-repeatable results    */
+#define AB200_FLAG_WHOLE_TILES 128  /* never share out a partial last round of tiles            */
 
 /* Which kernel the last call on this host thread chose: 1 tcgen05 tile-parallel, 2 tcgen05
  * swap-AB stream-K, 3 generic CUDA-core.  For tests and benchmarks. */

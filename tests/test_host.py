@@ -54,7 +54,7 @@ def test_header_constants_match_python():
     assert int(defines['AB200_FLAG_NO_PAIR']) == _lib.FLAG_NO_PAIR
     assert int(defines['AB200_FLAG_NO_TMA_STORE']) == _lib.FLAG_NO_TMA_STORE
     assert int(defines['AB200_FLAG_SAVE_DERIVATIVE']) == _lib.FLAG_SAVE_DERIVATIVE
-    assert int(defines['AB200_FLAG_DETERMINISTIC']) == _lib.FLAG_DETERMINISTIC
+    assert int(defines['AB200_FLAG_WHOLE_TILES']) == _lib.FLAG_WHOLE_TILES
     assert int(defines['AB200_ACT_SAVED_DERIVATIVE']) == _lib.ACT_SAVED_DERIVATIVE
 
 
@@ -89,12 +89,12 @@ def test_argument_validation_without_gpu(lib):
 
 def test_workspace_sizes(lib):
     assert lib.ab200_forward_workspace_bytes(8, 8192, 28672, 0) == 8 * 28672 * 4
-    assert lib.ab200_forward_workspace_bytes(8192, 4096, 4096, 0) == 148 * 128 * 256 * 4
+    assert lib.ab200_forward_workspace_bytes(8192, 4096, 4096, 0) == 2 * 148 * 128 * 256 * 4
     assert lib.ab200_forward_workspace_bytes(300, 264, 520, _lib.FLAG_FORCE_STREAMK) == 300 * 520 * 4
     assert lib.ab200_forward_workspace_bytes(8, 64, 64, _lib.FLAG_NO_STREAMK) == 0
     # A 16 x 96 weight gradient over 131072 rows is one tile: its reduction is shared out.
     assert lib.ab200_gemm_workspace_bytes(16, 96, 131072) == 16 * 96 * 4
-    assert lib.ab200_gemm_workspace_bytes(4096, 4096, 8192) == 148 * 128 * 256 * 4
+    assert lib.ab200_gemm_workspace_bytes(4096, 4096, 8192) == 2 * 148 * 128 * 256 * 4
     assert lib.ab200_gemm_workspace_bytes(256, 256, 8192) == 0
     assert lib.ab200_act_backward_workspace_bytes(8192, 4096) == 64 * 4096 * 4
     assert lib.ab200_act_backward_workspace_bytes(1, 16) == 64

@@ -425,14 +425,14 @@ def test_weight_gradient_in_row_blocks():
 def test_shared_out_last_round_of_tiles():
     """
     90 pair tiles on 74 CTA pairs: the 16 tiles of the second round have their reductions shared
-    out over all SMs (fp32 atomics + finishing kernel).  Parity with the oracle, and agreement with
-    the bit-repeatable whole-tile schedule.
+    out over all SMs (per-worker partial tiles summed in worker order by a finishing kernel).
+    Parity with the oracle, agreement of the forward output with the whole-tile schedule, and
+    bit-repeatability.
     """
     x, w, b, dy = seeded((2560, 1024), 2304, torch.bfloat16, seed=17)
     got = check_layer(x, w, b, 'gelu', dy)
-    whole = run_layer(x, w, b, 'gelu', dy, flags=_lib.FLAG_DETERMINISTIC)
-    for a, c in zip(got[:4], whole[:4]):
-        torch.testing.assert_close(a.float(), c.float(), rtol=1e-2, atol=1e-2)
-    again = run_layer(x, w, b, 'gelu', dy, flags=_lib.FLAG_DETERMINISTIC)
-    for a, c in zip(whole[:4], again[:4]):
+    whole = run_layer(x, w, b, 'gelu', dy, flags=_lib.FLAG_WHOLE_TILES)
+    torch.testing.assert_close(got[0].float(), whole[0].float(), rtol=1e-2, atol=1e-2)
+    again = run_layer(x, w, b, 'gelu', dy)
+    for a, c in zip(got[:4], again[:4]):
         assert torch.equal(a, c)
