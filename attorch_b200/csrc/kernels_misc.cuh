@@ -158,24 +158,39 @@ __global__ void streamk_finish_kernel(float* __restrict__ partial, long long ld_
                                       const void* bias, int bias_dtype, void* aux, long long ld_aux,
                                       void* out, long long ld_out, int out_dtype, int act,
                                       float act_param, int save_grad) {
-  const long long total = static_cast<long long>(M) * N;
+  // Four consecutive columns per thread where the row pitch allows 16-byte accesses.
+  const bool vec = (N % 4 == 0) && (ld_partial % 4 == 0);
+  const int width = vec ? 4 : 1;
+  const long long groups_per_row = N / width;
+  const long long total = static_cast<long long>(M) * groups_per_row;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int m = static_cast<int>(i / N);
-    const int n = static_cast<int>(i - static_cast<long long>(m) * N);
-    float* pp = partial + m * ld_partial + n;
-    float v[1] = {*pp};
-    *pp = 0.0f;
-    if (bias != nullptr) v[0] += round_through(load_as_f32(bias, bias_dtype, n), out_dtype);
-    if (aux != nullptr && save_grad) {
-      float zr[1] = {round_through(v[0], out_dtype)}, g[1];
-      act_fwd_grad(v, zr, g, act, act_param);
-      store_from_f32(aux, out_dtype, m * ld_aux + n, g[0]);
+    const long long m = i / groups_per_row;
+    const long long n0 = (i - m * groups_per_row) * width;
+    float* pp = partial + m * ld_partial + n0;
+    float vals[4];
+    if (vec) {
+      const float4 p = *reinterpret_cast<const float4*>(pp);
+      *reinterpret_cast<float4*>(pp) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      vals[0] = p.x; vals[1] = p.y; vals[2] = p.z; vals[3] = p.w;
     } else {
-      if (aux != nullptr) store_from_f32(aux, out_dtype, m * ld_aux + n, v[0]);
-      act_fwd_inplace(v, act, act_param);
+      vals[0] = *pp;
+      *pp = 0.0f;
     }
-    store_from_f32(out, out_dtype, m * ld_out + n, v[0]);
+    for (int e = 0; e < width; ++e) {
+      const long long n = n0 + e;
+      float v[1] = {vals[e]};
+      if (bias != nullptr) v[0] += round_through(load_as_f32(bias, bias_dtype, n), out_dtype);
+      if (aux != nullptr && save_grad) {
+        float zr[1] = {round_through(v[0], out_dtype)}, g[1];
+        act_fwd_grad(v, zr, g, act, act_param);
+        store_from_f32(aux, out_dtype, m * ld_aux + n, g[0]);
+      } else {
+        if (aux != nullptr) store_from_f32(aux, out_dtype, m * ld_aux + n, v[0]);
+        act_fwd_inplace(v, act, act_param);
+      }
+      store_from_f32(out, out_dtype, m * ld_out + n, v[0]);
+    }
   }
 }
 
@@ -196,49 +211,61 @@ struct HybridFinishArgs {
   int act; float act_param; int save_grad;
 };
 
+constexpr int kMaxTailPieces = 160;   // at most one piece per worker; B200 has 148 SMs
+
 __global__ void __launch_bounds__(256) hybrid_finish_kernel(const HybridFinishArgs a) {
-  // The workers whose shares overlap this tile's units form a contiguous range [w_lo, w_hi].
-  __shared__ int w_lo, w_hi;
-  const long long total = static_cast<long long>(a.tail_tiles) * a.k_blocks;
-  const long long t0 = static_cast<long long>(blockIdx.x) * a.k_blocks, t1 = t0 + a.k_blocks;
-  if (threadIdx.x == 0) {
-    int lo = a.workers, hi = -1;
-    for (int w = 0; w < a.workers; ++w) {
+  // Slots of the pieces of this tile, in worker order.
+  __shared__ int slots[kMaxTailPieces];
+  __shared__ int piece_slot[kMaxTailPieces];   // per worker: its slot for this tile, or -1
+  __shared__ int n_slots;
+  {
+    const long long total = static_cast<long long>(a.tail_tiles) * a.k_blocks;
+    const long long t0 = static_cast<long long>(blockIdx.x) * a.k_blocks, t1 = t0 + a.k_blocks;
+    for (int w = threadIdx.x; w < a.workers && w < kMaxTailPieces; w += blockDim.x) {
       const long long u0 = total * w / a.workers, u1 = total * (w + 1) / a.workers;
-      if (u0 < t1 && u1 > t0 && u1 > u0) {
-        if (w < lo) lo = w;
-        hi = w;
-      }
+      piece_slot[w] = (u0 < t1 && u1 > t0 && u1 > u0) ? 2 * w + ((u0 / a.k_blocks == blockIdx.x) ? 0 : 1) : -1;
     }
-    w_lo = lo;
-    w_hi = hi;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int n = 0;
+      for (int w = 0; w < a.workers && w < kMaxTailPieces; ++w)
+        if (piece_slot[w] >= 0) slots[n++] = piece_slot[w];
+      n_slots = n;
+    }
   }
   __syncthreads();
   int m_blk, n_blk;
   tile_to_blocks(a.first_tile + blockIdx.x, a.tiles_m, a.tiles_n, a.group_m, m_blk, n_blk);
   const int elems = a.tile_m * a.bn;
-  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < elems; i += gridDim.y * blockDim.x) {
+  const int pieces = n_slots;
+  // Four consecutive columns per thread (bn is a multiple of 32).
+  for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < elems; i += gridDim.y * blockDim.x * 4) {
     const int r = i / a.bn, c = i - r * a.bn;
     const long long m = static_cast<long long>(m_blk) * a.tile_m + r;
-    const long long n = static_cast<long long>(n_blk) * a.bn + c;
-    if (m >= a.M || n >= a.N) continue;
-    float v[1] = {0.0f};
-    for (int w = w_lo; w <= w_hi; ++w) {
-      const long long u0 = total * w / a.workers, u1 = total * (w + 1) / a.workers;
-      if (u1 <= u0) continue;
-      const int slot = 2 * w + ((u0 / a.k_blocks == blockIdx.x) ? 0 : 1);
-      v[0] += a.partial[static_cast<long long>(slot) * elems + i];
+    const long long n0 = static_cast<long long>(n_blk) * a.bn + c;
+    if (m >= a.M || n0 >= a.N) continue;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int j = 0; j < pieces; ++j) {
+      const float4 p = *reinterpret_cast<const float4*>(a.partial + static_cast<long long>(slots[j]) * elems + i);
+      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
     }
-    if (a.bias != nullptr) v[0] += round_through(load_as_f32(a.bias, a.bias_dtype, n), a.out_dtype);
-    if (a.aux != nullptr && a.save_grad) {
-      float zr[1] = {round_through(v[0], a.out_dtype)}, g[1];
-      act_fwd_grad(v, zr, g, a.act, a.act_param);
-      store_from_f32(a.aux, a.out_dtype, m * a.ld_aux + n, g[0]);
-    } else {
-      if (a.aux != nullptr) store_from_f32(a.aux, a.out_dtype, m * a.ld_aux + n, v[0]);
-      act_fwd_inplace(v, a.act, a.act_param);
+    const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const long long n = n0 + e;
+      if (n >= a.N) break;
+      float v[1] = {vals[e]};
+      if (a.bias != nullptr) v[0] += round_through(load_as_f32(a.bias, a.bias_dtype, n), a.out_dtype);
+      if (a.aux != nullptr && a.save_grad) {
+        float zr[1] = {round_through(v[0], a.out_dtype)}, g[1];
+        act_fwd_grad(v, zr, g, a.act, a.act_param);
+        store_from_f32(a.aux, a.out_dtype, m * a.ld_aux + n, g[0]);
+      } else {
+        if (a.aux != nullptr) store_from_f32(a.aux, a.out_dtype, m * a.ld_aux + n, v[0]);
+        act_fwd_inplace(v, a.act, a.act_param);
+      }
+      store_from_f32(a.out, a.out_dtype, m * a.ld_out + n, v[0]);
     }
-    store_from_f32(a.out, a.out_dtype, m * a.ld_out + n, v[0]);
   }
 }
 
