@@ -85,6 +85,19 @@ def _stream_scratch(device: torch.device) -> Dict[str, Tensor]:
     return entry
 
 
+_size_cache: Dict[Tuple, int] = {}
+
+
+def _cached_size(func_name: str, *shape: int) -> int:
+    """Workspace sizes depend on the shape only: ask the library once per shape."""
+    key = (func_name,) + shape
+    size = _size_cache.get(key)
+    if size is None:
+        size = int(getattr(_lib.load(), func_name)(*shape))
+        _size_cache[key] = size
+    return size
+
+
 def _workspace(device: torch.device, nbytes: int) -> Tensor:
     entry = _stream_scratch(device)
     if entry['workspace'].numel() < nbytes:
@@ -196,7 +209,7 @@ class LinearAutoGrad(torch.autograd.Function):
             output = torch.empty((batch_dim, out_feat_dim), device=input.device, dtype=output_dtype)
             pre_act = torch.empty_like(output) if save_pre_act else None
 
-            ws_bytes = lib.ab200_forward_workspace_bytes(batch_dim, in_feat_dim, out_feat_dim, _gemm_flags)
+            ws_bytes = _cached_size('ab200_forward_workspace_bytes', batch_dim, in_feat_dim, out_feat_dim, _gemm_flags)
             workspace = _workspace(input.device, ws_bytes) if ws_bytes else None
             _lib.check(lib.ab200_linear_forward(
                 _ptr(x_op), _ptr(w_op), _ptr(bias_op), _ptr(pre_act), _ptr(output),
@@ -270,7 +283,7 @@ class LinearAutoGrad(torch.autograd.Function):
             else:
                 pre_act_grad = torch.empty((batch_dim, out_feat_dim), dtype=op_dtype, device=device)
             if ctx.act_func is not None or need_db:
-                ws_bytes = lib.ab200_act_backward_workspace_bytes(batch_dim, out_feat_dim) if need_db else 0
+                ws_bytes = _cached_size('ab200_act_backward_workspace_bytes', batch_dim, out_feat_dim) if need_db else 0
                 workspace = _workspace(device, ws_bytes) if ws_bytes else None
                 _lib.check(lib.ab200_act_backward(
                     _ptr(dy), _ptr(pre_act),
@@ -295,7 +308,7 @@ class LinearAutoGrad(torch.autograd.Function):
                 chunks = ctx.dw_chunks if (ctx.grad_ready is not None and ctx.dw_chunks > 1 and
                                            in_feat_dim % (ctx.dw_chunks * 8) == 0) else 1
                 rows = in_feat_dim // chunks
-                ws_bytes = lib.ab200_gemm_workspace_bytes(rows, out_feat_dim, batch_dim)
+                ws_bytes = _cached_size('ab200_gemm_workspace_bytes', rows, out_feat_dim, batch_dim)
                 workspace = _workspace(device, ws_bytes) if ws_bytes else None
                 for c in range(chunks):
                     x_part = x_op[:, c * rows:(c + 1) * rows]
@@ -313,7 +326,7 @@ class LinearAutoGrad(torch.autograd.Function):
                 ctx.grad_ready(0, 1)
             if ctx.input_requires_grad:
                 input_grad = torch.empty((batch_dim, in_feat_dim), dtype=ctx.input_dtype, device=device)
-                ws_bytes = lib.ab200_gemm_workspace_bytes(batch_dim, in_feat_dim, out_feat_dim)
+                ws_bytes = _cached_size('ab200_gemm_workspace_bytes', batch_dim, in_feat_dim, out_feat_dim)
                 workspace = _workspace(device, ws_bytes) if ws_bytes else None
                 _lib.check(lib.ab200_linear_backward_input(
                     _ptr(pre_act_grad), _ptr(w_op), _ptr(input_grad),

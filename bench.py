@@ -72,6 +72,8 @@ class ClockSampler:
         self._stop = threading.Event()
         self._thread = None
         try:
+            if index < 0:
+                raise RuntimeError('only rank 0 samples')
             import pynvml
             pynvml.nvmlInit()
             self._nvml = pynvml
@@ -387,7 +389,7 @@ def main():
     # One step (forward, backward, gradient exchange) captured once as a CUDA graph and replayed:
     # the same kernels on the same buffers, without the host-side gaps between launches.
     run_step, graphed = (lambda: step(x_dev)), False
-    if not args.no_graph and world_size == 1:
+    if not args.no_graph and world_size == 1:   # capture with NCCL on a side stream deadlocked here
         try:
             side = torch.cuda.Stream(device)
             side.wait_stream(torch.cuda.current_stream())
@@ -411,7 +413,7 @@ def main():
     barrier()
     launches_before = lib.ab200_launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
+    with ClockSampler(local_rank if rank == 0 else -1) as clocks:
         barrier()
         start.record()
         host_t0 = time.perf_counter()
