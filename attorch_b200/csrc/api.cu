@@ -167,7 +167,6 @@ const char* ab200_error_string(int code) {
     case DEV_TIMEOUT_PRODUCER: return "device: TMA producer gave up waiting for a free stage";
     case DEV_TIMEOUT_MMA: return "device: MMA issuer gave up waiting for operands or an accumulator";
     case DEV_TIMEOUT_EPILOGUE: return "device: epilogue gave up waiting for an accumulator";
-    case DEV_TIMEOUT_TRANSFORM: return "device: transform warps gave up waiting";
     default: return "unknown code";
   }
 }

@@ -35,7 +35,6 @@ enum DeviceStatus : int {
   DEV_TIMEOUT_PRODUCER = 1,
   DEV_TIMEOUT_MMA = 2,
   DEV_TIMEOUT_EPILOGUE = 3,
-  DEV_TIMEOUT_TRANSFORM = 4,
 };
 
 template <class T>

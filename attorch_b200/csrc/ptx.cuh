@@ -1,8 +1,8 @@
 // Inline-PTX wrappers for the sm_100a features the linear-layer kernels use:
 // mbarrier, TMA (cp.async.bulk.tensor), tcgen05 (TMEM alloc / MMA / commit / ld) and
-// the fences that order them.  Every wait in this file is bounded: a waiter that runs
-// out of time returns false so that the kernel can record an error status and leave
-// instead of hanging the GPU.
+// the fences that order them.  The kernels build their waits from mbar_try_wait with a time limit
+// (kWaitLimitNs): a waiter that runs out of time records an error status and leaves instead of
+// hanging the GPU.
 #pragma once
 #include <cstdint>
 #include <cuda.h>
@@ -18,16 +18,6 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
-}
-
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
 }
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -103,27 +93,8 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
   return done != 0;
 }
 
-// Longest time one wait may take before the kernel gives up (nanoseconds of %globaltimer).
+// Longest time one mbarrier wait may take before a kernel gives up (nanoseconds of %globaltimer).
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-
-// Bounded wait for the phase with the given parity to complete.  Returns false on time-out.
-template <bool kCluster = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  uint32_t spins = 0;
-  uint64_t t0 = 0;
-  while (true) {
-    const bool ok = kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
-    if (ok) return true;
-    if ((++spins & 0x3FFu) == 0) {
-      const uint64_t now = globaltimer_ns();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
-        return false;
-      }
-    }
-  }
-}
 
 // ----------------------------------------------------------------------------------------------
 // TMA: 2-D tiled bulk tensor load, global -> shared, completion on an mbarrier.  No multicast.

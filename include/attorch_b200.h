@@ -51,7 +51,6 @@ extern "C" {
 #define AB200_DEV_TIMEOUT_PRODUCER 1
 #define AB200_DEV_TIMEOUT_MMA 2
 #define AB200_DEV_TIMEOUT_EPILOGUE 3
-#define AB200_DEV_TIMEOUT_TRANSFORM 4
 
 /* Activation ids: the act_func strings of attorch/linear_layer.py:42-49 in the order of the
  * dispatcher attorch/act_kernels.py:654-727.  Ids 17..21 take `act_param`. */
