@@ -85,6 +85,15 @@ int sm_count() {
 namespace {
 std::atomic<int> g_cta_limit{0};
 }
+int raster_group_m() {
+  static const int value = []() {
+    const char* e = std::getenv("AB200_GROUP_M");
+    const int v = e != nullptr ? std::atoi(e) : 0;
+    return v > 0 ? v : 4;
+  }();
+  return value;
+}
+
 int gemm_cta_limit() { return g_cta_limit.load(std::memory_order_relaxed); }
 void set_gemm_cta_limit(int ctas) { g_cta_limit.store(ctas < 0 ? 0 : ctas, std::memory_order_relaxed); }
 

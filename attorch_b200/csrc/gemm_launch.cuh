@@ -30,6 +30,10 @@ struct TcProblem {
 // Number of SMs of the current device (148 if it cannot be queried).
 int sm_count();
 
+// Row blocks (of 128 rows) per rasterisation group: 4 unless AB200_GROUP_M overrides it (a sweep of
+// 2 ... 64 on B200 moved the 8192 x 4096 x 4096 GEMMs by 2 % at most; 2 and 4 were the fastest).
+int raster_group_m();
+
 // Upper bound on the CTAs a GEMM launch may use (0 = every SM).  A persistent GEMM that takes every
 // SM leaves none for a collective running beside it; a caller that overlaps the two lowers this.
 int gemm_cta_limit();
@@ -95,7 +99,7 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   g.tiles_m = (g.M + Cfg::TILE_M - 1) / Cfg::TILE_M;
   g.tiles_n = (g.N + Cfg::BN - 1) / Cfg::BN;
   g.k_blocks = (g.K + Cfg::BKE - 1) / Cfg::BKE;
-  g.group_m = 8 / Cfg::CTAS;
+  g.group_m = raster_group_m() / Cfg::CTAS > 0 ? raster_group_m() / Cfg::CTAS : 1;
   const uint32_t fmt = p.op_dtype == DT_F32 ? 2u : (p.op_dtype == DT_BF16 ? 1u : 0u);
   g.idesc = ptx::make_idesc(fmt, Cfg::A_MN ? 1u : 0u, Cfg::B_MN ? 1u : 0u, Cfg::TILE_M, Cfg::BN);
 

@@ -436,3 +436,25 @@ def test_shared_out_last_round_of_tiles():
     again = run_layer(x, w, b, 'gelu', dy)
     for a, c in zip(got[:4], again[:4]):
         assert torch.equal(a, c)
+
+
+def test_gemms_under_a_cta_limit():
+    """With SMs held back for a collective the persistent GEMMs still cover every tile."""
+    lib = _lib.load()
+    x, w, b, dy = seeded((1536, 320), 768, torch.bfloat16, seed=19)
+    previous = lib.ab200_set_gemm_cta_limit(100)
+    try:
+        check_layer(x, w, b, 'silu', dy)
+    finally:
+        assert lib.ab200_set_gemm_cta_limit(previous) == 100
+
+
+def test_mlp_pair_shapes_of_config3():
+    """BASELINE config 3 at reduced token count: 4096 -> 14336 (silu, no bias) -> 4096 (no bias)."""
+    gen = torch.Generator().manual_seed(23)
+    x = torch.randn(384, 4096, generator=gen).bfloat16()
+    w_up = (torch.randn(4096, 14336, generator=gen) * 0.02).bfloat16()
+    w_down = (torch.randn(14336, 4096, generator=gen) * 0.02).bfloat16()
+    dy = (torch.randn(384, 4096, generator=gen) * 0.01).bfloat16()
+    up = check_layer(x, w_up, None, 'silu', torch.randn(384, 14336, generator=gen).bfloat16())
+    check_layer(up[0], w_down, None, None, dy)
