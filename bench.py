@@ -345,8 +345,12 @@ def main():
               for (k, n, act, bias) in spec['layers']]
     # With graph replay (the default) the forward + backward of a step is one captured graph and the
     # gradient exchange is one all-reduce of the whole bucket after it; with --no-graph the exchange
-    # is issued per block of dW from inside backward and overlaps the rest of it.  Measured on 4
-    # B200: 0.896 ms per step either way; at 8 GPUs the eager variant becomes host-bound.
+    # is issued per block of dW from inside backward and overlaps the rest of it.  Measured: 2 GPUs
+    # 0.839 ms eager-overlapped vs 0.887 ms graph; 8 GPUs 1.001 ms eager (host-bound: 0.91 ms of
+    # enqueue time per step with 2 host threads per rank).
+    # So: graph replay on one GPU and wherever a rank has fewer than 4 host threads to itself.
+    if world_size > 1 and (os.cpu_count() or 1) // world_size >= 4 and not os.environ.get('AB200_FORCE_GRAPH'):
+        args.no_graph = True
     overlap = args.no_graph and os.environ.get('AB200_DP_OVERLAP', '1') != '0'
     buckets = GradientBuckets(layers, comm_sms=int(os.environ.get('AB200_COMM_SMS', '16')),
                               overlap=overlap,
