@@ -12,6 +12,7 @@
 #include "common.cuh"
 #include "gemm_launch.cuh"
 #include "kernels_misc.cuh"
+#include "act_elementwise.cuh"
 
 namespace ab200 {
 
@@ -510,6 +511,50 @@ int ab200_linear_backward_weight(const void* x, const void* dz, void* dw, int64_
   g_last_path = AB200_PATH_GENERIC;
   return launch_any(a, stream);
 }
+
+extern "C++" {
+namespace {
+template <bool kBackward>
+int launch_act_elementwise(const void* x, const void* dy, void* out, int64_t n, int dtype, int act,
+                           float act_param, float drop_p, uint32_t seed, cudaStream_t stream) {
+  if (n < 0) return ERR_BAD_SHAPE;
+  if (!valid_dtype(dtype)) return ERR_BAD_DTYPE;
+  if (!valid_act(act)) return ERR_BAD_ACT;
+  if (!(drop_p >= 0.0f && drop_p < 1.0f)) return ERR_BAD_SHAPE;
+  if (n == 0) return OK;
+  if (!x || !out || (kBackward && !dy)) return ERR_NULL_POINTER;
+  const int dropout = drop_p > 0.0f ? 1 : 0;
+  const long long groups = (n + 7) / 8;
+  long long blocks = (groups + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+#define AB200_ACT_EW(T)                                                                                 \
+  act_elementwise_kernel<T, kBackward><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(              \
+      static_cast<const T*>(x), static_cast<const T*>(dy), static_cast<T*>(out), n, act, act_param,     \
+      drop_p, seed, dropout)
+  if (dtype == DT_F32) AB200_ACT_EW(float);
+  else if (dtype == DT_F16) AB200_ACT_EW(__half);
+  else AB200_ACT_EW(__nv_bfloat16);
+#undef AB200_ACT_EW
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
+}
+}  // namespace
+}  // extern "C++"
+
+int ab200_act_forward(const void* x, void* y, int64_t n, int dtype, int act, float act_param, float drop_p,
+                      uint32_t seed, void* stream) {
+  return launch_act_elementwise<false>(x, nullptr, y, n, dtype, act, act_param, drop_p, seed,
+                                       static_cast<cudaStream_t>(stream));
+}
+
+int ab200_act_input_grad(const void* dy, const void* x, void* dx, int64_t n, int dtype, int act,
+                         float act_param, float drop_p, uint32_t seed, void* stream) {
+  return launch_act_elementwise<true>(x, dy, dx, n, dtype, act, act_param, drop_p, seed,
+                                      static_cast<cudaStream_t>(stream));
+}
+
+float ab200_dropout_uniform(uint32_t seed, uint64_t index) { return dropout_uniform(seed, index); }
 
 int ab200_cast_2d(const void* src, void* dst, int64_t rows, int64_t cols, int64_t src_stride_r,
                   int64_t src_stride_c, int src_dtype, int dst_dtype, void* stream_) {

@@ -227,6 +227,32 @@ int ab200_linear_backward_weight(const void* x, const void* dz, void* dw, int64_
                                  int* status, void* stream, int flags);
 
 /*
+ * Standalone activation layer with fused dropout, forward:  y[i] = keep_i ? act(x[i]) / (1 - p) : 0.
+ * Replaces act_func_forward_kernel (attorch/act_kernels.py:840-880, launched at
+ * attorch/act_layers.py:66-73) with apply_dropout (attorch/dropout_kernels.py:12-28).  x, y: n
+ * contiguous elements of `dtype`; act != AB200_ACT_NONE is not required (identity + dropout works).
+ * drop_p = 0 switches dropout off; otherwise element i is dropped iff
+ * ab200_dropout_uniform(seed, i) < drop_p.
+ */
+int ab200_act_forward(const void* x, void* y, int64_t n, int dtype, int act, float act_param, float drop_p,
+                      uint32_t seed, void* stream);
+
+/*
+ * Its backward:  dx[i] = (keep_i ? dy[i] / (1 - p) : 0) * act'(x[i]), same mask as forward for the
+ * same seed.  Replaces act_func_backward_kernel (attorch/act_kernels.py:883-927, launched at
+ * attorch/act_layers.py:106-110) with apply_dropout_grad (attorch/dropout_kernels.py:31-46).
+ */
+int ab200_act_input_grad(const void* dy, const void* x, void* dx, int64_t n, int dtype, int act,
+                         float act_param, float drop_p, uint32_t seed, void* stream);
+
+/*
+ * The uniform number in [0, 1) the dropout mask compares with drop_p (host function; Philox 4x32-10,
+ * key (seed, 0), counter index / 4, word index % 4, top 24 bits).  The reference draws its numbers
+ * with Triton's tl.rand(seed, offset) (attorch/dropout_kernels.py:25); the streams differ.
+ */
+float ab200_dropout_uniform(uint32_t seed, uint64_t index);
+
+/*
  * dst[r, c] (contiguous, dst_dtype) = src[r * src_stride_r + c * src_stride_c] (src_dtype).
  * The operand casts that autocast implies (attorch/linear_kernels.py:161-163 casts in registers;
  * torch.autocast casts before its matmuls, attorch/linear_layer.py:152) and the copy that makes a

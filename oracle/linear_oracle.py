@@ -296,3 +296,73 @@ def linear_forward_backward(x: Tensor, weight: Tensor, bias: Optional[Tensor], a
     dx, dw, db = linear_backward(output_grad.to(out_dtype), x, pre_act, weight, act_func, out_dtype, bias,
                                  tf32=tf32)
     return out, pre_act, dx, dw, db
+
+
+# ------------------------------------------------------------------------------------------------
+# Standalone activation layers with fused dropout (attorch/act_layers.py:20-117,
+# attorch/act_kernels.py:840-927, attorch/dropout_kernels.py:12-46)
+# ------------------------------------------------------------------------------------------------
+def philox4x32_10(counter: 'np.ndarray', seed: int) -> 'np.ndarray':
+    """
+    Philox 4x32 with 10 rounds (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", 2011)
+    for counters (c, 0, 0, 0) with c a uint64 array split into two 32-bit words, key (seed, 0).
+    Returns an array [..., 4] of uint32.  This is the generator of the CUDA library's dropout mask
+    (csrc/act_elementwise.cuh); the reference's mask comes from Triton's tl.rand
+    (attorch/dropout_kernels.py:25) and is a different stream.
+    """
+    import numpy as np
+    c = np.asarray(counter, dtype=np.uint64)
+    c0 = (c & np.uint64(0xFFFFFFFF)).astype(np.uint64)
+    c1 = (c >> np.uint64(32)).astype(np.uint64)
+    c2 = np.zeros_like(c0)
+    c3 = np.zeros_like(c0)
+    k0, k1 = np.uint64(seed & 0xFFFFFFFF), np.uint64(0)
+    mask = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0 = np.uint64(0xD2511F53) * c0
+        p1 = np.uint64(0xCD9E8D57) * c2
+        n0 = ((p1 >> np.uint64(32)) ^ c1 ^ k0) & mask
+        n1 = p1 & mask
+        n2 = ((p0 >> np.uint64(32)) ^ c3 ^ k1) & mask
+        n3 = p0 & mask
+        c0, c1, c2, c3 = n0, n1, n2, n3
+        k0 = (k0 + np.uint64(0x9E3779B9)) & mask
+        k1 = (k1 + np.uint64(0xBB67AE85)) & mask
+    return np.stack([c0, c1, c2, c3], axis=-1).astype(np.uint32)
+
+
+def dropout_uniform(seed: int, n: int) -> Tensor:
+    """The n uniform numbers in [0, 1) that decide the dropout mask of elements 0 .. n-1."""
+    import numpy as np
+    blocks = philox4x32_10(np.arange((n + 3) // 4, dtype=np.uint64), seed).reshape(-1)[:n]
+    return torch.from_numpy(((blocks >> np.uint32(8)).astype(np.float32) / np.float32(16777216.0)))
+
+
+def act_layer_forward(x: Tensor, act_func: str, drop_p: float = 0.0, seed: int = 0) -> Tensor:
+    """
+    act_func_forward_kernel (attorch/act_kernels.py:840-880): the activation (in fp32 for the
+    activations of FP32_ACTS, else in x's dtype), then apply_dropout
+    (attorch/dropout_kernels.py:12-28): 0 where the uniform number is below drop_p, otherwise
+    divided by 1 - drop_p; stored in x's dtype.
+    """
+    name, param = parse_act_func(act_func)
+    z = x.float() if name in FP32_ACTS else x
+    y = act_forward(name, z, param)
+    if drop_p > 0:
+        u = dropout_uniform(seed, x.numel()).view(x.shape)
+        y = torch.where(u < drop_p, torch.zeros((), dtype=y.dtype), y / (1 - drop_p))
+    return y.to(x.dtype)
+
+
+def act_layer_backward(dy: Tensor, x: Tensor, act_func: str, drop_p: float = 0.0, seed: int = 0) -> Tensor:
+    """
+    act_func_backward_kernel (attorch/act_kernels.py:883-927): apply_dropout_grad
+    (attorch/dropout_kernels.py:31-46) on dy, times act'(x); stored in x's dtype.
+    """
+    name, param = parse_act_func(act_func)
+    z = x.float() if name in FP32_ACTS else x
+    g = dy
+    if drop_p > 0:
+        u = dropout_uniform(seed, x.numel()).view(x.shape)
+        g = torch.where(u < drop_p, torch.zeros((), dtype=dy.dtype), dy / (1 - drop_p))
+    return (g * act_grad(name, z, param)).to(x.dtype)

@@ -9,11 +9,11 @@ Usage (needs a checkout of the reference; no GPU):
 The reference is imported unmodified.  Two host-side shims make it importable without a GPU:
 ``torch.cuda.get_device_capability`` is stubbed (the reference queries it at import time,
 attorch/utils.py:12-24), and each autotuner is cut down to its first configuration so that no
-config is benchmarked (attorch/linear_kernels.py:44-56, attorch/act_kernels.py:883-887).
+config is benchmarked (attorch/linear_kernels.py:44-56, attorch/act_kernels.py:840-887).
 
 Each case is stored as one .npz with the inputs (or the seed that regenerates them plus a
-checksum) and the reference's output, dX, dW and db.  bf16 is not generated: the interpreter's
-bf16 dot product returns garbage.
+checksum) and the reference's output, dX, dW and db; the standalone activation layers go into
+act_layers_fp32.npz.  bf16 is not generated: the interpreter's bf16 dot product returns garbage.
 """
 
 import argparse
@@ -39,10 +39,11 @@ def load_reference(path: str):
     torch.cuda.get_device_capability = lambda *args, **kwargs: (10, 0)
     sys.path.insert(0, path)
     import attorch
-    from attorch.act_kernels import act_func_backward_kernel
+    from attorch.act_kernels import act_func_backward_kernel, act_func_forward_kernel
     from attorch.linear_kernels import linear_forward_kernel
     linear_forward_kernel.configs = linear_forward_kernel.configs[:1]
     act_func_backward_kernel.configs = act_func_backward_kernel.configs[:1]
+    act_func_forward_kernel.configs = act_func_forward_kernel.configs[:1]
     return attorch
 
 
@@ -156,6 +157,42 @@ def main():
     x, w, _, dy = small_inputs(3, torch.float32, shape=(7, 24), out_dim=40, strided=False)
     save('small_fp32_nobias_gelu', True, x, w, None, dy, run_reference(attorch, x, w, None, 'gelu', dy),
          act_func='gelu', dtype='float32')
+
+    act_layer_goldens(attorch)
+
+
+ACT_LAYERS = [('Sigmoid', {}), ('LogSigmoid', {}), ('Tanh', {}), ('ReLU', {}), ('GELU', {}),
+              ('GELU', {'approximate': 'tanh'}), ('SiLU', {}), ('ReLU6', {}), ('Hardsigmoid', {}),
+              ('Hardtanh', {}), ('Hardswish', {}), ('SELU', {}), ('Mish', {}), ('Softplus', {}),
+              ('Softsign', {}), ('Tanhshrink', {}), ('LeakyReLU', {'negative_slope': 0.01}),
+              ('ELU', {'alpha': 1.0}), ('CELU', {'alpha': 1.0}), ('Hardshrink', {'lambd': 0.5}),
+              ('Softshrink', {'lambd': 0.5})]
+
+
+def act_layer_goldens(attorch):
+    """
+    The reference's standalone activation layers (attorch/act_layers.py): for every layer class the
+    output and input gradient on a seeded input that also contains the piecewise switch points, without
+    dropout and with drop_p = 0.5 (whose mask comes from Triton's generator; the vectors pin what a
+    dropped and a kept element look like, not which elements are dropped).
+    """
+    gen = torch.Generator().manual_seed(4)
+    x = torch.randn(6, 40, generator=gen) * 2
+    x[0, :12] = torch.tensor([-6.0, -3.0, -1.0, -0.5, 0.0, 0.5, 1.0, 3.0, 6.0, 7.0, -7.0, 2.0])
+    dy = torch.randn(6, 40, generator=gen)
+    data = {'x': x.numpy(), 'dy': dy.numpy()}
+    for index, (name, kwargs) in enumerate(ACT_LAYERS):
+        for drop_p in (0.0, 0.5):
+            layer = getattr(attorch, name)(drop_p=drop_p, **kwargs)
+            layer.train()
+            xin = x.clone().requires_grad_(True)
+            y = layer(xin)
+            y.backward(dy)
+            tag = f'{index:02d}_{name}_{"drop" if drop_p else "plain"}'
+            data[f'y_{tag}'] = y.detach().numpy()
+            data[f'dx_{tag}'] = xin.grad.numpy()
+    np.savez_compressed(OUT_DIR / 'act_layers_fp32.npz', **data)
+    print('wrote act_layers_fp32.npz')
 
 
 if __name__ == '__main__':

@@ -16,7 +16,25 @@ TOLERANCE = {torch.float32: 1e-2, torch.float16: 1e-2, torch.bfloat16: 1e-2}
 
 
 def golden_names(prefix: str = ''):
-    return sorted(p.stem for p in GOLDEN_DIR.glob(f'{prefix}*.npz'))
+    """Names of the linear-layer golden cases (the activation-layer file has its own loader)."""
+    return sorted(p.stem for p in GOLDEN_DIR.glob(f'{prefix}*.npz') if not p.stem.startswith('act_layers'))
+
+
+# (module name, constructor arguments, act_func string) in the order of tests/golden/make_golden.py.
+ACT_LAYERS = [('Sigmoid', {}, 'sigmoid'), ('LogSigmoid', {}, 'logsigmoid'), ('Tanh', {}, 'tanh'),
+              ('ReLU', {}, 'relu'), ('GELU', {}, 'gelu'), ('GELU', {'approximate': 'tanh'}, 'geluapprox'),
+              ('SiLU', {}, 'silu'), ('ReLU6', {}, 'relu6'), ('Hardsigmoid', {}, 'hardsigmoid'),
+              ('Hardtanh', {}, 'hardtanh'), ('Hardswish', {}, 'hardswish'), ('SELU', {}, 'selu'),
+              ('Mish', {}, 'mish'), ('Softplus', {}, 'softplus'), ('Softsign', {}, 'softsign'),
+              ('Tanhshrink', {}, 'tanhshrink'), ('LeakyReLU', {'negative_slope': 0.01}, 'leaky_relu_0.01'),
+              ('ELU', {'alpha': 1.0}, 'elu_1.0'), ('CELU', {'alpha': 1.0}, 'celu_1.0'),
+              ('Hardshrink', {'lambd': 0.5}, 'hardshrink_0.5'), ('Softshrink', {'lambd': 0.5}, 'softshrink_0.5')]
+
+
+def load_act_layer_golden():
+    """The reference's activation-layer vectors: dict of torch tensors keyed as in the .npz."""
+    raw = np.load(GOLDEN_DIR / 'act_layers_fp32.npz')
+    return {key: torch.from_numpy(raw[key]) for key in raw.files}
 
 
 def config1_inputs():
