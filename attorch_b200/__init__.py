@@ -8,15 +8,17 @@ Public surface (mirrors the reference's for this path, attorch/__init__.py:7-22)
     check_status      raise if a kernel reported a device-side time-out
     Sigmoid ... Softshrink, ActFuncAutoGrad
                       the standalone activation layers with fused dropout (attorch/act_layers.py)
+    set_dropout_stream
+                      the reference's dropout mask (default) or a cheaper generator
 """
 
 from .act_layers import (CELU, ELU, GELU, SELU, ActFuncAutoGrad, Hardshrink, Hardsigmoid, Hardswish,
                          Hardtanh, LeakyReLU, LogSigmoid, Mish, ReLU, ReLU6, Sigmoid, SiLU, Softplus,
-                         Softshrink, Softsign, Tanh, Tanhshrink)
+                         Softshrink, Softsign, Tanh, Tanhshrink, set_dropout_stream)
 from .linear_layer import (Linear, LinearAutoGrad, check_status, get_output_dtype, set_gemm_flags,
                            set_save_derivative)
 
 __all__ = ['Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags',
-           'set_save_derivative', 'ActFuncAutoGrad', 'CELU', 'ELU', 'GELU', 'SELU', 'Hardshrink',
+           'set_save_derivative', 'set_dropout_stream', 'ActFuncAutoGrad', 'CELU', 'ELU', 'GELU', 'SELU', 'Hardshrink',
            'Hardsigmoid', 'Hardswish', 'Hardtanh', 'LeakyReLU', 'LogSigmoid', 'Mish', 'ReLU', 'ReLU6',
            'Sigmoid', 'SiLU', 'Softplus', 'Softshrink', 'Softsign', 'Tanh', 'Tanhshrink']

@@ -22,6 +22,7 @@ FLAG_NO_PAIR = 16
 FLAG_NO_TMA_STORE = 32
 FLAG_SAVE_DERIVATIVE = 64
 FLAG_WHOLE_TILES = 128
+FLAG_DROPOUT_PACKED = 256
 ACT_SAVED_DERIVATIVE = 22
 
 PATH_TCGEN05, PATH_STREAMK, PATH_GENERIC = 1, 2, 3
@@ -56,9 +57,11 @@ SIGNATURES = {
     'ab200_linear_backward_weight': (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64,
                                             _i64, _i64, _i64, _i64, _i64,
                                             _int, _int, _ptr, _i64, _ptr, _ptr, _int]),
-    'ab200_act_forward': (_int, [_ptr, _ptr, _i64, _int, _int, _f32, _f32, ctypes.c_uint32, _ptr]),
-    'ab200_act_input_grad': (_int, [_ptr, _ptr, _ptr, _i64, _int, _int, _f32, _f32, ctypes.c_uint32, _ptr]),
-    'ab200_dropout_uniform': (_f32, [ctypes.c_uint32, ctypes.c_uint64]),
+    'ab200_act_forward': (_int, [_ptr, _ptr, _i64, _int, _int, _f32, _f32, ctypes.c_uint32, _ptr, _int]),
+    'ab200_act_input_grad': (_int, [_ptr, _ptr, _ptr, _i64, _int, _int, _f32, _f32, ctypes.c_uint32, _ptr,
+                                    _int]),
+    'ab200_dropout_uniform': (_f32, [ctypes.c_uint32, ctypes.c_uint64, _int]),
+    'ab200_dropout_threshold': (ctypes.c_uint32, [_f32, _int]),
     'ab200_cast_2d': (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _int, _int, _ptr]),
 }
 

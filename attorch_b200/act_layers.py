@@ -7,6 +7,9 @@ Same constructors (``drop_p`` and, where the PyTorch base class has them, ``inpl
 activation's parameter), same behaviour: the output has the input's shape and dtype, dropout is
 applied after the activation while ``training`` and ``drop_p > 0``, the seed is drawn with
 ``random.randint(0, 65535)`` per forward call, and backward regenerates the mask from the seed.
+The mask is the reference's own: the same seed (hence the same ``random.seed``) drops the same
+elements as ``tl.rand`` does there (attorch/dropout_kernels.py:26).  ``set_dropout_stream('packed')``
+switches to a generator that does a quarter of the integer work and yields a different mask.
 """
 
 import warnings
@@ -19,6 +22,21 @@ from torch import Tensor, nn
 from . import _lib
 from .acts import act_id, parse_act_func
 from .linear_layer import _dtype_id, _require_cuda
+
+
+_dropout_flags = 0
+
+
+def set_dropout_stream(stream: str) -> None:
+    """
+    Chooses the generator behind the dropout mask of layers called from now on: ``'reference'``
+    (default; bit-identical to the reference's mask for a given seed, one Philox block per element)
+    or ``'packed'`` (one Philox block per four elements; faster on 2-byte tensors, other mask).
+    """
+    global _dropout_flags
+    if stream not in ('reference', 'packed'):
+        raise ValueError(f"dropout stream must be 'reference' or 'packed', received {stream!r}")
+    _dropout_flags = _lib.FLAG_DROPOUT_PACKED if stream == 'packed' else 0
 
 
 class ActFuncAutoGrad(torch.autograd.Function):
@@ -35,6 +53,7 @@ class ActFuncAutoGrad(torch.autograd.Function):
         ctx.drop_p = float(drop_p)
         ctx.dropout = drop_p > 0 and training
         ctx.seed = randint(0, 65535) if ctx.dropout else 0
+        ctx.flags = _dropout_flags
         if input.requires_grad:
             ctx.save_for_backward(input)
 
@@ -44,7 +63,7 @@ class ActFuncAutoGrad(torch.autograd.Function):
             _lib.check(_lib.load().ab200_act_forward(
                 flattened_input.data_ptr(), output.data_ptr(), flattened_input.numel(),
                 _dtype_id(input.dtype), ctx.act, ctx.param, ctx.drop_p if ctx.dropout else 0.0,
-                ctx.seed, torch.cuda.current_stream().cuda_stream), 'ab200_act_forward')
+                ctx.seed, torch.cuda.current_stream().cuda_stream, ctx.flags), 'ab200_act_forward')
         return output.view(input.shape)
 
     @staticmethod
@@ -58,7 +77,7 @@ class ActFuncAutoGrad(torch.autograd.Function):
                 output_grad.data_ptr(), flattened_input.data_ptr(), input_grad.data_ptr(),
                 flattened_input.numel(), _dtype_id(input.dtype), ctx.act, ctx.param,
                 ctx.drop_p if ctx.dropout else 0.0, ctx.seed,
-                torch.cuda.current_stream().cuda_stream), 'ab200_act_input_grad')
+                torch.cuda.current_stream().cuda_stream, ctx.flags), 'ab200_act_input_grad')
         return input_grad.view(input.shape), None, None, None
 
 

@@ -5,10 +5,17 @@
 //   forward    y  = keep ? act(x) / (1 - p) : 0          keep = (u(seed, index) >= p)
 //   backward   dx = (keep ? dy / (1 - p) : 0) * act'(x)
 //
-// u(seed, index) is a counter-based generator (Philox 4x32 with 10 rounds, key = (seed, 0), counter
-// = (index / 4, 0, 0, 0), word index % 4, top 24 bits -> [0, 1)), so forward and backward see the
-// same mask without storing it, as in the reference; the stream itself is this library's own (the
-// reference's comes from Triton's tl.rand and is not reproduced bit for bit).
+// u(seed, index) comes from a counter-based generator (Philox 4x32 with 10 rounds, key = (seed, 0)),
+// so forward and backward see the same mask without storing it.  Two streams:
+//
+//   reference (default)  the numbers Triton's tl.rand(seed, offset) yields, which the reference draws
+//                        (attorch/dropout_kernels.py:26): counter (uint32(index), 0, 0, 0), first output
+//                        word w, as int32 mirrored onto [0, 2^31) (w < 0 ? -w - 1 : w), converted to
+//                        fp32 and scaled by 4.6566127342e-10.  Same seed, same mask as the reference.
+//                        One Philox block per element: 17 32x32->64-bit multiplies, which makes the
+//                        2-byte kernels ALU-bound rather than HBM-bound.
+//   packed               counter (index / 4, 0, 0, 0), word index % 4, top 24 bits -> [0, 1): one block
+//                        per four elements, a quarter of the integer work; a different mask.
 #pragma once
 #include "act_math.cuh"
 #include "common.cuh"
@@ -32,18 +39,63 @@ __host__ __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1,
   out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
 }
 
-// Uniform number in [0, 1) for element `index` of the stream `seed`.
-__host__ __device__ __forceinline__ float dropout_uniform(uint32_t seed, uint64_t index) {
+enum DropoutStream : int { DROPOUT_OFF = 0, DROPOUT_REFERENCE = 1, DROPOUT_PACKED = 2 };
+
+// A word taken as int32 and mirrored onto [0, 2^31): w < 0 ? -w - 1 : w.
+__host__ __device__ __forceinline__ uint32_t mirrored_word(uint32_t w) {
+  return w ^ static_cast<uint32_t>(static_cast<int32_t>(w) >> 31);
+}
+
+__host__ __device__ __forceinline__ float reference_uniform_of(uint32_t mirrored) {
+  return static_cast<float>(static_cast<int32_t>(mirrored)) * 4.6566127342e-10f;
+}
+
+// First output word of the block with counter (c0, 0, 0, 0) -> uniform fp32 in [0, 1), as tl.rand does it.
+__host__ __device__ __forceinline__ float reference_uniform(uint32_t seed, uint32_t c0) {
   uint32_t r[4];
-  philox4x32_10(static_cast<uint32_t>(index >> 2), static_cast<uint32_t>(index >> 34), 0u, 0u, seed, 0u, r);
-  return static_cast<float>(r[index & 3] >> 8) * (1.0f / 16777216.0f);
+  philox4x32_10(c0, 0u, 0u, 0u, seed, 0u, r);
+  return reference_uniform_of(mirrored_word(r[0]));
+}
+
+__host__ __device__ __forceinline__ float packed_uniform(uint32_t word) {
+  return static_cast<float>(word >> 8) * (1.0f / 16777216.0f);
+}
+
+// Uniform number in [0, 1) for element `index` of the stream `seed`.
+__host__ __device__ __forceinline__ float dropout_uniform(uint32_t seed, uint64_t index, int stream) {
+  if (stream == DROPOUT_PACKED) {
+    uint32_t r[4];
+    philox4x32_10(static_cast<uint32_t>(index >> 2), static_cast<uint32_t>(index >> 34), 0u, 0u, seed, 0u, r);
+    return packed_uniform(r[index & 3]);
+  }
+  return reference_uniform(seed, static_cast<uint32_t>(index));
+}
+
+// The integer t with  u < drop_p  <=>  m < t, where m is the mirrored word (reference stream) or the
+// raw word (packed stream) u is made from: both conversions are monotonic in m, so the float
+// comparison has an exact integer form.  0 <= drop_p < 1.
+inline uint32_t dropout_threshold(float drop_p, int stream) {
+  if (stream == DROPOUT_PACKED) {
+    // float(word >> 8) / 2^24 < p  <=>  (word >> 8) < ceil(p 2^24)  <=>  word < ceil(p 2^24) << 8.
+    const double scaled = static_cast<double>(drop_p) * 16777216.0;
+    uint64_t t = static_cast<uint64_t>(scaled);
+    if (static_cast<double>(t) < scaled) ++t;
+    return static_cast<uint32_t>(t << 8);
+  }
+  // Smallest m in [0, 2^31] with float(m) * scale >= drop_p, by bisection.
+  uint64_t lo = 0, hi = 1ull << 31;   // invariant: u(m) < p for m < lo, u(m) >= p for m >= hi
+  while (lo < hi) {
+    const uint64_t mid = (lo + hi) / 2;
+    if (reference_uniform_of(static_cast<uint32_t>(mid)) < drop_p) lo = mid + 1; else hi = mid;
+  }
+  return static_cast<uint32_t>(lo);
 }
 
 // kBackward = false: y = dropout(act(x));  true: dx = dropout_grad(dy) * act'(x).
 template <class T, bool kBackward>
 __global__ void __launch_bounds__(256)
 act_elementwise_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restrict__ out, long long n,
-                       int act, float param, float drop_p, uint32_t seed, int dropout) {
+                       int act, float param, float drop_p, uint32_t seed, int dropout, uint32_t threshold) {
   const float keep_scale = dropout ? 1.0f / (1.0f - drop_p) : 1.0f;
   const long long groups = (n + 7) / 8;
   const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
@@ -85,19 +137,24 @@ act_elementwise_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __r
       for (int i = 0; i < 8; ++i) res[i] = xv[i];
       act_fwd_inplace(res, act, param);
     }
-    if (dropout) {
+    // "u < drop_p" as an integer comparison with dropout_threshold(): no int -> float conversion.
+    if (dropout == DROPOUT_REFERENCE) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint32_t r[4];
+        philox4x32_10(static_cast<uint32_t>(base + i), 0u, 0u, 0u, seed, 0u, r);
+        res[i] = (mirrored_word(r[0]) < threshold) ? 0.0f : res[i] * keep_scale;
+      }
+    } else if (dropout == DROPOUT_PACKED) {
       // Two Philox blocks cover the 8 consecutive indices of this group.
-      uint32_t r[8];
       uint32_t a[4], b[4];
       const uint64_t blk = static_cast<uint64_t>(base) >> 2;
       philox4x32_10(static_cast<uint32_t>(blk), static_cast<uint32_t>(blk >> 32), 0u, 0u, seed, 0u, a);
       philox4x32_10(static_cast<uint32_t>(blk + 1), static_cast<uint32_t>((blk + 1) >> 32), 0u, 0u, seed, 0u, b);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { r[i] = a[i]; r[4 + i] = b[i]; }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float u = static_cast<float>(r[i] >> 8) * (1.0f / 16777216.0f);
-        res[i] = (u < drop_p) ? 0.0f : res[i] * keep_scale;
+      for (int i = 0; i < 4; ++i) {
+        res[i] = (a[i] < threshold) ? 0.0f : res[i] * keep_scale;
+        res[4 + i] = (b[i] < threshold) ? 0.0f : res[4 + i] * keep_scale;
       }
     }
     if (full) {

@@ -516,14 +516,16 @@ extern "C++" {
 namespace {
 template <bool kBackward>
 int launch_act_elementwise(const void* x, const void* dy, void* out, int64_t n, int dtype, int act,
-                           float act_param, float drop_p, uint32_t seed, cudaStream_t stream) {
+                           float act_param, float drop_p, uint32_t seed, cudaStream_t stream, int flags) {
   if (n < 0) return ERR_BAD_SHAPE;
   if (!valid_dtype(dtype)) return ERR_BAD_DTYPE;
   if (!valid_act(act)) return ERR_BAD_ACT;
   if (!(drop_p >= 0.0f && drop_p < 1.0f)) return ERR_BAD_SHAPE;
   if (n == 0) return OK;
   if (!x || !out || (kBackward && !dy)) return ERR_NULL_POINTER;
-  const int dropout = drop_p > 0.0f ? 1 : 0;
+  const int dropout = drop_p > 0.0f ? ((flags & AB200_FLAG_DROPOUT_PACKED) ? DROPOUT_PACKED : DROPOUT_REFERENCE)
+                                    : DROPOUT_OFF;
+  const uint32_t threshold = dropout ? dropout_threshold(drop_p, dropout) : 0u;
   const long long groups = (n + 7) / 8;
   long long blocks = (groups + 255) / 256;
   const long long cap = static_cast<long long>(sm_count()) * 16;
@@ -531,7 +533,7 @@ int launch_act_elementwise(const void* x, const void* dy, void* out, int64_t n, 
 #define AB200_ACT_EW(T)                                                                                 \
   act_elementwise_kernel<T, kBackward><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(              \
       static_cast<const T*>(x), static_cast<const T*>(dy), static_cast<T*>(out), n, act, act_param,     \
-      drop_p, seed, dropout)
+      drop_p, seed, dropout, threshold)
   if (dtype == DT_F32) AB200_ACT_EW(float);
   else if (dtype == DT_F16) AB200_ACT_EW(__half);
   else AB200_ACT_EW(__nv_bfloat16);
@@ -543,18 +545,24 @@ int launch_act_elementwise(const void* x, const void* dy, void* out, int64_t n, 
 }  // extern "C++"
 
 int ab200_act_forward(const void* x, void* y, int64_t n, int dtype, int act, float act_param, float drop_p,
-                      uint32_t seed, void* stream) {
+                      uint32_t seed, void* stream, int flags) {
   return launch_act_elementwise<false>(x, nullptr, y, n, dtype, act, act_param, drop_p, seed,
-                                       static_cast<cudaStream_t>(stream));
+                                       static_cast<cudaStream_t>(stream), flags);
 }
 
 int ab200_act_input_grad(const void* dy, const void* x, void* dx, int64_t n, int dtype, int act,
-                         float act_param, float drop_p, uint32_t seed, void* stream) {
+                         float act_param, float drop_p, uint32_t seed, void* stream, int flags) {
   return launch_act_elementwise<true>(x, dy, dx, n, dtype, act, act_param, drop_p, seed,
-                                      static_cast<cudaStream_t>(stream));
+                                      static_cast<cudaStream_t>(stream), flags);
 }
 
-float ab200_dropout_uniform(uint32_t seed, uint64_t index) { return dropout_uniform(seed, index); }
+uint32_t ab200_dropout_threshold(float drop_p, int flags) {
+  return dropout_threshold(drop_p, (flags & AB200_FLAG_DROPOUT_PACKED) ? DROPOUT_PACKED : DROPOUT_REFERENCE);
+}
+
+float ab200_dropout_uniform(uint32_t seed, uint64_t index, int flags) {
+  return dropout_uniform(seed, index, (flags & AB200_FLAG_DROPOUT_PACKED) ? DROPOUT_PACKED : DROPOUT_REFERENCE);
+}
 
 int ab200_cast_2d(const void* src, void* dst, int64_t rows, int64_t cols, int64_t src_stride_r,
                   int64_t src_stride_c, int src_dtype, int dst_dtype, void* stream_) {

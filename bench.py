@@ -14,6 +14,7 @@ Workloads (synthetic, seeded; shapes of BASELINE.json's configs):
       split over the N GPUs (strong scaling), same all-reduce.
   c3  transformer MLP pair 4096 -> 14336 (silu) -> 4096, no biases, bf16, 16384 tokens per GPU.
   c4  skinny forward only, fp16, 8192 -> 28672, M in {1, 8, 32, 128}: prints weight-read GB/s.
+  act standalone activation layer (GELU, drop_p = 0.1, bf16, 8192 x 4096 elements): GB/s.
 
 One "step" is one forward + backward of the workload on one batch.  ``value`` is the whole-job
 TFLOP/s at 6 * M * K * N floating-point operations per layer and step with the inputs resident in
@@ -289,12 +290,84 @@ def skinny_forward(args, device, lib):
                                    'peak_source': peak_source}}), flush=True)
 
 
+def activation_layer(args, device):
+    """
+    The standalone activation layer with fused dropout (the row after the linear layer in the scope
+    table): GELU with drop_p = 0.1 on a bf16 [32768, 4096] tensor (268 MB, larger than L2), forward and
+    input gradient, timed through the C ABI (the kernels alone) and through attorch_b200.GELU (with
+    the host work of the module around them).  HBM-bound: algorithmic bytes are 2 n e forward (read x,
+    write y) and 3 n e backward (read dy and x, write dx).
+    """
+    import attorch_b200
+    from attorch_b200 import _lib
+    from attorch_b200.acts import act_id, parse_act_func
+    lib = _lib.load()
+    peaks, peak_source = measured_peaks()
+    n_rows, n_cols = 32768, 4096
+    n = n_rows * n_cols
+    x = torch.randn(n_rows, n_cols, device=device).bfloat16()
+    dy = torch.randn(n_rows, n_cols, device=device).bfloat16()
+    out = torch.empty_like(x)
+    act, param = act_id(parse_act_func('gelu')[0]), 0.0
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def kernel_forward(flags=0):
+        rc = lib.ab200_act_forward(x.data_ptr(), out.data_ptr(), n, _lib.BF16, act, param, 0.1, 7, stream, flags)
+        assert rc == 0, rc
+
+    def kernel_backward(flags=0):
+        rc = lib.ab200_act_input_grad(dy.data_ptr(), x.data_ptr(), out.data_ptr(), n, _lib.BF16, act, param,
+                                      0.1, 7, stream, flags)
+        assert rc == 0, rc
+
+    def kernel_forward_no_dropout():
+        rc = lib.ab200_act_forward(x.data_ptr(), out.data_ptr(), n, _lib.BF16, act, param, 0.0, 0, stream, 0)
+        assert rc == 0, rc
+
+    layer = attorch_b200.GELU(drop_p=0.1)
+    layer.train()
+    xg = x.clone().requires_grad_(True)
+
+    def module_step():
+        layer(xg).backward(dy)
+        xg.grad = None
+
+    packed = _lib.FLAG_DROPOUT_PACKED
+    results = {}
+    for name, fn, nbytes in (('kernel_forward', kernel_forward, 2 * n * 2.0),
+                             ('kernel_backward', kernel_backward, 3 * n * 2.0),
+                             ('kernel_forward_packed_stream', lambda: kernel_forward(packed), 2 * n * 2.0),
+                             ('kernel_backward_packed_stream', lambda: kernel_backward(packed), 3 * n * 2.0),
+                             ('kernel_forward_no_dropout', kernel_forward_no_dropout, 2 * n * 2.0),
+                             ('module_forward_backward', module_step, 5 * n * 2.0)):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / args.steps
+        results[name] = {'us': round(ms * 1e3, 2), 'gbs': round(nbytes / (ms * 1e-3) / 1e9, 1)}
+    best = results['kernel_forward']['gbs']
+    print(json.dumps({'metric': 'activation_layer_gbs', 'value': best, 'unit': 'GB/s', 'n_gpus': 1,
+                      'steps': args.steps, 'warmup': args.warmup, 'higher_is_better': True, 'dtype': 'bf16',
+                      'data': 'synthetic',
+                      'config': {'workload': 'act', 'layer': 'GELU(drop_p=0.1)', 'shape': [n_rows, n_cols],
+                                 'l2': 'inputs larger than L2', **results},
+                      'roofline': {'bound': 'hbm', 'achieved': best, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
+                                   'frac': best / peaks['hbm_gbs'], 'traffic': None, 'peak_source': peak_source}}),
+          flush=True)
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     parser.add_argument('--gpus', type=int, default=1)
     parser.add_argument('--steps', type=int, default=200)
     parser.add_argument('--warmup', type=int, default=10)
-    parser.add_argument('--workload', choices=sorted(WORKLOADS) + ['c4'], default='c2')
+    parser.add_argument('--workload', choices=sorted(WORKLOADS) + ['c4', 'act'], default='c2')
     parser.add_argument('--impl', choices=['b200', 'reference'], default='b200')
     parser.add_argument('--no-cpu-baseline', action='store_true')
     parser.add_argument('--no-graph', action='store_true',
@@ -305,13 +378,16 @@ def main():
                         help='override the tokens per GPU (profiling of reduced cases)')
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.workload == 'c4':
+    if args.workload in ('c4', 'act'):
         if args.impl == 'reference':
-            print(json.dumps({'impl': 'reference', 'unavailable': 'c4 has no CPU arm; use c2'}))
+            print(json.dumps({'impl': 'reference', 'unavailable': f'{args.workload} has no CPU arm; use c2'}))
             return
         from attorch_b200 import _lib
         torch.cuda.set_device(0)
-        skinny_forward(args, torch.device('cuda', 0), _lib.load())
+        if args.workload == 'c4':
+            skinny_forward(args, torch.device('cuda', 0), _lib.load())
+        else:
+            activation_layer(args, torch.device('cuda', 0))
         return
     spec = WORKLOADS[args.workload]
 

@@ -90,6 +90,7 @@ extern "C" {
 #define AB200_FLAG_NO_TMA_STORE 32  /* epilogue stores from registers, not through TMA           */
 #define AB200_FLAG_SAVE_DERIVATIVE 64 /* forward: pre_act receives act'(Z) instead of Z            */
 #define AB200_FLAG_WHOLE_TILES 128  /* never share out a partial last round of tiles            */
+#define AB200_FLAG_DROPOUT_PACKED 256 /* activation layers: the cheaper dropout stream (see below) */
 
 /* Which kernel the last call on this host thread chose: 1 tcgen05 tile-parallel, 2 tcgen05
  * swap-AB stream-K, 3 generic CUDA-core.  For tests and benchmarks. */
@@ -232,25 +233,37 @@ int ab200_linear_backward_weight(const void* x, const void* dz, void* dw, int64_
  * attorch/act_layers.py:66-73) with apply_dropout (attorch/dropout_kernels.py:12-28).  x, y: n
  * contiguous elements of `dtype`; act != AB200_ACT_NONE is not required (identity + dropout works).
  * drop_p = 0 switches dropout off; otherwise element i is dropped iff
- * ab200_dropout_uniform(seed, i) < drop_p.
+ * ab200_dropout_uniform(seed, i, flags) < drop_p.  flags: 0 or AB200_FLAG_DROPOUT_PACKED.
  */
 int ab200_act_forward(const void* x, void* y, int64_t n, int dtype, int act, float act_param, float drop_p,
-                      uint32_t seed, void* stream);
+                      uint32_t seed, void* stream, int flags);
 
 /*
  * Its backward:  dx[i] = (keep_i ? dy[i] / (1 - p) : 0) * act'(x[i]), same mask as forward for the
- * same seed.  Replaces act_func_backward_kernel (attorch/act_kernels.py:883-927, launched at
- * attorch/act_layers.py:106-110) with apply_dropout_grad (attorch/dropout_kernels.py:31-46).
+ * same seed and flags.  Replaces act_func_backward_kernel (attorch/act_kernels.py:883-927, launched
+ * at attorch/act_layers.py:106-110) with apply_dropout_grad (attorch/dropout_kernels.py:31-46).
  */
 int ab200_act_input_grad(const void* dy, const void* x, void* dx, int64_t n, int dtype, int act,
-                         float act_param, float drop_p, uint32_t seed, void* stream);
+                         float act_param, float drop_p, uint32_t seed, void* stream, int flags);
 
 /*
- * The uniform number in [0, 1) the dropout mask compares with drop_p (host function; Philox 4x32-10,
- * key (seed, 0), counter index / 4, word index % 4, top 24 bits).  The reference draws its numbers
- * with Triton's tl.rand(seed, offset) (attorch/dropout_kernels.py:25); the streams differ.
+ * The uniform number in [0, 1) the dropout mask compares with drop_p (host function).
+ * flags = 0: the number the reference draws for the same seed and element, tl.rand(seed, offset)
+ * (attorch/dropout_kernels.py:26) - Philox 4x32-10 with key (seed, 0) and counter
+ * (uint32(index), 0, 0, 0); the first output word w as int32, mirrored (w < 0 ? -w - 1 : w),
+ * converted to fp32 and multiplied by 4.6566127342e-10 - so that a given seed drops the same
+ * elements here and there.  AB200_FLAG_DROPOUT_PACKED: counter index / 4, word index % 4, top 24
+ * bits: a quarter of the integer work (one block per four elements), a different mask.
  */
-float ab200_dropout_uniform(uint32_t seed, uint64_t index);
+float ab200_dropout_uniform(uint32_t seed, uint64_t index, int flags);
+
+/*
+ * The integer form of "ab200_dropout_uniform(...) < drop_p" the kernels use (host function; no
+ * counterpart in the reference): element i is dropped iff m < ab200_dropout_threshold(drop_p, flags),
+ * m being the Philox word of element i - mirrored (w < 0 ? -w - 1 : w) with flags = 0, as it is with
+ * AB200_FLAG_DROPOUT_PACKED.  Exact, because the word -> fp32 conversions are monotonic.
+ */
+uint32_t ab200_dropout_threshold(float drop_p, int flags);
 
 /*
  * dst[r, c] (contiguous, dst_dtype) = src[r * src_stride_r + c * src_stride_c] (src_dtype).

@@ -306,9 +306,9 @@ def philox4x32_10(counter: 'np.ndarray', seed: int) -> 'np.ndarray':
     """
     Philox 4x32 with 10 rounds (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", 2011)
     for counters (c, 0, 0, 0) with c a uint64 array split into two 32-bit words, key (seed, 0).
-    Returns an array [..., 4] of uint32.  This is the generator of the CUDA library's dropout mask
-    (csrc/act_elementwise.cuh); the reference's mask comes from Triton's tl.rand
-    (attorch/dropout_kernels.py:25) and is a different stream.
+    Returns an array [..., 4] of uint32.  Triton's tl.rand, from which the reference draws its
+    dropout mask (attorch/dropout_kernels.py:26), is built on the same generator (triton 3.x,
+    triton/language/random.py: philox, randint, uint_to_uniform_float).
     """
     import numpy as np
     c = np.asarray(counter, dtype=np.uint64)
@@ -331,14 +331,31 @@ def philox4x32_10(counter: 'np.ndarray', seed: int) -> 'np.ndarray':
     return np.stack([c0, c1, c2, c3], axis=-1).astype(np.uint32)
 
 
-def dropout_uniform(seed: int, n: int) -> Tensor:
-    """The n uniform numbers in [0, 1) that decide the dropout mask of elements 0 .. n-1."""
+def dropout_uniform(seed: int, n: int, stream: str = 'reference') -> Tensor:
+    """
+    The n uniform numbers in [0, 1) that decide the dropout mask of elements 0 .. n-1.
+
+    'reference': tl.rand(seed, offset) as the reference calls it (attorch/dropout_kernels.py:26 with
+    the int32 offsets of attorch/act_kernels.py:869-870): one Philox block per element, counter
+    (offset, 0, 0, 0); its first word as int32, mirrored onto the non-negative half
+    (w < 0 ? -w - 1 : w), converted to fp32 and scaled by 4.6566127342e-10.
+    'packed': the CUDA library's cheaper stream: block index // 4, word index % 4, top 24 bits.
+    """
     import numpy as np
-    blocks = philox4x32_10(np.arange((n + 3) // 4, dtype=np.uint64), seed).reshape(-1)[:n]
-    return torch.from_numpy(((blocks >> np.uint32(8)).astype(np.float32) / np.float32(16777216.0)))
+    if stream == 'packed':
+        blocks = philox4x32_10(np.arange((n + 3) // 4, dtype=np.uint64), seed).reshape(-1)[:n]
+        return torch.from_numpy(((blocks >> np.uint32(8)).astype(np.float32) / np.float32(16777216.0)))
+    if stream != 'reference':
+        raise ValueError(stream)
+    words = philox4x32_10(np.arange(n, dtype=np.uint64) & np.uint64(0xFFFFFFFF), seed)[..., 0]
+    signed = words.astype(np.int64)
+    signed = np.where(signed >= 2 ** 31, signed - 2 ** 32, signed)
+    mirrored = np.where(signed < 0, -signed - 1, signed)
+    return torch.from_numpy(mirrored.astype(np.float32) * np.float32(4.6566127342e-10))
 
 
-def act_layer_forward(x: Tensor, act_func: str, drop_p: float = 0.0, seed: int = 0) -> Tensor:
+def act_layer_forward(x: Tensor, act_func: str, drop_p: float = 0.0, seed: int = 0,
+                      stream: str = 'reference') -> Tensor:
     """
     act_func_forward_kernel (attorch/act_kernels.py:840-880): the activation (in fp32 for the
     activations of FP32_ACTS, else in x's dtype), then apply_dropout
@@ -349,12 +366,13 @@ def act_layer_forward(x: Tensor, act_func: str, drop_p: float = 0.0, seed: int =
     z = x.float() if name in FP32_ACTS else x
     y = act_forward(name, z, param)
     if drop_p > 0:
-        u = dropout_uniform(seed, x.numel()).view(x.shape)
+        u = dropout_uniform(seed, x.numel(), stream).view(x.shape)
         y = torch.where(u < drop_p, torch.zeros((), dtype=y.dtype), y / (1 - drop_p))
     return y.to(x.dtype)
 
 
-def act_layer_backward(dy: Tensor, x: Tensor, act_func: str, drop_p: float = 0.0, seed: int = 0) -> Tensor:
+def act_layer_backward(dy: Tensor, x: Tensor, act_func: str, drop_p: float = 0.0, seed: int = 0,
+                       stream: str = 'reference') -> Tensor:
     """
     act_func_backward_kernel (attorch/act_kernels.py:883-927): apply_dropout_grad
     (attorch/dropout_kernels.py:31-46) on dy, times act'(x); stored in x's dtype.
@@ -363,6 +381,6 @@ def act_layer_backward(dy: Tensor, x: Tensor, act_func: str, drop_p: float = 0.0
     z = x.float() if name in FP32_ACTS else x
     g = dy
     if drop_p > 0:
-        u = dropout_uniform(seed, x.numel()).view(x.shape)
+        u = dropout_uniform(seed, x.numel(), stream).view(x.shape)
         g = torch.where(u < drop_p, torch.zeros((), dtype=dy.dtype), dy / (1 - drop_p))
     return (g * act_grad(name, z, param)).to(x.dtype)

@@ -173,24 +173,30 @@ def act_layer_goldens(attorch):
     """
     The reference's standalone activation layers (attorch/act_layers.py): for every layer class the
     output and input gradient on a seeded input that also contains the piecewise switch points, without
-    dropout and with drop_p = 0.5 (whose mask comes from Triton's generator; the vectors pin what a
-    dropped and a kept element look like, not which elements are dropped).
+    dropout and with drop_p = 0.5 and 0.3.  The layer draws its dropout seed with random.randint(0, 65535)
+    (attorch/act_layers.py:54); Python's generator is seeded just before, and the seed the layer drew is
+    stored beside the result, so that the vectors pin WHICH elements are dropped for a given seed.
     """
+    import random
     gen = torch.Generator().manual_seed(4)
     x = torch.randn(6, 40, generator=gen) * 2
     x[0, :12] = torch.tensor([-6.0, -3.0, -1.0, -0.5, 0.0, 0.5, 1.0, 3.0, 6.0, 7.0, -7.0, 2.0])
     dy = torch.randn(6, 40, generator=gen)
     data = {'x': x.numpy(), 'dy': dy.numpy()}
     for index, (name, kwargs) in enumerate(ACT_LAYERS):
-        for drop_p in (0.0, 0.5):
+        for drop_p, label in ((0.0, 'plain'), (0.5, 'drop'), (0.3, 'drop30')):
             layer = getattr(attorch, name)(drop_p=drop_p, **kwargs)
             layer.train()
             xin = x.clone().requires_grad_(True)
+            random.seed(1000 + 3 * index + len(label))
+            drawn = random.randint(0, 65535)
+            random.seed(1000 + 3 * index + len(label))
             y = layer(xin)
             y.backward(dy)
-            tag = f'{index:02d}_{name}_{"drop" if drop_p else "plain"}'
+            tag = f'{index:02d}_{name}_{label}'
             data[f'y_{tag}'] = y.detach().numpy()
             data[f'dx_{tag}'] = xin.grad.numpy()
+            data[f'seed_{tag}'] = np.array(drawn)
     np.savez_compressed(OUT_DIR / 'act_layers_fp32.npz', **data)
     print('wrote act_layers_fp32.npz')
 
