@@ -37,6 +37,7 @@ SIGNATURES = {
     'ab200_version': (_int, []),
     'ab200_error_string': (ctypes.c_char_p, [_int]),
     'ab200_last_path': (_int, []),
+    'ab200_last_schedule': (_int, []),
     'ab200_launch_count': (_i64, []),
     'ab200_set_gemm_cta_limit': (_int, [_int]),
     'ab200_forward_workspace_bytes': (_i64, [_i64, _i64, _i64, _int]),

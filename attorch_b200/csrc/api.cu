@@ -136,6 +136,7 @@ int run_tiles_or_split(TcProblem& p, void* workspace, int64_t workspace_bytes, c
   if (!(flags & AB200_FLAG_WHOLE_TILES)) {
     p.tail_workspace = workspace;
     p.tail_workspace_bytes = workspace_bytes;
+    p.allow_split_tail = true;
   }
   g_last_path = AB200_PATH_TCGEN05;
   return launch_tc_counted(p, bn, stream);
@@ -173,6 +174,7 @@ const char* ab200_error_string(int code) {
 }
 
 int ab200_last_path(void) { return g_last_path; }
+int ab200_last_schedule(void) { return last_schedule(); }
 int ab200_set_gemm_cta_limit(int ctas) {
   const int previous = gemm_cta_limit();
   set_gemm_cta_limit(ctas);

@@ -97,6 +97,14 @@ int raster_group_m() {
 int gemm_cta_limit() { return g_cta_limit.load(std::memory_order_relaxed); }
 void set_gemm_cta_limit(int ctas) { g_cta_limit.store(ctas < 0 ? 0 : ctas, std::memory_order_relaxed); }
 
+namespace { thread_local int g_last_schedule = 0; }
+int tail_mode_override() {
+  const char* e = std::getenv("AB200_TAIL_MODE");   // read per call: experiments switch it at run time
+  return e == nullptr ? 0 : std::atoi(e);
+}
+int last_schedule() { return g_last_schedule; }
+void set_last_schedule(int mode) { g_last_schedule = mode; }
+
 int launch_tc(const TcProblem& p, int bn, cudaStream_t stream) {
   if (p.op_dtype == DT_F32) {
     if (!p.a_mn && p.b_mn) return launch_tc_4_km(p, bn, stream);

@@ -21,6 +21,8 @@ struct TcProblem {
   int op_dtype;
   bool allow_pair;   // may run as CTA pairs (cta_group::2) where a configuration for it exists
   bool allow_tma_store;   // the epilogue may write its outputs with TMA stores
+  // A partial last round that would keep at most half of the workers busy may run as half-width tiles.
+  bool allow_split_tail;
   // Optional scratch for sharing out a partial last round of tiles (hybrid scheduling).
   void* tail_workspace;
   long long tail_workspace_bytes;
@@ -38,6 +40,14 @@ int raster_group_m();
 // SM leaves none for a collective running beside it; a caller that overlaps the two lowers this.
 int gemm_cta_limit();
 void set_gemm_cta_limit(int ctas);
+
+// Work decomposition (GemmArgs::stream_k) of the last tensor-core GEMM launched from this host thread.
+int last_schedule();
+void set_last_schedule(int mode);
+
+// AB200_TAIL_MODE: unset / 0 = a partial last round of tiles is shared out where that is possible;
+// 3 = it runs as half-width tiles whenever it fills at most half of the workers.
+int tail_mode_override();
 
 // Finishing pass of the hybrid schedule (defined next to the kernel, in api.cu): shared-out tiles
 // [first_tile, first_tile + count) of the launch described by g, tile_m x bn each.
@@ -145,6 +155,18 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   // workers busy), its tiles' reductions are shared out over all workers instead.
   int tail_tiles = 0;
   CUtensorMap tpartial = ta;
+  // Opt-in (AB200_TAIL_MODE=3): a last round filling at most half of the workers runs as twice as
+  // many half-width tiles (one half-length round, fused epilogue, nothing to finish).  Measured on
+  // the 4096 x 4096 x 8192 weight-gradient product it is no faster than whole tiles or the shared-out
+  // round (212-216 us each, same process): sustained GEMMs run at the power limit, where idle SMs
+  // let the busy ones clock higher, so evening out the last round buys nothing there.
+  const int last_round = tiles > workers ? static_cast<int>(tiles % workers) : 0;
+  const int tail_mode = tail_mode_override();
+  if (!g.stream_k && p.allow_split_tail && Cfg::BN >= 64 && last_round > 0 && last_round * 2 <= workers &&
+      tail_mode == 3) {
+    g.stream_k = 3;
+    g.dp_tiles = static_cast<int>(tiles) - last_round;
+  }
   if (!g.stream_k && p.tail_workspace != nullptr && tiles > workers && g.k_blocks >= 16) {
     const int rem = static_cast<int>(tiles % workers);
     // Two slots per worker (its share of the tail touches at most two tiles).
@@ -175,6 +197,7 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   }
   const cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<Cfg>, ta, tb, tout, taux, tpartial, g);
   if (err != cudaSuccess) return ERR_LAUNCH;
+  set_last_schedule(g.stream_k);
   if (tail_tiles > 0)
     return launch_hybrid_finish(g, g.dp_tiles, tail_tiles, workers, Cfg::TILE_M, Cfg::BN, stream);
   return OK;

@@ -48,8 +48,9 @@ struct GemmArgs {
   int tiles_m, tiles_n;   // ceil(M / 128), ceil(N / BN)
   int group_m;            // row-blocks per rasterisation group
   int k_blocks;           // ceil(K / elements per stage)
-  int stream_k;           // 0: whole tiles; 1: equal (tile, k-block) shares + atomics; 2: hybrid
-  int dp_tiles;           // hybrid: tiles computed whole (a multiple of the worker count)
+  int stream_k;           // 0: whole tiles; 1: equal (tile, k-block) shares + atomics; 2: hybrid;
+                          // 3: whole tiles, those of the partial last round as two half-width tiles
+  int dp_tiles;           // modes 2, 3: tiles computed whole (a multiple of the worker count)
   uint32_t idesc;         // tcgen05 instruction descriptor (operand format, majorness, 128 x BN)
   // Direct epilogue
   void* out;              // [M, N], row pitch ld_out elements
@@ -112,6 +113,7 @@ struct GemmCfg {
 
 struct Segment {
   int m_blk, n_blk;
+  int n_off, n_cols;  // columns [n_off, n_off + n_cols) of the tile: all BN of them, or one half
   int kb0, kb1;     // k-block range [kb0, kb1)
   int partial;      // 1: add the result to the fp32 partial sums; 0: whole tile, fused epilogue
   int sk_index;     // hybrid mode: slot of this worker's partial tile (2 * worker + 0 or 1)
@@ -140,6 +142,10 @@ __host__ __device__ __forceinline__ void tile_to_blocks(int t, int tiles_m, int 
 //                 each piece is written, not added, to the worker's own slot (2 * worker, then
 //                 2 * worker + 1) and a finishing kernel sums the slots of a tile in worker order:
 //                 no atomics, no clearing, bit-repeatable.
+//   stream_k = 3  the first dp_tiles tiles whole, as in mode 0; each remaining tile as two units of
+//                 BN / 2 columns (unit h = column half h % 2 of tile dp_tiles + h / 2), handed out
+//                 like tiles.  A last round that would occupy at most half of the workers then takes
+//                 half as long, and every unit still ends in the fused epilogue.
 struct SegmentIter {
   long long unit, unit_end;   // position in the shared-out (tile, k-block) units
   int tile, tile_end;         // next whole tile
@@ -152,17 +158,34 @@ struct SegmentIter {
     stride = workers;
     tile = worker;
     slot = 2 * worker;
-    tile_end = a.stream_k == 0 ? tiles : (a.stream_k == 2 ? a.dp_tiles : 0);
-    first_shared = a.stream_k == 0 ? tiles : (a.stream_k == 2 ? a.dp_tiles : 0);
-    const long long total = static_cast<long long>(tiles - first_shared) * a.k_blocks;
-    unit = total * worker / workers;
-    unit_end = total * (worker + 1) / workers;
+    tile_end = a.stream_k == 0 ? tiles : (a.stream_k >= 2 ? a.dp_tiles : 0);
+    first_shared = a.stream_k == 0 ? tiles : (a.stream_k >= 2 ? a.dp_tiles : 0);
+    if (a.stream_k == 3) {
+      unit = worker;                                   // half-width units, round robin
+      unit_end = 2ll * (tiles - first_shared);
+    } else {
+      const long long total = static_cast<long long>(tiles - first_shared) * a.k_blocks;
+      unit = total * worker / workers;
+      unit_end = total * (worker + 1) / workers;
+    }
   }
-  __device__ __forceinline__ bool next(const GemmArgs& a, Segment& s) {
+  __device__ __forceinline__ bool next(const GemmArgs& a, Segment& s, int bn) {
     int t;
+    s.n_off = 0;
+    s.n_cols = bn;
     if (tile < tile_end) {
       t = tile;
       tile += stride;
+      s.kb0 = 0;
+      s.kb1 = a.k_blocks;
+      s.partial = 0;
+      s.sk_index = 0;
+    } else if (a.stream_k == 3) {
+      if (unit >= unit_end) return false;
+      t = first_shared + static_cast<int>(unit >> 1);
+      s.n_cols = bn / 2;
+      s.n_off = static_cast<int>(unit & 1) * (bn / 2);
+      unit += stride;
       s.kb0 = 0;
       s.kb1 = a.k_blocks;
       s.partial = 0;
@@ -376,9 +399,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      while (ok && it.next(args, seg)) {
+      while (ok && it.next(args, seg, BN)) {
         const int m0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM;      // this CTA's rows of A
-        const int n0 = seg.n_blk * BN + static_cast<int>(cta) * Cfg::BN_CTA;      // this CTA's columns of B
+        // This CTA's columns of B.  A half-width unit needs only the first half of what the boxes
+        // fetch; the rest lands in shared memory unread (same byte count for the barrier).
+        const int n0 = seg.n_blk * BN + seg.n_off + static_cast<int>(cta) * (seg.n_cols / CTAS);
         for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
           if (!wait(empty_bar(s), ph ^ 1u, DEV_TIMEOUT_PRODUCER)) { ok = false; break; }
           // The pair's loads all complete on the leader's barrier, which expects both CTAs' bytes.
@@ -419,12 +444,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t ph = 0;
       uint32_t n_acc = 0;
       bool ok = true;
-      while (ok && it.next(args, seg)) {
+      while (ok && it.next(args, seg, BN)) {
         const uint32_t b = n_acc & 1u;
         const uint32_t acc_ph = (n_acc >> 1) & 1u;
         if (!wait(acc_empty_bar(b), acc_ph ^ 1u, DEV_TIMEOUT_MMA)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + b * BN;
+        // Instruction descriptor with this unit's N (bits 17-22 hold N / 8).
+        const uint32_t idesc = args.idesc - (static_cast<uint32_t>((BN - seg.n_cols) >> 3) << 17);
         for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
           if (!wait(full_bar(s), ph, DEV_TIMEOUT_MMA)) { ok = false; break; }
           ptx::tc_fence_after_sync();
@@ -441,7 +468,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 Cfg::B_MN ? ptx::make_smem_desc(b_addr + k * Cfg::UMMA_K * 128, Cfg::MN_BOX_BYTES,
                                                 Cfg::MN_SBO, Cfg::MN_LAYOUT)
                           : ptx::make_smem_desc(b_addr + k * 32, 16, 1024);
-            ptx::umma<CTAS, kTf32>(d_tmem, a_desc, b_desc, args.idesc, (kb > seg.kb0 || k > 0) ? 1u : 0u);
+            ptx::umma<CTAS, kTf32>(d_tmem, a_desc, b_desc, idesc, (kb > seg.kb0 || k > 0) ? 1u : 0u);
           }
           // The stage is reusable (in both CTAs) once these MMAs have read it.
           if constexpr (kPair) ptx::umma_commit_pair(empty_bar(s), 3);
@@ -464,7 +491,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     Segment seg;
     uint32_t n_acc = 0;
     bool ok = true;
-    while (ok && it.next(args, seg)) {
+    while (ok && it.next(args, seg, BN)) {
       const uint32_t b = n_acc & 1u;
       const uint32_t acc_ph = (n_acc >> 1) & 1u;
       if (!wait(acc_full_bar(b), acc_ph, DEV_TIMEOUT_EPILOGUE)) { ok = false; break; }
@@ -472,8 +499,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32 + lane;
       const bool row_ok = row < args.M;
 #pragma unroll 1
-      for (int c = half; c < BN / 32; c += 2) {
-        const int col0 = seg.n_blk * BN + c * 32;
+      for (int c = half; c < seg.n_cols / 32; c += 2) {
+        const int col0 = seg.n_blk * BN + seg.n_off + c * 32;
         if (col0 >= args.N) break;             // warp-uniform
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * BN + c * 32, r);

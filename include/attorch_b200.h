@@ -89,7 +89,7 @@ extern "C" {
 #define AB200_FLAG_NO_PAIR 16       /* one CTA per tile: no cta_group::2 kernels                */
 #define AB200_FLAG_NO_TMA_STORE 32  /* epilogue stores from registers, not through TMA           */
 #define AB200_FLAG_SAVE_DERIVATIVE 64 /* forward: pre_act receives act'(Z) instead of Z            */
-#define AB200_FLAG_WHOLE_TILES 128  /* never share out a partial last round of tiles            */
+#define AB200_FLAG_WHOLE_TILES 128  /* never share out or halve a partial last round of tiles   */
 #define AB200_FLAG_DROPOUT_PACKED 256 /* activation layers: the cheaper dropout stream (see below) */
 
 /* Which kernel the last call on this host thread chose: 1 tcgen05 tile-parallel, 2 tcgen05
@@ -106,6 +106,13 @@ const char* ab200_error_string(int code);
 
 /* Kernel chosen by the last GEMM entry point called on this host thread (AB200_PATH_*). */
 int ab200_last_path(void);
+
+/*
+ * How the last tensor-core GEMM launched from this host thread divided its work: 0 whole tiles;
+ * 1 equal (tile, k-block) shares added atomically (stream-K); 2 whole tiles, the partial last round
+ * shared out and summed in a fixed order; 3 whole tiles, the partial last round as half-width tiles.
+ */
+int ab200_last_schedule(void);
 
 /*
  * Limits the CTAs (= SMs) the persistent GEMM kernels launch with, process-wide; 0 restores "all".
