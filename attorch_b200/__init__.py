@@ -8,17 +8,22 @@ Public surface (mirrors the reference's for this path, attorch/__init__.py:7-22)
     check_status      raise if a kernel reported a device-side time-out
     Sigmoid ... Softshrink, ActFuncAutoGrad
                       the standalone activation layers with fused dropout (attorch/act_layers.py)
+    GLU, GLUAutoGrad  the gated linear unit with an arbitrary activation (attorch/glu_layer.py)
     set_dropout_stream
                       the reference's dropout mask (default) or a cheaper generator
+    nn                torch.nn with this package's modules in place of PyTorch's (attorch/nn.py)
+    convert           parameters between torch.nn.Linear's [out, in] and this package's [in, out]
 """
 
+from . import convert, nn
 from .act_layers import (CELU, ELU, GELU, SELU, ActFuncAutoGrad, Hardshrink, Hardsigmoid, Hardswish,
                          Hardtanh, LeakyReLU, LogSigmoid, Mish, ReLU, ReLU6, Sigmoid, SiLU, Softplus,
                          Softshrink, Softsign, Tanh, Tanhshrink, set_dropout_stream)
+from .glu_layer import GLU, GLUAutoGrad
 from .linear_layer import (Linear, LinearAutoGrad, check_status, get_output_dtype, set_gemm_flags,
                            set_save_derivative)
 
-__all__ = ['Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags',
+__all__ = ['convert', 'nn', 'GLU', 'GLUAutoGrad', 'Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags',
            'set_save_derivative', 'set_dropout_stream', 'ActFuncAutoGrad', 'CELU', 'ELU', 'GELU', 'SELU', 'Hardshrink',
            'Hardsigmoid', 'Hardswish', 'Hardtanh', 'LeakyReLU', 'LogSigmoid', 'Mish', 'ReLU', 'ReLU6',
            'Sigmoid', 'SiLU', 'Softplus', 'Softshrink', 'Softsign', 'Tanh', 'Tanhshrink']

@@ -61,6 +61,8 @@ SIGNATURES = {
     'ab200_act_forward': (_int, [_ptr, _ptr, _i64, _int, _int, _f32, _f32, ctypes.c_uint32, _ptr, _int]),
     'ab200_act_input_grad': (_int, [_ptr, _ptr, _ptr, _i64, _int, _int, _f32, _f32, ctypes.c_uint32, _ptr,
                                     _int]),
+    'ab200_glu_forward': (_int, [_ptr, _ptr, _i64, _i64, _int, _int, _f32, _ptr]),
+    'ab200_glu_backward': (_int, [_ptr, _ptr, _ptr, _i64, _i64, _int, _int, _f32, _ptr]),
     'ab200_dropout_uniform': (_f32, [ctypes.c_uint32, ctypes.c_uint64, _int]),
     'ab200_dropout_threshold': (ctypes.c_uint32, [_f32, _int]),
     'ab200_cast_2d': (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _int, _int, _ptr]),

@@ -13,6 +13,7 @@
 #include "gemm_launch.cuh"
 #include "kernels_misc.cuh"
 #include "act_elementwise.cuh"
+#include "glu.cuh"
 
 namespace ab200 {
 
@@ -556,6 +557,48 @@ int ab200_act_input_grad(const void* dy, const void* x, void* dx, int64_t n, int
                          float act_param, float drop_p, uint32_t seed, void* stream, int flags) {
   return launch_act_elementwise<true>(x, dy, dx, n, dtype, act, act_param, drop_p, seed,
                                       static_cast<cudaStream_t>(stream), flags);
+}
+
+extern "C++" {
+namespace {
+template <bool kBackward>
+int launch_glu(const void* x, const void* dy, void* out, int64_t outer, int64_t inner, int dtype, int act,
+               float act_param, cudaStream_t stream) {
+  if (outer < 0 || inner < 0) return ERR_BAD_SHAPE;
+  if (!valid_dtype(dtype)) return ERR_BAD_DTYPE;
+  if (!valid_act(act)) return ERR_BAD_ACT;
+  if (outer == 0 || inner == 0) return OK;
+  if (!x || !out || (kBackward && !dy)) return ERR_NULL_POINTER;
+  if (outer > (1ll << 40) / (inner > 0 ? inner : 1)) return ERR_TOO_LARGE;   // 2 * outer * inner must index safely
+  const auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const int vec = inner % 8 == 0 && aligned(x) && aligned(out) && (!kBackward || aligned(dy)) ? 1 : 0;
+  const long long groups_per_row = (inner + 7) / 8;
+  const long long groups = outer * groups_per_row;
+  long long blocks = (groups + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+#define AB200_GLU(T)                                                                                          \
+  glu_kernel<T, kBackward><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                              \
+      static_cast<const T*>(x), static_cast<const T*>(dy), static_cast<T*>(out), outer, inner, groups_per_row, \
+      act, act_param, vec)
+  if (dtype == DT_F32) AB200_GLU(float);
+  else if (dtype == DT_F16) AB200_GLU(__half);
+  else AB200_GLU(__nv_bfloat16);
+#undef AB200_GLU
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
+}
+}  // namespace
+}  // extern "C++"
+
+int ab200_glu_forward(const void* x, void* y, int64_t outer, int64_t inner, int dtype, int act, float act_param,
+                      void* stream) {
+  return launch_glu<false>(x, nullptr, y, outer, inner, dtype, act, act_param, static_cast<cudaStream_t>(stream));
+}
+
+int ab200_glu_backward(const void* dy, const void* x, void* dx, int64_t outer, int64_t inner, int dtype, int act,
+                       float act_param, void* stream) {
+  return launch_glu<true>(x, dy, dx, outer, inner, dtype, act, act_param, static_cast<cudaStream_t>(stream));
 }
 
 uint32_t ab200_dropout_threshold(float drop_p, int flags) {

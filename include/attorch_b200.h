@@ -273,6 +273,26 @@ float ab200_dropout_uniform(uint32_t seed, uint64_t index, int flags);
 uint32_t ab200_dropout_threshold(float drop_p, int flags);
 
 /*
+ * Gated linear unit with an arbitrary activation, forward:  y = x1 * act(x2), x1 and x2 being the two
+ * halves of the input along the gated dimension.  Replaces glu_forward_kernel
+ * (attorch/glu_kernels.py:13-53, launched at attorch/glu_layer.py:58-79) together with the two
+ * .contiguous() copies of the halves made there: x is the contiguous input seen as
+ * [outer, 2 * inner] (outer = product of the dimensions before the gated one, inner = half the gated
+ * extent times the product of the dimensions after it), y is [outer, inner].  act = AB200_ACT_NONE
+ * gives the bilinear unit x1 * x2.
+ */
+int ab200_glu_forward(const void* x, void* y, int64_t outer, int64_t inner, int dtype, int act, float act_param,
+                      void* stream);
+
+/*
+ * Its backward:  dx1 = dy * act(x2),  dx2 = dy * x1 * act'(x2), written into dx in the layout of x
+ * (no concatenation pass).  Replaces glu_backward_kernel (attorch/glu_kernels.py:56-105, launched at
+ * attorch/glu_layer.py:101-116).
+ */
+int ab200_glu_backward(const void* dy, const void* x, void* dx, int64_t outer, int64_t inner, int dtype, int act,
+                       float act_param, void* stream);
+
+/*
  * dst[r, c] (contiguous, dst_dtype) = src[r * src_stride_r + c * src_stride_c] (src_dtype).
  * The operand casts that autocast implies (attorch/linear_kernels.py:161-163 casts in registers;
  * torch.autocast casts before its matmuls, attorch/linear_layer.py:152) and the copy that makes a

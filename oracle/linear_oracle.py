@@ -384,3 +384,28 @@ def act_layer_backward(dy: Tensor, x: Tensor, act_func: str, drop_p: float = 0.0
         u = dropout_uniform(seed, x.numel(), stream).view(x.shape)
         g = torch.where(u < drop_p, torch.zeros((), dtype=dy.dtype), dy / (1 - drop_p))
     return (g * act_grad(name, z, param)).to(x.dtype)
+
+
+def glu_forward(x: Tensor, dim: int, act_func: str) -> Tensor:
+    """
+    glu_forward_kernel (attorch/glu_kernels.py:13-53) on the halves attorch/glu_layer.py:58-60 makes:
+    x1 * act(x2), the activation in fp32 for the activations of FP32_ACTS, else in x's dtype; stored
+    in x's dtype.
+    """
+    name, param = parse_act_func(act_func)
+    x1, x2 = x.chunk(2, dim=dim)
+    z = x2.float() if name in FP32_ACTS else x2
+    return (x1 * act_forward(name, z, param)).to(x.dtype)
+
+
+def glu_backward(dy: Tensor, x: Tensor, dim: int, act_func: str) -> Tensor:
+    """
+    glu_backward_kernel (attorch/glu_kernels.py:56-105): dx1 = dy * act(x2), dx2 = dy * x1 * act'(x2),
+    concatenated along dim (attorch/glu_layer.py:116).
+    """
+    name, param = parse_act_func(act_func)
+    x1, x2 = x.chunk(2, dim=dim)
+    z = x2.float() if name in FP32_ACTS else x2
+    g1 = (dy * act_forward(name, z, param)).to(x.dtype)
+    g2 = (dy * x1 * act_grad(name, z, param)).to(x.dtype)
+    return torch.cat([g1, g2], dim=dim)

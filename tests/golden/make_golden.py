@@ -9,11 +9,12 @@ Usage (needs a checkout of the reference; no GPU):
 The reference is imported unmodified.  Two host-side shims make it importable without a GPU:
 ``torch.cuda.get_device_capability`` is stubbed (the reference queries it at import time,
 attorch/utils.py:12-24), and each autotuner is cut down to its first configuration so that no
-config is benchmarked (attorch/linear_kernels.py:44-56, attorch/act_kernels.py:840-887).
+config is benchmarked (attorch/linear_kernels.py:44-56, attorch/act_kernels.py:840-887,
+attorch/glu_kernels.py:13-16 and 56-59).
 
 Each case is stored as one .npz with the inputs (or the seed that regenerates them plus a
 checksum) and the reference's output, dX, dW and db; the standalone activation layers go into
-act_layers_fp32.npz.  bf16 is not generated: the interpreter's bf16 dot product returns garbage.
+act_layers_fp32.npz, the gated linear unit into glu_fp32.npz.  bf16 is not generated: the interpreter's bf16 dot product returns garbage.
 """
 
 import argparse
@@ -40,10 +41,13 @@ def load_reference(path: str):
     sys.path.insert(0, path)
     import attorch
     from attorch.act_kernels import act_func_backward_kernel, act_func_forward_kernel
+    from attorch.glu_kernels import glu_backward_kernel, glu_forward_kernel
     from attorch.linear_kernels import linear_forward_kernel
     linear_forward_kernel.configs = linear_forward_kernel.configs[:1]
     act_func_backward_kernel.configs = act_func_backward_kernel.configs[:1]
     act_func_forward_kernel.configs = act_func_forward_kernel.configs[:1]
+    glu_forward_kernel.configs = glu_forward_kernel.configs[:1]
+    glu_backward_kernel.configs = glu_backward_kernel.configs[:1]
     return attorch
 
 
@@ -159,6 +163,7 @@ def main():
          act_func='gelu', dtype='float32')
 
     act_layer_goldens(attorch)
+    glu_goldens(attorch)
 
 
 ACT_LAYERS = [('Sigmoid', {}), ('LogSigmoid', {}), ('Tanh', {}), ('ReLU', {}), ('GELU', {}),
@@ -199,6 +204,36 @@ def act_layer_goldens(attorch):
             data[f'seed_{tag}'] = np.array(drawn)
     np.savez_compressed(OUT_DIR / 'act_layers_fp32.npz', **data)
     print('wrote act_layers_fp32.npz')
+
+
+GLU_CASES = [((6, 10), -1), ((6, 10), 0), ((4, 6, 5), 1), ((2, 3, 8), 2), ((2, 4, 3, 2), -3)]
+
+
+def glu_goldens(attorch):
+    """
+    The reference's gated linear unit (attorch/glu_layer.py) for every activation setting on a 2-D
+    input gated over its last dimension, and for sigmoid / gelu / relu over every dimension of inputs
+    with 2 to 4 dimensions: output and input gradient.
+    """
+    gen = torch.Generator().manual_seed(5)
+    data = {}
+    for case, (shape, dim) in enumerate(GLU_CASES):
+        x = torch.randn(shape, generator=gen) * 2
+        out_shape = list(shape)
+        out_shape[dim] //= 2
+        dy = torch.randn(out_shape, generator=gen)
+        data[f'x_{case}'] = x.numpy()
+        data[f'dy_{case}'] = dy.numpy()
+        acts = [a for a in ALL_ACT_FUNCS if a is not None] if case == 0 else ['sigmoid', 'gelu', 'relu']
+        for act_func in acts:
+            xin = x.clone().requires_grad_(True)
+            y = attorch.GLU(dim=dim, act_func=act_func)(xin)
+            y.backward(dy)
+            tag = f'{case}_{act_func.replace(".", "p")}'
+            data[f'y_{tag}'] = y.detach().numpy()
+            data[f'dx_{tag}'] = xin.grad.numpy()
+    np.savez_compressed(OUT_DIR / 'glu_fp32.npz', **data)
+    print('wrote glu_fp32.npz')
 
 
 if __name__ == '__main__':

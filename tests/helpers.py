@@ -16,8 +16,9 @@ TOLERANCE = {torch.float32: 1e-2, torch.float16: 1e-2, torch.bfloat16: 1e-2}
 
 
 def golden_names(prefix: str = ''):
-    """Names of the linear-layer golden cases (the activation-layer file has its own loader)."""
-    return sorted(p.stem for p in GOLDEN_DIR.glob(f'{prefix}*.npz') if not p.stem.startswith('act_layers'))
+    """Names of the linear-layer golden cases (the activation-layer and GLU files have their own loaders)."""
+    return sorted(p.stem for p in GOLDEN_DIR.glob(f'{prefix}*.npz')
+                  if not p.stem.startswith(('act_layers', 'glu_')))
 
 
 # (module name, constructor arguments, act_func string) in the order of tests/golden/make_golden.py.
@@ -75,3 +76,23 @@ def assert_close(actual: torch.Tensor, expected: torch.Tensor, tol: float, what:
     assert actual.dtype == expected.dtype, f'{what}: dtype {actual.dtype} vs {expected.dtype}'
     torch.testing.assert_close(actual.float().cpu(), expected.float().cpu(), rtol=tol, atol=tol,
                                equal_nan=True, msg=lambda m: f'{what}: {m}')
+
+
+# (input shape, gated dimension) of the cases in tests/golden/glu_fp32.npz; case 0 holds every
+# activation setting, the others sigmoid, gelu and relu (tests/golden/make_golden.py: GLU_CASES).
+GLU_CASES = [((6, 10), -1), ((6, 10), 0), ((4, 6, 5), 1), ((2, 3, 8), 2), ((2, 4, 3, 2), -3)]
+
+
+def glu_golden_cases():
+    """[(case index, gated dimension, act_func, tag)] for every vector pair in glu_fp32.npz."""
+    from oracle.linear_oracle import ALL_ACT_FUNCS
+    cases = []
+    for case, (_, dim) in enumerate(GLU_CASES):
+        acts = [a for a in ALL_ACT_FUNCS if a is not None] if case == 0 else ['sigmoid', 'gelu', 'relu']
+        cases += [(case, dim, act, f'{case}_{act.replace(".", "p")}') for act in acts]
+    return cases
+
+
+def load_glu_golden():
+    raw = np.load(GOLDEN_DIR / 'glu_fp32.npz')
+    return {key: torch.from_numpy(raw[key]) for key in raw.files}
