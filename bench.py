@@ -14,7 +14,8 @@ Workloads (synthetic, seeded; shapes of BASELINE.json's configs):
       split over the N GPUs (strong scaling), same all-reduce.
   c3  transformer MLP pair 4096 -> 14336 (silu) -> 4096, no biases, bf16, 16384 tokens per GPU.
   c4  skinny forward only, fp16, 8192 -> 28672, M in {1, 8, 32, 128}: prints weight-read GB/s.
-  act standalone activation layer (GELU, drop_p = 0.1, bf16, 8192 x 4096 elements): GB/s.
+  act standalone activation layer (GELU, drop_p = 0.1, bf16, 32768 x 4096 elements) and gated linear
+      unit (silu, bf16, 16384 x 2*14336): GB/s.
 
 One "step" is one forward + backward of the workload on one batch.  ``value`` is the whole-job
 TFLOP/s at 6 * M * K * N floating-point operations per layer and step with the inputs resident in
@@ -340,6 +341,8 @@ def activation_layer(args, device):
                              ('kernel_backward_packed_stream', lambda: kernel_backward(packed), 3 * n * 2.0),
                              ('kernel_forward_no_dropout', kernel_forward_no_dropout, 2 * n * 2.0),
                              ('module_forward_backward', module_step, 5 * n * 2.0)):
+        if args.only and name != args.only:
+            continue
         for _ in range(max(args.warmup, 3)):
             fn()
         torch.cuda.synchronize()
@@ -351,7 +354,41 @@ def activation_layer(args, device):
         torch.cuda.synchronize()
         ms = t0.elapsed_time(t1) / args.steps
         results[name] = {'us': round(ms * 1e3, 2), 'gbs': round(nbytes / (ms * 1e-3) / 1e9, 1)}
-    best = results['kernel_forward']['gbs']
+    # Gated linear unit of the MLP pair of workload c3: silu gate over the last dimension of
+    # [16384, 2 * 14336] bf16 (3 n e bytes forward, 5 n e backward for n output elements).
+    del x, dy, out, xg
+    rows, half = 16384, 14336
+    gx = torch.randn(rows, 2 * half, device=device).bfloat16()
+    gdy = torch.randn(rows, half, device=device).bfloat16()
+    gy = torch.empty(rows, half, device=device, dtype=torch.bfloat16)
+    gdx = torch.empty_like(gx)
+    silu = act_id('silu')
+
+    def glu_forward():
+        rc = lib.ab200_glu_forward(gx.data_ptr(), gy.data_ptr(), rows, half, _lib.BF16, silu, 0.0, stream)
+        assert rc == 0, rc
+
+    def glu_backward():
+        rc = lib.ab200_glu_backward(gdy.data_ptr(), gx.data_ptr(), gdx.data_ptr(), rows, half, _lib.BF16, silu, 0.0,
+                                    stream)
+        assert rc == 0, rc
+
+    for name, fn, nbytes in (('glu_forward', glu_forward, 3 * rows * half * 2.0),
+                             ('glu_backward', glu_backward, 5 * rows * half * 2.0)):
+        if args.only and name != args.only:
+            continue
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / args.steps
+        results[name] = {'us': round(ms * 1e3, 2), 'gbs': round(nbytes / (ms * 1e-3) / 1e9, 1)}
+    best = results[args.only or 'kernel_forward']['gbs']
     print(json.dumps({'metric': 'activation_layer_gbs', 'value': best, 'unit': 'GB/s', 'n_gpus': 1,
                       'steps': args.steps, 'warmup': args.warmup, 'higher_is_better': True, 'dtype': 'bf16',
                       'data': 'synthetic',
@@ -368,6 +405,8 @@ def main():
     parser.add_argument('--steps', type=int, default=200)
     parser.add_argument('--warmup', type=int, default=10)
     parser.add_argument('--workload', choices=sorted(WORKLOADS) + ['c4', 'act'], default='c2')
+    parser.add_argument('--only', default=None,
+                        help='workload act: time just this entry (e.g. kernel_forward, glu_backward)')
     parser.add_argument('--impl', choices=['b200', 'reference'], default='b200')
     parser.add_argument('--no-cpu-baseline', action='store_true')
     parser.add_argument('--no-graph', action='store_true',
