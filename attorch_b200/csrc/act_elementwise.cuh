@@ -91,82 +91,103 @@ inline uint32_t dropout_threshold(float drop_p, int stream) {
   return static_cast<uint32_t>(lo);
 }
 
+// The arithmetic of one group of 8 elements: res = act(xv) or gv * act'(xv), then the dropout mask of
+// elements base .. base + 7.
+template <bool kBackward>
+__device__ __forceinline__ void act_group(const float (&xv)[8], const float (&gv)[8], float (&res)[8],
+                                          long long base, int act, float param, float keep_scale,
+                                          uint32_t seed, int dropout, uint32_t threshold) {
+  if constexpr (kBackward) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) res[i] = gv[i];
+    act_grad_mul(res, xv, act, param);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) res[i] = xv[i];
+    act_fwd_inplace(res, act, param);
+  }
+  // "u < drop_p" as an integer comparison with dropout_threshold(): no int -> float conversion.
+  if (dropout == DROPOUT_REFERENCE) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint32_t r[4];
+      philox4x32_10(static_cast<uint32_t>(base + i), 0u, 0u, 0u, seed, 0u, r);
+      res[i] = (mirrored_word(r[0]) < threshold) ? 0.0f : res[i] * keep_scale;
+    }
+  } else if (dropout == DROPOUT_PACKED) {
+    // Two Philox blocks cover the 8 consecutive indices of this group.
+    uint32_t a[4], b[4];
+    const uint64_t blk = static_cast<uint64_t>(base) >> 2;
+    philox4x32_10(static_cast<uint32_t>(blk), static_cast<uint32_t>(blk >> 32), 0u, 0u, seed, 0u, a);
+    philox4x32_10(static_cast<uint32_t>(blk + 1), static_cast<uint32_t>((blk + 1) >> 32), 0u, 0u, seed, 0u, b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      res[i] = (a[i] < threshold) ? 0.0f : res[i] * keep_scale;
+      res[4 + i] = (b[i] < threshold) ? 0.0f : res[4 + i] * keep_scale;
+    }
+  }
+}
+
 // kBackward = false: y = dropout(act(x));  true: dx = dropout_grad(dy) * act'(x).
+// Whole, 16-byte aligned groups go two per thread and trip with every load issued before the
+// arithmetic (the kernel is bound by memory latency unless the dropout generator dominates); the
+// ragged tail and unaligned tensors take the element-wise path.
 template <class T, bool kBackward>
 __global__ void __launch_bounds__(256)
 act_elementwise_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restrict__ out, long long n,
                        int act, float param, float drop_p, uint32_t seed, int dropout, uint32_t threshold) {
   const float keep_scale = dropout ? 1.0f / (1.0f - drop_p) : 1.0f;
-  const long long groups = (n + 7) / 8;
   const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
                        (!kBackward || (reinterpret_cast<uintptr_t>(dy) & 15) == 0);
   constexpr int kWords = sizeof(T) * 8 / 16;
-  for (long long gidx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; gidx < groups;
-       gidx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long base = gidx * 8;
-    const bool full = aligned && base + 8 <= n;
-    float xv[8], gv[8];
-    if (full) {
-      uint4 xq[kWords], gq[kWords];
+  const long long whole = aligned ? n / 8 : 0;             // groups handled 16 bytes at a time
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long first = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  for (long long g0 = first; g0 < whole; g0 += 2 * stride) {
+    const long long g1 = g0 + stride < whole ? g0 + stride : g0;   // the last trip may repeat g0
+    const long long gs[2] = {g0, g1};
+    uint4 xq[2][kWords], gq[2][kWords];
 #pragma unroll
-      for (int w = 0; w < kWords; ++w) xq[w] = __ldg(reinterpret_cast<const uint4*>(x + base) + w);
+    for (int u = 0; u < 2; ++u) {
+#pragma unroll
+      for (int w = 0; w < kWords; ++w) xq[u][w] = __ldg(reinterpret_cast<const uint4*>(x + gs[u] * 8) + w);
       if constexpr (kBackward) {
 #pragma unroll
-        for (int w = 0; w < kWords; ++w) gq[w] = __ldg(reinterpret_cast<const uint4*>(dy + base) + w);
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        xv[i] = to_f32<T>(reinterpret_cast<const T*>(xq)[i]);
-        gv[i] = kBackward ? to_f32<T>(reinterpret_cast<const T*>(gq)[i]) : 0.0f;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const bool in = base + i < n;
-        xv[i] = in ? to_f32<T>(x[base + i]) : 0.0f;
-        gv[i] = (kBackward && in) ? to_f32<T>(dy[base + i]) : 0.0f;
+        for (int w = 0; w < kWords; ++w) gq[u][w] = __ldg(reinterpret_cast<const uint4*>(dy + gs[u] * 8) + w);
       }
     }
-    float res[8];
-    if constexpr (kBackward) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) res[i] = gv[i];
-      act_grad_mul(res, xv, act, param);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) res[i] = xv[i];
-      act_fwd_inplace(res, act, param);
-    }
-    // "u < drop_p" as an integer comparison with dropout_threshold(): no int -> float conversion.
-    if (dropout == DROPOUT_REFERENCE) {
+    for (int u = 0; u < 2; ++u) {
+      if (u == 1 && g1 == g0) break;
+      float xv[8], gv[8], res[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        uint32_t r[4];
-        philox4x32_10(static_cast<uint32_t>(base + i), 0u, 0u, 0u, seed, 0u, r);
-        res[i] = (mirrored_word(r[0]) < threshold) ? 0.0f : res[i] * keep_scale;
+        xv[i] = to_f32<T>(reinterpret_cast<const T*>(xq[u])[i]);
+        gv[i] = kBackward ? to_f32<T>(reinterpret_cast<const T*>(gq[u])[i]) : 0.0f;
       }
-    } else if (dropout == DROPOUT_PACKED) {
-      // Two Philox blocks cover the 8 consecutive indices of this group.
-      uint32_t a[4], b[4];
-      const uint64_t blk = static_cast<uint64_t>(base) >> 2;
-      philox4x32_10(static_cast<uint32_t>(blk), static_cast<uint32_t>(blk >> 32), 0u, 0u, seed, 0u, a);
-      philox4x32_10(static_cast<uint32_t>(blk + 1), static_cast<uint32_t>((blk + 1) >> 32), 0u, 0u, seed, 0u, b);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        res[i] = (a[i] < threshold) ? 0.0f : res[i] * keep_scale;
-        res[4 + i] = (b[i] < threshold) ? 0.0f : res[4 + i] * keep_scale;
-      }
-    }
-    if (full) {
+      act_group<kBackward>(xv, gv, res, gs[u] * 8, act, param, keep_scale, seed, dropout, threshold);
       alignas(16) T o[8];
       pack8<T>(res, o);
 #pragma unroll
-      for (int w = 0; w < kWords; ++w) reinterpret_cast<uint4*>(out + base)[w] = reinterpret_cast<const uint4*>(o)[w];
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (base + i < n) out[base + i] = from_f32<T>(res[i]);
+      for (int w = 0; w < kWords; ++w)
+        reinterpret_cast<uint4*>(out + gs[u] * 8)[w] = reinterpret_cast<const uint4*>(o)[w];
     }
+  }
+  // Element-wise remainder: everything if the tensors are not 16-byte aligned, else the last n % 8.
+  const long long groups = (n + 7) / 8;
+  for (long long g = whole + first; g < groups; g += stride) {
+    const long long base = g * 8;
+    float xv[8], gv[8], res[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const bool in = base + i < n;
+      xv[i] = in ? to_f32<T>(x[base + i]) : 0.0f;
+      gv[i] = (kBackward && in) ? to_f32<T>(dy[base + i]) : 0.0f;
+    }
+    act_group<kBackward>(xv, gv, res, base, act, param, keep_scale, seed, dropout, threshold);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (base + i < n) out[base + i] = from_f32<T>(res[i]);
   }
 }
 

@@ -499,7 +499,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32 + lane;
       const bool row_ok = row < args.M;
 #pragma unroll 1
-      for (int c = half; c < seg.n_cols / 32; c += 2) {
+      for (int c = half; c < seg.n_cols / 32; c += Cfg::kEpilogueWarps / 4) {
         const int col0 = seg.n_blk * BN + seg.n_off + c * 32;
         if (col0 >= args.N) break;             // warp-uniform
         uint32_t r[32];
