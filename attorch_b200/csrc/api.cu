@@ -278,6 +278,33 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
   return run_tiles_or_split(p, workspace, workspace_bytes, stream, flags);
 }
 
+extern "C++" {
+namespace {
+// Rows per block of act_backward_kernel for an M x N problem whose blocks are cols_per_block wide:
+// kActRows, or more where that makes the grid a whole number of waves of resident blocks (a grid of
+// 1.7 waves costs as much as one of 2).  Never fewer, so ceil(M / kActRows) partial rows always suffice.
+int act_rows_per_block(int64_t M, int64_t N, int cols_per_block) {
+  static const int resident = []() {
+    int blocks = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, act_backward_kernel<__nv_bfloat16, true, 32>, 256, 0) !=
+            cudaSuccess || blocks <= 0)
+      blocks = 4;
+    return blocks;
+  }();
+  const int64_t gx = (N + cols_per_block - 1) / cols_per_block;
+  const int64_t max_gy = (M + kActRows - 1) / kActRows;
+  const int64_t slots = static_cast<int64_t>(sm_count()) * resident;
+  const int64_t waves = gx * max_gy / slots;
+  if (waves < 1) return kActRows;
+  const int64_t gy = waves * slots / gx;
+  if (gy < 1 || gy > max_gy) return kActRows;
+  int64_t rows = (M + gy - 1) / gy;
+  rows = (rows + 7) / 8 * 8;
+  return static_cast<int>(rows < kActRows ? kActRows : rows);
+}
+}  // namespace
+}  // extern "C++"
+
 int64_t ab200_act_backward_workspace_bytes(int64_t M, int64_t N) {
   if (M <= 0 || N <= 0) return 0;
   return ((M + kActRows - 1) / kActRows) * N * 4;
@@ -295,7 +322,8 @@ int ab200_act_backward(const void* dy, const void* z, void* dz, void* db, int64_
   if (M > 0 && (!dy || (act != ACT_NONE && !z))) return ERR_NULL_POINTER;
   if (dz == nullptr && db == nullptr) return OK;
   if (ld_dy < N || (z && ld_z < N) || (dz && ld_dz < N)) return ERR_BAD_STRIDE;
-  const int chunks = static_cast<int>((M + kActRows - 1) / kActRows);
+  const int rows_per_block = act_rows_per_block(M, N, 256);
+  const int chunks = static_cast<int>((M + rows_per_block - 1) / rows_per_block);
   float* partial = nullptr;
   if (db != nullptr) {
     if (M == 0) {
@@ -319,7 +347,8 @@ int ab200_act_backward(const void* dy, const void* z, void* dz, void* db, int64_
   const int Mi = static_cast<int>(M), Ni = static_cast<int>(N);
 #define AB200_LAUNCH_ACT_V(T, V, C)                                                                  \
   act_backward_kernel<T, V, C><<<grid, 256, 0, stream>>>(static_cast<const T*>(dy), ld_dy,           \
-      static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param)
+      static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param,     \
+      rows_per_block)
 #define AB200_LAUNCH_ACT(T)                                                  \
   do {                                                                       \
     if (vec && wide) AB200_LAUNCH_ACT_V(T, true, 256);                       \
@@ -392,9 +421,11 @@ int ab200_act_backward_static(const void* dy, const void* z, void* dz, void* db,
   if (M > 0 && (!dy || (act != ACT_NONE && !z))) return ERR_NULL_POINTER;
   if (dz == nullptr && db == nullptr) return OK;
   if (ld_dy < N || (z && ld_z < N) || (dz && ld_dz < N)) return ERR_BAD_STRIDE;
-  const int64_t chunks = (M + kActRows - 1) / kActRows;
-  // One fp32 per (row block, column): reject shapes the built-in array cannot hold.
-  if (db != nullptr && chunks * N > kStaticScratchFloats) return ERR_STATIC_SCRATCH_TOO_SMALL;
+  // One fp32 per (row block, column): reject shapes the built-in array cannot hold (by the documented
+  // bound, ceil(M / 128) * N; the grid may use fewer, taller row blocks).
+  if (db != nullptr && (M + kActRows - 1) / kActRows * N > kStaticScratchFloats) return ERR_STATIC_SCRATCH_TOO_SMALL;
+  const int rows_per_block = act_rows_per_block(M, N, 256);
+  const int64_t chunks = (M + rows_per_block - 1) / rows_per_block;
   if (M == 0) {
     if (db == nullptr) return OK;
     return cudaMemsetAsync(db, 0, N * dtype_size(db_dtype), stream) == cudaSuccess ? OK : ERR_LAUNCH;
@@ -418,10 +449,12 @@ int ab200_act_backward_static(const void* dy, const void* z, void* dz, void* db,
   do {                                                                                                 \
     if (vec)                                                                                           \
       act_backward_kernel<T, true, 32><<<grid, 256, 0, stream>>>(static_cast<const T*>(dy), ld_dy,     \
-          static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param); \
+          static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param, \
+          rows_per_block);                                                                             \
     else                                                                                               \
       act_backward_kernel<T, false, 32><<<grid, 256, 0, stream>>>(static_cast<const T*>(dy), ld_dy,    \
-          static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param); \
+          static_cast<const T*>(z), ld_z, static_cast<T*>(dz), ld_dz, partial, Mi, Ni, act, act_param, \
+          rows_per_block);                                                                             \
   } while (0)
   if (dtype == DT_F32) AB200_LAUNCH_ACT_STATIC(float);
   else if (dtype == DT_F16) AB200_LAUNCH_ACT_STATIC(__half);

@@ -21,7 +21,9 @@ namespace ab200 {
 // kColThreads = 256 (wide matrices) every row pass reads 4 KB (2-byte types) of one row
 // contiguously, which keeps DRAM pages open, and a thread owns its 8 columns for all rows of the
 // block, so the column sums need no exchange; with kColThreads = 32 (narrow matrices) the row
-// lanes' sums meet in shared memory.  partial is [gridDim.y][N] fp32.
+// lanes' sums meet in shared memory.  partial is [gridDim.y][N] fp32.  A block takes rows_per_block
+// consecutive rows: at least kActRows (which bounds the partial sums a caller must provide room for)
+// and otherwise as many as make the grid a whole number of waves of resident blocks.
 // ------------------------------------------------------------------------------------------------
 constexpr int kActRows = 128;
 
@@ -29,7 +31,7 @@ template <class T, bool kVec, int kColThreads>
 __global__ void __launch_bounds__(256)
 act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restrict__ z, long long ld_z,
                     T* __restrict__ dz, long long ld_dz, float* __restrict__ partial, int M, int N,
-                    int act, float act_param) {
+                    int act, float act_param, int rows_per_block) {
   constexpr int kRowLanes = 256 / kColThreads;
   // Rows in flight per thread.  Four rows were slower on B200 (45.7 vs 40.5 us on 8192 x 4096 bf16):
   // at 124 registers only two blocks fit an SM, so no more loads are in flight than with two rows.
@@ -38,8 +40,8 @@ act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restri
   const int ct = threadIdx.x % kColThreads;
   const int rl = threadIdx.x / kColThreads;
   const int col0 = (blockIdx.x * kColThreads + ct) * 8;
-  const int row_begin = blockIdx.y * kActRows;
-  const int row_end = min(M, row_begin + kActRows);
+  const int row_begin = blockIdx.y * rows_per_block;
+  const int row_end = min(M, row_begin + rows_per_block);
   float sum[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
