@@ -51,10 +51,24 @@ bool tma_ok(const void* p, long long pitch_elems, long long unit_stride, int elt
   return true;
 }
 
+// A forward pass with at most 128 rows is a stream of W through the SMs, bound by HBM.  When W is wide
+// enough that its 256-column blocks give at least 60 % of the SMs one whole tile each, that single
+// wave of whole tiles (fused epilogue, no workspace, X re-read once per 256 columns) is the fastest
+// schedule measured: 76-81 us for M = 8 ... 128 on 8192 -> 28672 fp16 (6.0-6.2 TB/s), against 90-137 us
+// for the swap-AB stream-K kernel, which stays for narrower outputs and for fewer than 8 rows (86 us).
+bool few_rows_wide_output(long long M, long long N) {
+  return M >= 8 && M <= 128 && ((N + 255) / 256) * 10 >= static_cast<long long>(sm_count()) * 6;
+}
+
 // Widest tile that still gives every SM work; otherwise the narrowest that covers N.
 int pick_bn(long long M, long long N) {
+  if (const char* e = std::getenv("AB200_BN")) {   // experiments only
+    const int v = std::atoi(e);
+    if (v == 32 || v == 64 || v == 128 || v == 256) return v;
+  }
   const long long tm = (M + 127) / 128;
   const int sms = sm_count();
+  if (few_rows_wide_output(M, N)) return 256;
   if (N > 128 && tm * ((N + 255) / 256) >= sms) return 256;
   if (N > 64 && tm * ((N + 127) / 128) >= sms) return 128;
   if (N > 128) return 256;
@@ -185,7 +199,11 @@ int64_t ab200_launch_count(void) { return g_launches.load(); }
 
 int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N, int flags) {
   if (M <= 0 || N <= 0) return 0;
-  if ((M <= 128 && !(flags & AB200_FLAG_NO_STREAMK)) || (flags & AB200_FLAG_FORCE_STREAMK)) return M * N * 4;
+  if ((M <= 128 && !few_rows_wide_output(M, N) && !(flags & AB200_FLAG_NO_STREAMK)) ||
+      (flags & AB200_FLAG_FORCE_STREAMK))
+    return M * N * 4;
+  // One wave of whole tiles: nothing to share out, no scratch.
+  if (few_rows_wide_output(M, N) && (N + 255) / 256 <= sm_count()) return 0;
   return ab200_gemm_workspace_bytes(M, N, K);
 }
 
@@ -241,7 +259,8 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
   p.op_dtype = op_dtype;
   GemmArgs& g = p.g;
   g.status = status;
-  const bool skinny = ((M <= 128 && !(flags & AB200_FLAG_NO_STREAMK)) || (flags & AB200_FLAG_FORCE_STREAMK));
+  const bool skinny = ((M <= 128 && !few_rows_wide_output(M, N) && !(flags & AB200_FLAG_NO_STREAMK)) ||
+                       (flags & AB200_FLAG_FORCE_STREAMK));
   if (skinny) {
     // Swap-AB: D'[N, M] = W^T[N, K] * X^T[K, M].  A = W (MN-major), B = X (K-major).  The fp32
     // partial sums land in workspace as [M, N] (coalesced along N) and a finishing kernel applies

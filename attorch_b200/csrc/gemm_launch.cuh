@@ -46,7 +46,7 @@ int last_schedule();
 void set_last_schedule(int mode);
 
 // AB200_TAIL_MODE: unset / 0 = a partial last round of tiles is shared out where that is possible;
-// 3 = it runs as half-width tiles whenever it fills at most half of the workers.
+// 1 = never; 3 = it runs as half-width tiles whenever it fills at most half of the workers.
 int tail_mode_override();
 
 // Finishing pass of the hybrid schedule (defined next to the kernel, in api.cu): shared-out tiles
@@ -167,7 +167,7 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
     g.stream_k = 3;
     g.dp_tiles = static_cast<int>(tiles) - last_round;
   }
-  if (!g.stream_k && p.tail_workspace != nullptr && tiles > workers && g.k_blocks >= 16) {
+  if (!g.stream_k && tail_mode != 1 && p.tail_workspace != nullptr && tiles > workers && g.k_blocks >= 16) {
     const int rem = static_cast<int>(tiles % workers);
     // Two slots per worker (its share of the tail touches at most two tiles).
     const long long need = 2ll * workers * Cfg::TILE_M * Cfg::BN * 4;

@@ -257,6 +257,7 @@ def skinny_forward(args, device, lib):
     back-to-back launches are cold.
     """
     import attorch_b200
+    from attorch_b200 import _lib
     K, N = 8192, 28672
     peaks, peak_source = measured_peaks()
     layer = attorch_b200.Linear(K, N, bias=False, device=device, dtype=torch.float16)
@@ -277,7 +278,9 @@ def skinny_forward(args, device, lib):
             torch.cuda.synchronize()
         ms = t0.elapsed_time(t1) / args.steps
         nbytes = 2.0 * (K * N + m * K + m * N)
-        rows.append({'M': m, 'us': ms * 1e3, 'gbs': nbytes / (ms * 1e-3) / 1e9,
+        path = {_lib.PATH_STREAMK: 'memset + swap-AB stream-K tcgen05 + finish',
+                _lib.PATH_TCGEN05: 'one wave of whole 128 x 256 tcgen05 tiles'}.get(lib.ab200_last_path(), 'other')
+        rows.append({'M': m, 'us': ms * 1e3, 'gbs': nbytes / (ms * 1e-3) / 1e9, 'path': path,
                      'frac_of_measured_hbm': nbytes / (ms * 1e-3) / 1e9 / peaks['hbm_gbs'],
                      'frac_of_nominal_8000': nbytes / (ms * 1e-3) / 1e9 / 8000.0})
     attorch_b200.check_status()
@@ -285,7 +288,7 @@ def skinny_forward(args, device, lib):
     print(json.dumps({'metric': 'skinny_forward_weight_read_gbs', 'value': best, 'unit': 'GB/s', 'n_gpus': 1,
                       'steps': args.steps, 'warmup': args.warmup, 'higher_is_better': True, 'dtype': 'f16',
                       'data': 'synthetic', 'config': {'workload': 'c4', 'K': K, 'N': N, 'rows': rows,
-                                                      'path': 'module call: memset + swap-AB stream-K tcgen05 + finish'},
+                                                      'call': 'attorch_b200.Linear under torch.no_grad()'},
                       'roofline': {'bound': 'hbm', 'achieved': best, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
                                    'frac': best / peaks['hbm_gbs'], 'traffic': None,
                                    'peak_source': peak_source}}), flush=True)

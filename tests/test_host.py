@@ -88,7 +88,10 @@ def test_argument_validation_without_gpu(lib):
 
 
 def test_workspace_sizes(lib):
-    assert lib.ab200_forward_workspace_bytes(8, 8192, 28672, 0) == 8 * 28672 * 4
+    assert lib.ab200_forward_workspace_bytes(4, 8192, 28672, 0) == 4 * 28672 * 4
+    # From 8 rows on a wide output runs as one wave of whole tiles: no scratch.
+    assert lib.ab200_forward_workspace_bytes(8, 8192, 28672, 0) == 0
+    assert lib.ab200_forward_workspace_bytes(8, 8192, 4096, 0) == 8 * 4096 * 4
     assert lib.ab200_forward_workspace_bytes(8192, 4096, 4096, 0) == 2 * 148 * 128 * 256 * 4
     assert lib.ab200_forward_workspace_bytes(300, 264, 520, _lib.FLAG_FORCE_STREAMK) == 300 * 520 * 4
     assert lib.ab200_forward_workspace_bytes(8, 64, 64, _lib.FLAG_NO_STREAMK) == 0

@@ -404,6 +404,30 @@ def test_config4_skinny_fp16(m):
     assert_close(y.cpu(), e_y, TOL, 'output')
 
 
+@pytest.mark.parametrize('act_func', [None, 'silu'])
+@pytest.mark.parametrize('m', [1, 8, 32, 100, 128])
+def test_config4_full_width_fp16(m, act_func):
+    """
+    BASELINE config 4 at its full output width (N = 28672) and reduced K: from 8 rows on, the 112
+    column blocks of 256 run as one wave of whole tiles with the fused epilogue; fewer rows keep the
+    swap-AB stream-K kernel.  Both against the oracle.
+    """
+    gen = torch.Generator().manual_seed(100 + m)
+    K, N = 512, 28672
+    x = torch.randn(m, K, generator=gen).half()
+    w = (torch.randn(K, N, generator=gen) * 0.05).half()
+    b = torch.randn(N, generator=gen).half()
+    layer = make_layer(w, b, act_func, torch.float16)
+    with torch.no_grad():
+        y = layer(x.to(DEV))
+    attorch_b200.check_status()
+    if torch.cuda.get_device_properties(0).multi_processor_count <= 186:
+        expected = _lib.PATH_TCGEN05 if m >= 8 else _lib.PATH_STREAMK
+        assert _lib.load().ab200_last_path() == expected
+    e_y, _ = oracle.linear_forward(x, w, b, act_func)
+    assert_close(y.cpu(), e_y, TOL, 'output')
+
+
 def test_weight_gradient_in_row_blocks():
     """dW computed in four row blocks (as the data-parallel harness asks for) equals dW in one piece."""
     x, w, b, dy = seeded((512, 1024), 768, torch.bfloat16, seed=13)
