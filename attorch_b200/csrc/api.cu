@@ -55,17 +55,14 @@ bool tma_ok(const void* p, long long pitch_elems, long long unit_stride, int elt
 // enough that its 256-column blocks give at least 60 % of the SMs one whole tile each, that single
 // wave of whole tiles (fused epilogue, no workspace, X re-read once per 256 columns) is the fastest
 // schedule measured: 76-81 us for M = 8 ... 128 on 8192 -> 28672 fp16 (6.0-6.2 TB/s), against 90-137 us
-// for the swap-AB stream-K kernel, which stays for narrower outputs and for fewer than 8 rows (86 us).
+// for the swap-AB stream-K kernel, which stays for narrower outputs and for fewer than 8 rows (86 us;
+// whole tiles take 97 us there, and 82 us when the CTAs start at spread-out k-blocks: not understood).
 bool few_rows_wide_output(long long M, long long N) {
   return M >= 8 && M <= 128 && ((N + 255) / 256) * 10 >= static_cast<long long>(sm_count()) * 6;
 }
 
 // Widest tile that still gives every SM work; otherwise the narrowest that covers N.
 int pick_bn(long long M, long long N) {
-  if (const char* e = std::getenv("AB200_BN")) {   // experiments only
-    const int v = std::atoi(e);
-    if (v == 32 || v == 64 || v == 128 || v == 256) return v;
-  }
   const long long tm = (M + 127) / 128;
   const int sms = sm_count();
   if (few_rows_wide_output(M, N)) return 256;
