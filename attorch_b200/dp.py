@@ -11,6 +11,12 @@ Each layer writes its weight and bias gradient straight into a slice of one flat
 all-reduced on a side stream while the layer's ``dX`` product - and the backward of the layers
 before it - still run on the compute stream.  Because the upstream gradient is given per token,
 SUM reproduces the single-GPU full-batch gradient.
+
+A step that is replayed from CUDA graphs cannot issue NCCL calls from inside backward; for it the
+harness can hold back the first layer's ``dX`` (``defer_first_input_grad``): the step becomes "graph 1:
+forward and backward without that product", ``start_exchange()`` (one all-reduce of the whole bucket on
+the side stream), "graph 2: ``run_deferred()``", ``finish()`` - the exchange hides behind the one GEMM
+nothing else waits for.
 """
 
 from typing import Iterable, List, Optional
@@ -48,9 +54,14 @@ class GradientBuckets:
             would only start once they end.
         dw_chunks: Each layer's dW is computed and exchanged in this many blocks of rows, which
             widens the window the exchange can hide in from "dX" to "the rest of dW, then dX".
+        defer_first_input_grad: The first layer's dX - the last product of backward, which nothing
+            inside backward consumes - is not launched by backward but by ``run_deferred()``.  A
+            step can then be two replayable pieces with the exchange started in between:
+            forward + backward without that dX; ``start_exchange()``; ``run_deferred()``;
+            ``finish()``.  The input's ``.grad`` is complete only after ``run_deferred()``.
     """
     def __init__(self, layers: Iterable[Linear], process_group=None, overlap: bool = True,
-                 comm_sms: int = 16, dw_chunks: int = 2) -> None:
+                 comm_sms: int = 16, dw_chunks: int = 2, defer_first_input_grad: bool = False) -> None:
         self.layers: List[Linear] = list(layers)
         self.group = process_group
         self.world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -65,9 +76,15 @@ class GradientBuckets:
         self.comm_stream = torch.cuda.Stream(self.device) if self.overlap else None
         self._pending: List[torch.cuda.Event] = []
         self._gemm_ctas = 0
+        self._deferred: List = []
+        if defer_first_input_grad:
+            self.layers[0].defer_input_grad = self._deferred.append
         if self.overlap:
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
             self._gemm_ctas = max(2, sms - comm_sms)
+        elif self.device.type == 'cuda' and self.world_size > 1:
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            self._exchange_ctas = max(2, sms - comm_sms)
         offset = 0
         for index, layer in enumerate(self.layers):
             if layer.weight.dtype is not self.dtype:
@@ -110,6 +127,35 @@ class GradientBuckets:
         # The GEMMs enqueued from here to finish() run beside the collective.
         _lib.load().ab200_set_gemm_cta_limit(self._gemm_ctas)
 
+    def start_exchange(self) -> None:
+        """
+        Starts the all-reduce of the whole bucket on the side stream, ordered after everything enqueued
+        so far on the current stream (for steps that run backward with ``overlap=False`` and
+        ``defer_first_input_grad=True``); ``finish()`` waits for it.
+        """
+        if self.world_size == 1 or self.device.type != 'cuda':
+            return
+        if self.comm_stream is None:
+            self.comm_stream = torch.cuda.Stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ready)
+            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+            done = torch.cuda.Event()
+            done.record(self.comm_stream)
+        self._pending.append(done)
+
+    def exchange_cta_limit(self) -> int:
+        """CTAs a GEMM should be limited to while it runs beside the exchange (0: no limit)."""
+        return getattr(self, '_exchange_ctas', self._gemm_ctas)
+
+    def run_deferred(self) -> None:
+        """Launches the products ``defer_first_input_grad`` held back, on the current stream."""
+        for launch in self._deferred:
+            launch()
+        self._deferred.clear()
+
     def finish(self) -> None:
         """
         Completes the gradient exchange of one step: after it returns (in stream order on the
@@ -117,12 +163,13 @@ class GradientBuckets:
         """
         if self.world_size == 1:
             return
-        if self.overlap:
+        if self.overlap or self._pending:
             current = torch.cuda.current_stream(self.device)
             for done in self._pending:
                 current.wait_event(done)
             self._pending.clear()
-            _lib.load().ab200_set_gemm_cta_limit(0)
+            if self.overlap:
+                _lib.load().ab200_set_gemm_cta_limit(0)
         else:
             dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
 

@@ -163,12 +163,16 @@ class LinearAutoGrad(torch.autograd.Function):
     are written into (e.g. views of a flat all-reduce bucket), and a callable ``grad_ready(i, n)``
     that backward invokes each time block ``i`` of ``n`` row blocks of ``dW`` is enqueued (``db`` is
     complete before block 0), before ``dX`` is, so that the gradient exchange of this layer can
-    overlap the remaining work; ``dw_chunks`` is ``n``.
+    overlap the remaining work; ``dw_chunks`` is ``n``.  ``defer_input_grad``, if given, is called with
+    a function that launches the ``dX`` product instead of launching it: backward then returns the
+    buffer ``dX`` will be written to once the caller runs that function (on any stream ordered after
+    backward), which lets a data-parallel step start its gradient exchange before ``dX``.
     """
     @staticmethod
     def forward(ctx, input: Tensor, weight: Tensor, bias: Optional[Tensor] = None,
                 act_func: Optional[str] = None, weight_grad_out: Optional[Tensor] = None,
-                bias_grad_out: Optional[Tensor] = None, grad_ready=None, dw_chunks: int = 1) -> Tensor:
+                bias_grad_out: Optional[Tensor] = None, grad_ready=None, dw_chunks: int = 1,
+                defer_input_grad=None) -> Tensor:
         assert weight.ndim == 2, \
             f'Weights must be 2D, received shape {weight.shape}'
         assert bias is None or bias.ndim == 1, \
@@ -237,6 +241,7 @@ class LinearAutoGrad(torch.autograd.Function):
         ctx.has_grad_out = (weight_grad_out is not None, bias_grad_out is not None)
         ctx.grad_ready = grad_ready
         ctx.dw_chunks = int(dw_chunks)
+        ctx.defer_input_grad = defer_input_grad
         ctx.saved_derivative = requires_grad and name is not None and _save_derivative
         if requires_grad:
             # Backward multiplies in the output dtype, so the converted operands are what it
@@ -326,19 +331,32 @@ class LinearAutoGrad(torch.autograd.Function):
                 ctx.grad_ready(0, 1)
             if ctx.input_requires_grad:
                 input_grad = torch.empty((batch_dim, in_feat_dim), dtype=ctx.input_dtype, device=device)
-                ws_bytes = _cached_size('ab200_gemm_workspace_bytes', batch_dim, in_feat_dim, out_feat_dim)
-                workspace = _workspace(device, ws_bytes) if ws_bytes else None
-                _lib.check(lib.ab200_linear_backward_input(
-                    _ptr(pre_act_grad), _ptr(w_op), _ptr(input_grad),
-                    batch_dim, in_feat_dim, out_feat_dim,
-                    pre_act_grad.stride(0), pre_act_grad.stride(1), w_op.stride(0), w_op.stride(1),
-                    in_feat_dim, _dtype_id(op_dtype), _dtype_id(input_grad.dtype),
-                    _ptr(workspace), ws_bytes, status, stream, _gemm_flags),
-                    'ab200_linear_backward_input')
+                dx_ptr, dx_dtype = input_grad.data_ptr(), _dtype_id(input_grad.dtype)
+
+                # Holds dZ and W alive but not dX: autograd must remain the only owner of the
+                # tensor it is handed, or it would copy it before the deferred product has run.
+                def launch_input_grad(dz=pre_act_grad, w=w_op):
+                    with torch.cuda.device(device):
+                        run_stream = torch.cuda.current_stream().cuda_stream
+                        run_scratch = _stream_scratch(device)
+                        nbytes = _cached_size('ab200_gemm_workspace_bytes', batch_dim, in_feat_dim, out_feat_dim)
+                        space = _workspace(device, nbytes) if nbytes else None
+                        _lib.check(lib.ab200_linear_backward_input(
+                            _ptr(dz), _ptr(w), dx_ptr,
+                            batch_dim, in_feat_dim, out_feat_dim,
+                            dz.stride(0), dz.stride(1), w.stride(0), w.stride(1),
+                            in_feat_dim, _dtype_id(op_dtype), dx_dtype,
+                            _ptr(space), nbytes, _ptr(run_scratch['status']), run_stream, _gemm_flags),
+                            'ab200_linear_backward_input')
+
+                if ctx.defer_input_grad is not None:
+                    ctx.defer_input_grad(launch_input_grad)
+                else:
+                    launch_input_grad()
                 input_grad = input_grad.view(ctx.input_shape)
 
         # One slot per forward argument (attorch/linear_layer.py:158-161 pads with None).
-        return input_grad, weight_grad, bias_grad, None, None, None, None, None
+        return input_grad, weight_grad, bias_grad, None, None, None, None, None, None
 
 
 class Linear(nn.Linear):
@@ -374,8 +392,10 @@ class Linear(nn.Linear):
         # Optional callable run in backward as blocks of dW are enqueued (see LinearAutoGrad).
         self.grad_ready = None
         self.dw_chunks = 1
+        # Optional callable that receives the launcher of dX instead of dX being launched (see LinearAutoGrad).
+        self.defer_input_grad = None
 
     def forward(self, input: Tensor) -> Tensor:
         return LinearAutoGrad.apply(input, self.weight, self.bias, self.act_func,
                                     self.weight_grad_out, self.bias_grad_out, self.grad_ready,
-                                    self.dw_chunks)
+                                    self.dw_chunks, self.defer_input_grad)

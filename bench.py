@@ -461,17 +461,24 @@ def main():
     layers = [attorch_b200.Linear(k, n, bias=bias, act_func=act, device=device,
                                   dtype=spec['param_dtype'])
               for (k, n, act, bias) in spec['layers']]
-    # With graph replay (the default) the forward + backward of a step is one captured graph and the
-    # gradient exchange is one all-reduce of the whole bucket after it; with --no-graph the exchange
-    # is issued per block of dW from inside backward and overlaps the rest of it.  Measured: 2 GPUs
-    # 0.839 ms eager-overlapped vs 0.887 ms graph; 8 GPUs 1.001 ms eager (host-bound: 0.91 ms of
-    # enqueue time per step with 2 host threads per rank).
-    # So: graph replay on one GPU and wherever a rank has fewer than 4 host threads to itself.
-    if world_size > 1 and (os.cpu_count() or 1) // world_size >= 4 and not os.environ.get('AB200_FORCE_GRAPH'):
+    # One GPU: a step is one captured CUDA graph.  Several GPUs: NCCL cannot be captured here (see
+    # below), so either the step is launched eagerly with the gradient exchange issued per block of dW
+    # from inside backward, overlapping the rest of it (--no-graph; the default where a rank has at
+    # least 4 host threads to itself), or the local computation is replayed from a graph and followed by
+    # one all-reduce of the bucket.  Measured at 2 GPUs: eager overlapped 0.839-0.894 ms, graph + one
+    # all-reduce 0.886-0.887 ms, eager without overlap 0.877 ms; at 8 GPUs eager overlapped 0.959 ms
+    # (1.001 ms on a box with 2 host threads per rank, where enqueueing takes 0.91 ms per step).
+    # AB200_DEFER_DX=1 selects a third schedule: two graphs per step with the all-reduce started between
+    # them, so that it overlaps the first layer's dX (which runs on 16 fewer SMs).  It measured slower
+    # at 2 GPUs (0.914-0.924 ms): the exchange and the GEMM slow each other down more than the overlap
+    # saves.
+    if world_size > 1 and (os.cpu_count() or 1) // world_size >= 4 and not os.environ.get('AB200_FORCE_GRAPH') \
+            and os.environ.get('AB200_DEFER_DX', '0') != '1':
         args.no_graph = True
+    defer = world_size > 1 and not args.no_graph and os.environ.get('AB200_DEFER_DX', '0') == '1'
     overlap = args.no_graph and os.environ.get('AB200_DP_OVERLAP', '1') != '0'
     buckets = GradientBuckets(layers, comm_sms=int(os.environ.get('AB200_COMM_SMS', '16')),
-                              overlap=overlap,
+                              overlap=overlap, defer_first_input_grad=defer,
                               dw_chunks=int(os.environ.get('AB200_DW_CHUNKS', '2')))
     k_in, n_out = spec['layers'][0][0], spec['layers'][-1][1]
     gen = torch.Generator(device=device).manual_seed(1 + rank)
@@ -490,8 +497,19 @@ def main():
                 h = layer(h)
         h.backward(dy)
 
+    def deferred_products():
+        # The GEMMs held back run beside the exchange: leave NCCL some SMs.
+        lib.ab200_set_gemm_cta_limit(buckets.exchange_cta_limit())
+        try:
+            buckets.run_deferred()
+        finally:
+            lib.ab200_set_gemm_cta_limit(0)
+
     def step(x):
         compute(x)
+        if defer:
+            buckets.start_exchange()
+            deferred_products()
         buckets.finish()
 
     def barrier():
@@ -527,20 +545,27 @@ def main():
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 for _ in range(3):
-                    compute(x_dev)
+                    step(x_dev)
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 compute(x_dev)
-            graph.replay()
-            buckets.finish()
-            torch.cuda.synchronize()
-            attorch_b200.check_status()
+            tail_graph = None
+            if defer:
+                tail_graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(tail_graph, pool=graph.pool()):
+                    deferred_products()
 
             def run_step():
                 graph.replay()
+                if tail_graph is not None:
+                    buckets.start_exchange()
+                    tail_graph.replay()
                 buckets.finish()
+            run_step()
+            torch.cuda.synchronize()
+            attorch_b200.check_status()
             graphed = True
         except Exception as error:  # capture unsupported here: time the eager loop instead
             print(f'CUDA graph capture failed, timing eager launches: {error}', file=sys.stderr)
@@ -662,8 +687,10 @@ def main():
                    'autocast': str(spec['autocast']).replace('torch.', ''),
                    'parallelism': f'dp{world_size}',
                    'collective': ('none' if world_size == 1 else
-                                  'NCCL all-reduce of dW/db, ' + ('issued per dW block inside backward, overlapped'
-                                                                 if overlap else 'one call after the captured step')),
+                                  'NCCL all-reduce of dW/db, ' + (
+                                      'issued per dW block inside backward, overlapped' if overlap else
+                                      'one call between the two captured graphs of a step, overlapping the first '
+                                      "layer's dX" if defer and graphed else 'one call after the step')),
                    'cuda_graph': graphed,
                    'l2': 'per-step working set (operands, activations, gradients) exceeds the 126 MB L2; no flush',
                    'tflops_per_gpu': value / world_size,

@@ -42,7 +42,7 @@ def _two_layer_grads(x, w1, b1, w2, b2, dy):
     return dw1, db1, dw2, db2
 
 
-def _worker(rank: int, world_size: int, port: int, overlap_requested: bool) -> None:
+def _worker(rank: int, world_size: int, port: int, overlap_requested: bool, defer: bool = False) -> None:
     os.environ['MASTER_ADDR'] = '127.0.0.1'
     os.environ['MASTER_PORT'] = str(port)
     dist.init_process_group('gloo', rank=rank, world_size=world_size)
@@ -50,8 +50,9 @@ def _worker(rank: int, world_size: int, port: int, overlap_requested: bool) -> N
         x, w1, b1, w2, b2, dy = _inputs()
         layers = [attorch_b200.Linear(24, 32, act_func='gelu', device='cpu'),
                   attorch_b200.Linear(32, 16, device='cpu')]
-        buckets = GradientBuckets(layers, overlap=overlap_requested)
+        buckets = GradientBuckets(layers, overlap=overlap_requested, defer_first_input_grad=defer)
         assert buckets.world_size == world_size
+        assert (layers[0].defer_input_grad is not None) == defer and layers[1].defer_input_grad is None
         assert not buckets.overlap            # side streams exist only on CUDA
         assert buckets.flat.numel() == 24 * 32 + 32 + 32 * 16 + 16
         # The gradient destinations alias the flat bucket.
@@ -64,6 +65,13 @@ def _worker(rank: int, world_size: int, port: int, overlap_requested: bool) -> N
         layers[1].bias_grad_out.copy_(db2)
         for layer in layers:
             layer.grad_ready()
+        launched = []
+        if defer:
+            # What backward would hand over instead of launching the first layer's dX.
+            layers[0].defer_input_grad(lambda: launched.append(rank))
+            buckets.start_exchange()          # CPU ranks: the exchange happens in finish()
+            buckets.run_deferred()
+            assert launched == [rank] and not buckets._deferred
         buckets.finish()
         f_dw1, f_db1, f_dw2, f_db2 = _two_layer_grads(x, w1, b1, w2, b2, dy)
         torch.testing.assert_close(layers[0].weight_grad_out, f_dw1, rtol=1e-5, atol=1e-5)
@@ -77,6 +85,10 @@ def _worker(rank: int, world_size: int, port: int, overlap_requested: bool) -> N
 @pytest.mark.parametrize('overlap', [False, True])
 def test_data_parallel_gradients_match_full_batch(overlap):
     mp.spawn(_worker, args=(2, _free_port(), overlap), nprocs=2, join=True)
+
+
+def test_deferred_input_gradient_step():
+    mp.spawn(_worker, args=(2, _free_port(), False, True), nprocs=2, join=True)
 
 
 def test_shard_rows():

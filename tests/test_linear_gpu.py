@@ -484,3 +484,29 @@ def test_mlp_pair_shapes_of_config3():
     dy = (torch.randn(384, 4096, generator=gen) * 0.01).bfloat16()
     up = check_layer(x, w_up, None, 'silu', torch.randn(384, 14336, generator=gen).bfloat16())
     check_layer(up[0], w_down, None, None, dy)
+
+
+def test_deferred_input_gradient():
+    """
+    The data-parallel harness may hold back the first layer's dX (the last product of backward) and
+    launch it later: the input's gradient tensor is the buffer that product writes, and everything
+    equals the undeferred run bit for bit.
+    """
+    from attorch_b200.dp import GradientBuckets
+    x, w, b, dy = seeded((512, 256), 384, torch.bfloat16, seed=29)
+    results = []
+    for defer in (False, True):
+        layer = make_layer(w, b, 'gelu', torch.bfloat16)
+        buckets = GradientBuckets([layer], overlap=False, defer_first_input_grad=defer)
+        xg = x.to(DEV).requires_grad_(True)
+        layer(xg).backward(dy.to(DEV))
+        if defer:
+            assert len(buckets._deferred) == 1
+            buckets.start_exchange()        # world size 1: nothing to exchange
+            buckets.run_deferred()
+            assert not buckets._deferred
+        buckets.finish()
+        attorch_b200.check_status()
+        results.append((xg.grad.cpu(), layer.weight.grad.cpu(), layer.bias.grad.cpu()))
+    for plain, deferred in zip(*results):
+        assert torch.equal(plain, deferred)
