@@ -56,7 +56,7 @@ WORKLOADS = {
                global_tokens=None, param_dtype=torch.bfloat16, input_dtype=torch.bfloat16,
                autocast=None, scaling='weak'),
 }
-# Workload c4 (BASELINE config 4) is forward only and HBM-bound: see skinny_forward().
+# Workload c4 (BASELINE.json config 4) is forward only and HBM-bound: see skinny_forward().
 
 
 def measured_peaks():
@@ -251,7 +251,7 @@ def kernel_only(args, spec, tokens, device, lib):
 
 def skinny_forward(args, device, lib):
     """
-    BASELINE config 4: y = x @ W for fp16 x [M, 8192], W [8192, 28672], no bias, no activation, under
+    BASELINE.json config 4: y = x @ W for fp16 x [M, 8192], W [8192, 28672], no bias, no activation, under
     torch.no_grad(), through the module.  HBM-bound: the score is algorithmic bytes
     2 * (K * N + M * K + M * N) over the CUDA-event time, in GB/s.  W (448 MiB) exceeds the L2, so
     back-to-back launches are cold.

@@ -92,7 +92,7 @@ def save(name, store_inputs, x, w, b, dy, outs, **meta):
 
 
 def config1_inputs():
-    """BASELINE config 1: fp32, X [64, 128], 128 -> 256, bias, relu, every draw under seed 0."""
+    """BASELINE.json config 1: fp32, X [64, 128], 128 -> 256, bias, relu, every draw under seed 0."""
     torch.manual_seed(0)
     x = torch.randn(64, 128)
     torch.manual_seed(0)
@@ -134,7 +134,7 @@ def switch_point_inputs():
 
 def main():
     parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument('--reference', default='/root/reference')
+    parser.add_argument('--reference', required=True, help='path of a checkout of BobMcDear/attorch')
     args = parser.parse_args()
     attorch = load_reference(args.reference)
 
