@@ -29,6 +29,7 @@ int launch_hybrid_finish(const GemmArgs& g, int first_tile, int count, int worke
   a.aux = g.aux; a.ld_aux = g.ld_aux;
   a.out = g.out; a.ld_out = g.ld_out; a.out_dtype = g.out_dtype;
   a.act = g.act; a.act_param = g.act_param; a.save_grad = g.save_grad;
+  a.residual = g.residual; a.ld_res = g.ld_res;
   // 16 blocks per tile: enough parallelism for a handful of tiles.
   hybrid_finish_kernel<<<dim3(count, 16), 256, 0, stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
@@ -106,7 +107,7 @@ int launch_finish(float* partial, const GemmArgs& e, long long M, long long N, c
   if (blocks > cap) blocks = cap;
   streamk_finish_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
       partial, N, static_cast<int>(M), static_cast<int>(N), e.bias, e.bias_dtype, e.aux, e.ld_aux, e.out,
-      e.ld_out, e.out_dtype, e.act, e.act_param, e.save_grad);
+      e.ld_out, e.out_dtype, e.act, e.act_param, e.save_grad, e.residual, e.ld_res);
   ++g_launches;
   return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
 }
@@ -221,8 +222,21 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
                          int op_dtype, int out_dtype, int bias_dtype, int act, float act_param,
                          void* workspace, int64_t workspace_bytes, int* status, void* stream_,
                          int flags) {
+  return ab200_linear_forward_residual(x, w, bias, pre_act, out, nullptr, M, K, N, x_stride_m, x_stride_k,
+                                       w_stride_k, w_stride_n, ld_pre, ld_out, 0, op_dtype, out_dtype,
+                                       bias_dtype, act, act_param, workspace, workspace_bytes, status, stream_,
+                                       flags);
+}
+
+int ab200_linear_forward_residual(const void* x, const void* w, const void* bias, void* pre_act, void* out,
+                                  const void* residual, int64_t M, int64_t K, int64_t N, int64_t x_stride_m,
+                                  int64_t x_stride_k, int64_t w_stride_k, int64_t w_stride_n, int64_t ld_pre,
+                                  int64_t ld_out, int64_t ld_res, int op_dtype, int out_dtype, int bias_dtype,
+                                  int act, float act_param, void* workspace, int64_t workspace_bytes,
+                                  int* status, void* stream_, int flags) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M < 0 || K < 0 || N < 0) return ERR_BAD_SHAPE;
+  if (residual != nullptr && ld_res < N) return ERR_BAD_STRIDE;
   if (!fits_int(M) || !fits_int(K) || !fits_int(N)) return ERR_TOO_LARGE;
   if (!valid_dtype(op_dtype) || !valid_dtype(out_dtype) || (bias && !valid_dtype(bias_dtype)))
     return ERR_BAD_DTYPE;
@@ -248,6 +262,7 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
     a.bias = bias; a.bias_dtype = bias_dtype;
     a.act = act; a.act_param = act_param;
     a.save_grad = save_grad;
+    a.residual = residual; a.ld_res = ld_res;
     g_last_path = AB200_PATH_GENERIC;
     return launch_any(a, stream);
   }
@@ -280,6 +295,7 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
     e.bias = bias; e.bias_dtype = bias_dtype; e.aux = pre_act; e.ld_aux = ld_pre;
     e.out = out; e.ld_out = ld_out; e.out_dtype = out_dtype; e.act = act; e.act_param = act_param;
     e.save_grad = save_grad;
+    e.residual = residual; e.ld_res = ld_res;
     return launch_finish(static_cast<float*>(workspace), e, M, N, stream);
   }
 
@@ -291,6 +307,7 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
   g.bias = bias; g.bias_dtype = bias_dtype;
   g.act = act; g.act_param = act_param;
   g.save_grad = save_grad;
+  g.residual = residual; g.ld_res = ld_res;
   return run_tiles_or_split(p, workspace, workspace_bytes, stream, flags);
 }
 

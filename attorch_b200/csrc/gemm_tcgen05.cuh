@@ -62,6 +62,8 @@ struct GemmArgs {
   int bias_dtype;
   int act;
   float act_param;
+  const void* residual;   // optional [M, N] in the output dtype, added after the activation
+  long long ld_res;
   // Stream-K epilogue
   float* partial;         // fp32; mode 1: zero on entry, [M, N] (pitch ld_partial) or, if transposed,
                           // [N, M]; mode 2: 2 * workers dense TILE_M x BN slots, written through a map
@@ -303,6 +305,46 @@ __device__ __forceinline__ void add_bias_chunk(float (&v)[32], const void* bias,
 #pragma unroll
     for (int i = 0; i < 32; ++i)
       if (i < valid) v[i] += round_through(load_as_f32(bias, dt, col0 + i), round_dt);
+  }
+}
+
+// v[i] += residual[row, col0 + i] for the valid columns of a 32-column chunk of one row (16 bytes at a
+// time when the chunk is whole and aligned).
+__device__ __forceinline__ void add_residual_chunk(float (&v)[32], const void* residual, int dt, long long offset,
+                                                   int valid) {
+  const int elt = dt == DT_F32 ? 4 : 2;
+  const char* p = static_cast<const char*>(residual) + offset * elt;
+  if (valid == 32 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+    if (dt == DT_F32) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 r = __ldg(reinterpret_cast<const float4*>(p) + i);
+        v[4 * i] += r.x; v[4 * i + 1] += r.y; v[4 * i + 2] += r.z; v[4 * i + 3] += r.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 r = __ldg(reinterpret_cast<const uint4*>(p) + i);
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float lo, hi;
+          if (dt == DT_F16) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+            lo = f.x; hi = f.y;
+          } else {
+            lo = __uint_as_float(w[j] << 16);
+            hi = __uint_as_float(w[j] & 0xFFFF0000u);
+          }
+          v[8 * i + 2 * j] += lo;
+          v[8 * i + 2 * j + 1] += hi;
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < valid) v[i] += load_as_f32(residual, dt, offset + i);
   }
 }
 
@@ -572,6 +614,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (args.aux != nullptr) emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, v);
             act_fwd_inplace(v, args.act, args.act_param);
           }
+          if (args.residual != nullptr && row_ok)
+            add_residual_chunk(v, args.residual, args.out_dtype, static_cast<long long>(row) * args.ld_res + col0, valid);
           emit(&tmap_out, args.out, args.ld_out, (args.tma_store & 1) != 0, v);
         }
       }

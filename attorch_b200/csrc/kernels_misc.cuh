@@ -177,7 +177,8 @@ colsum_finish_kernel(const float* __restrict__ partial, int chunks, int N, void*
 __global__ void streamk_finish_kernel(float* __restrict__ partial, long long ld_partial, int M, int N,
                                       const void* bias, int bias_dtype, void* aux, long long ld_aux,
                                       void* out, long long ld_out, int out_dtype, int act,
-                                      float act_param, int save_grad) {
+                                      float act_param, int save_grad, const void* residual,
+                                      long long ld_res) {
   // Four consecutive columns per thread where the row pitch allows 16-byte accesses.
   const bool vec = (N % 4 == 0) && (ld_partial % 4 == 0);
   const int width = vec ? 4 : 1;
@@ -209,6 +210,7 @@ __global__ void streamk_finish_kernel(float* __restrict__ partial, long long ld_
         if (aux != nullptr) store_from_f32(aux, out_dtype, m * ld_aux + n, v[0]);
         act_fwd_inplace(v, act, act_param);
       }
+      if (residual != nullptr) v[0] += load_as_f32(residual, out_dtype, m * ld_res + n);
       store_from_f32(out, out_dtype, m * ld_out + n, v[0]);
     }
   }
@@ -229,6 +231,7 @@ struct HybridFinishArgs {
   void* aux; long long ld_aux;
   void* out; long long ld_out; int out_dtype;
   int act; float act_param; int save_grad;
+  const void* residual; long long ld_res;
 };
 
 constexpr int kMaxTailPieces = 160;   // at most one piece per worker; B200 has 148 SMs
@@ -284,6 +287,7 @@ __global__ void __launch_bounds__(256) hybrid_finish_kernel(const HybridFinishAr
         if (a.aux != nullptr) store_from_f32(a.aux, a.out_dtype, m * a.ld_aux + n, v[0]);
         act_fwd_inplace(v, a.act, a.act_param);
       }
+      if (a.residual != nullptr) v[0] += load_as_f32(a.residual, a.out_dtype, m * a.ld_res + n);
       store_from_f32(a.out, a.out_dtype, m * a.ld_out + n, v[0]);
     }
   }
@@ -366,6 +370,7 @@ struct AnyGemmArgs {
   const void* bias; int bias_dtype;
   int act; float act_param;
   int save_grad;          // aux receives act'(Z) instead of Z
+  const void* residual; long long ld_res;   // optional [M, N] in the output dtype, added after the activation
 };
 
 __global__ void __launch_bounds__(256) gemm_any_kernel(const AnyGemmArgs g) {
@@ -438,6 +443,7 @@ __global__ void __launch_bounds__(256) gemm_any_kernel(const AnyGemmArgs g) {
         if (g.aux != nullptr) store_from_f32(g.aux, g.out_dtype, m * g.ld_aux + n, v[0]);
         act_fwd_inplace(v, g.act, g.act_param);
       }
+      if (g.residual != nullptr) v[0] += load_as_f32(g.residual, g.out_dtype, m * g.ld_res + n);
       store_from_f32(g.out, g.out_dtype, m * g.ld_out + n, v[0]);
     }
   }

@@ -166,13 +166,15 @@ class LinearAutoGrad(torch.autograd.Function):
     overlap the remaining work; ``dw_chunks`` is ``n``.  ``defer_input_grad``, if given, is called with
     a function that launches the ``dX`` product instead of launching it: backward then returns the
     buffer ``dX`` will be written to once the caller runs that function (on any stream ordered after
-    backward), which lets a data-parallel step start its gradient exchange before ``dX``.
+    backward), which lets a data-parallel step start its gradient exchange before ``dX``.  ``residual``, a tensor
+    of the output's shape, is added to the output after the activation inside the kernel's epilogue
+    (``act(X W + b) + R``); its gradient is the upstream gradient.
     """
     @staticmethod
     def forward(ctx, input: Tensor, weight: Tensor, bias: Optional[Tensor] = None,
                 act_func: Optional[str] = None, weight_grad_out: Optional[Tensor] = None,
                 bias_grad_out: Optional[Tensor] = None, grad_ready=None, dw_chunks: int = 1,
-                defer_input_grad=None) -> Tensor:
+                defer_input_grad=None, residual: Optional[Tensor] = None) -> Tensor:
         assert weight.ndim == 2, \
             f'Weights must be 2D, received shape {weight.shape}'
         assert bias is None or bias.ndim == 1, \
@@ -191,7 +193,8 @@ class LinearAutoGrad(torch.autograd.Function):
         _, out_feat_dim = weight.shape
 
         requires_grad = (input.requires_grad or weight.requires_grad or
-                         (bias is not None and bias.requires_grad))
+                         (bias is not None and bias.requires_grad) or
+                         (residual is not None and residual.requires_grad))
         save_pre_act = requires_grad and (name is not None)
 
         output_dtype = get_output_dtype(input.dtype)
@@ -215,18 +218,37 @@ class LinearAutoGrad(torch.autograd.Function):
 
             ws_bytes = _cached_size('ab200_forward_workspace_bytes', batch_dim, in_feat_dim, out_feat_dim, _gemm_flags)
             workspace = _workspace(input.device, ws_bytes) if ws_bytes else None
-            _lib.check(lib.ab200_linear_forward(
-                _ptr(x_op), _ptr(w_op), _ptr(bias_op), _ptr(pre_act), _ptr(output),
+            residual_op = None
+            if residual is not None:
+                assert residual.shape == (*input.shape[:-1], out_feat_dim), \
+                    f'Incompatible residual ({residual.shape}) and output shape'
+                _require_cuda(residual, 'residual')
+                residual_op = residual.reshape(batch_dim, out_feat_dim)
+                if residual_op.dtype is not output_dtype or residual_op.stride(1) != 1 or \
+                        (batch_dim > 1 and residual_op.stride(0) < out_feat_dim):
+                    # Another dtype or layout than the kernel reads: one strided, converting copy.
+                    dense = torch.empty((batch_dim, out_feat_dim), dtype=output_dtype, device=input.device)
+                    if dense.numel():
+                        _lib.check(lib.ab200_cast_2d(
+                            residual_op.data_ptr(), dense.data_ptr(), batch_dim, out_feat_dim,
+                            residual_op.stride(0), residual_op.stride(1), _dtype_id(residual_op.dtype),
+                            _dtype_id(output_dtype), stream), 'ab200_cast_2d')
+                    residual_op = dense
+            _lib.check(lib.ab200_linear_forward_residual(
+                _ptr(x_op), _ptr(w_op), _ptr(bias_op), _ptr(pre_act), _ptr(output), _ptr(residual_op),
                 batch_dim, in_feat_dim, out_feat_dim,
                 x_op.stride(0), x_op.stride(1), w_op.stride(0), w_op.stride(1),
                 out_feat_dim, out_feat_dim,
+                residual_op.stride(0) if residual_op is not None and batch_dim > 1 else out_feat_dim,
                 _dtype_id(op_dtype), _dtype_id(output_dtype),
                 _dtype_id(bias_op.dtype) if bias_op is not None else 0,
                 act_id(name), 0.0 if param is None else param,
                 _ptr(workspace), ws_bytes, _ptr(scratch['status']), stream,
                 _gemm_flags | (_lib.FLAG_SAVE_DERIVATIVE if saves_derivative else 0)),
-                'ab200_linear_forward')
+                'ab200_linear_forward_residual')
 
+        ctx.residual_requires_grad = residual is not None and residual.requires_grad
+        ctx.residual_dtype = None if residual is None else residual.dtype
         ctx.param = param
         ctx.act_func = name
         ctx.bias_requires_grad = False if bias is None else bias.requires_grad
@@ -356,7 +378,8 @@ class LinearAutoGrad(torch.autograd.Function):
                 input_grad = input_grad.view(ctx.input_shape)
 
         # One slot per forward argument (attorch/linear_layer.py:158-161 pads with None).
-        return input_grad, weight_grad, bias_grad, None, None, None, None, None, None
+        residual_grad = output_grad.to(ctx.residual_dtype) if ctx.residual_requires_grad else None
+        return input_grad, weight_grad, bias_grad, None, None, None, None, None, None, residual_grad
 
 
 class Linear(nn.Linear):
@@ -395,7 +418,12 @@ class Linear(nn.Linear):
         # Optional callable that receives the launcher of dX instead of dX being launched (see LinearAutoGrad).
         self.defer_input_grad = None
 
-    def forward(self, input: Tensor) -> Tensor:
+    def forward(self, input: Tensor, residual: Optional[Tensor] = None) -> Tensor:
+        """
+        ``act(input @ weight + bias)``, as the reference's layer; with ``residual`` (a tensor of the
+        output's shape) the kernel's epilogue adds it to the result, which saves the separate pass
+        a caller's ``x + linear(...)`` makes over the output.
+        """
         return LinearAutoGrad.apply(input, self.weight, self.bias, self.act_func,
                                     self.weight_grad_out, self.bias_grad_out, self.grad_ready,
-                                    self.dw_chunks, self.defer_input_grad)
+                                    self.dw_chunks, self.defer_input_grad, residual)

@@ -154,6 +154,22 @@ int ab200_linear_forward(const void* x, const void* w, const void* bias, void* p
                          void* workspace, int64_t workspace_bytes, int* status, void* stream,
                          int flags);
 
+/*
+ * ab200_linear_forward with a residual added after the activation:
+ *     Y = act(X W + b) + R
+ * R: [M, N] in out_dtype with row pitch ld_res elements (>= N), or NULL (then this is
+ * ab200_linear_forward).  pre_act still receives Z (or act'(Z)), which does not involve R, so the
+ * backward entry points are unchanged; the gradient of R is the upstream gradient itself.  No
+ * counterpart in the reference, whose callers add the residual in a separate pass over Y
+ * (examples/wikitext-2/gpt.py:82).
+ */
+int ab200_linear_forward_residual(const void* x, const void* w, const void* bias, void* pre_act, void* out,
+                                  const void* residual, int64_t M, int64_t K, int64_t N, int64_t x_stride_m,
+                                  int64_t x_stride_k, int64_t w_stride_k, int64_t w_stride_n, int64_t ld_pre,
+                                  int64_t ld_out, int64_t ld_res, int op_dtype, int out_dtype, int bias_dtype,
+                                  int act, float act_param, void* workspace, int64_t workspace_bytes,
+                                  int* status, void* stream, int flags);
+
 /* Workspace the forward call may use for this shape and these flags (0 when it needs none). */
 int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N, int flags);
 

@@ -81,6 +81,13 @@ def test_argument_validation_without_gpu(lib):
     assert fwd(ld_out=4) == -5
     assert fwd(M=2 ** 31) == -9
     assert fwd(M=0) == 0            # empty batch: nothing to launch
+    # The residual variant: same checks, plus the residual's row pitch.
+    def fwd_res(ld_res, residual=fake, M=4):
+        return lib.ab200_linear_forward_residual(fake, fake, None, None, fake, residual, M, 8, 8, 8, 1, 8, 1, 8, 8,
+                                                 ld_res, 2, 2, 0, 0, 0.0, None, 0, None, None, 0)
+    assert fwd_res(4) == -5
+    assert fwd_res(4, residual=None, M=0) == 0
+    assert fwd_res(8, M=-1) == -2
     assert lib.ab200_act_backward(fake, None, fake, None, 4, 8, 8, 8, 8, 2, 2, 5, 0.0, None, 0, None) == -1
     assert lib.ab200_act_backward(fake, fake, fake, fake, 4, 8, 8, 8, 8, 2, 2, 5, 0.0, None, 0, None) == -6
     assert lib.ab200_cast_2d(fake, fake, -1, 2, 2, 1, 0, 2, None) == -2
