@@ -1,7 +1,7 @@
 """
 Benchmark of the fused linear layer (forward + backward) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|act] [--impl reference]
 
 For N > 1 launch one rank per GPU with torchrun (RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the
 environment).  Rank 0 prints one JSON line.
@@ -43,7 +43,7 @@ PEAK_FALLBACK = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustaine
 
 # DRAM bytes per launch of the dominant kernel (forward GEMM of c2) from the ncu capture summarised
 # in profiles/c2_kernel_fwd.md (algorithmic bytes: 224 MiB = 234.9e6).
-NCU_DRAM_BYTES_PER_LAUNCH = 286.3e6   # profiles/c2_kernel_fwd.md: 184.1 MB read + 102.2 MB written
+NCU_DRAM_BYTES_PER_LAUNCH = 255.3e6   # profiles/c2_kernel_fwd.md: 150.6 MB read + 104.7 MB written
 
 WORKLOADS = {
     'c2': dict(layers=[(4096, 4096, 'gelu', True)], tokens_per_gpu=8192, global_tokens=None,
