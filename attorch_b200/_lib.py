@@ -5,11 +5,13 @@ There is no fallback: if the library is missing or does not load, every entry po
 """
 
 import ctypes
+import os
 from pathlib import Path
 from typing import Optional
 
 PKG_DIR = Path(__file__).resolve().parent
-LIB_PATH = PKG_DIR / 'libattorch_b200.so'
+# The in-tree build, unless AB200_LIBRARY names another build of the same sources (A/B comparisons).
+LIB_PATH = Path(os.environ['AB200_LIBRARY']) if os.environ.get('AB200_LIBRARY') else PKG_DIR / 'libattorch_b200.so'
 
 # Element type ids (include/attorch_b200.h).
 F32, F16, BF16 = 0, 1, 2
@@ -23,6 +25,7 @@ FLAG_NO_TMA_STORE = 32
 FLAG_SAVE_DERIVATIVE = 64
 FLAG_WHOLE_TILES = 128
 FLAG_DROPOUT_PACKED = 256
+FLAG_RESERVE_SMS_SHIFT = 16   # bits 16-23: SMs a GEMM call leaves free
 ACT_SAVED_DERIVATIVE = 22
 
 PATH_TCGEN05, PATH_STREAMK, PATH_GENERIC = 1, 2, 3

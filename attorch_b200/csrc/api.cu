@@ -131,6 +131,7 @@ int run_tiles_or_split(TcProblem& p, void* workspace, int64_t workspace_bytes, c
   GemmArgs& g = p.g;
   p.allow_pair = pair_allowed(flags);
   p.allow_tma_store = !(flags & AB200_FLAG_NO_TMA_STORE);
+  p.reserve_sms = (flags >> AB200_FLAG_RESERVE_SMS_SHIFT) & 0xFF;
   const int bn = pick_bn(g.M, g.N);
   const int64_t need = static_cast<int64_t>(g.M) * g.N * 4;
   if (want_split(g.M, g.N, g.K, dtype_size(p.op_dtype)) && workspace != nullptr && workspace_bytes >= need) {

@@ -23,6 +23,8 @@ struct TcProblem {
   bool allow_tma_store;   // the epilogue may write its outputs with TMA stores
   // A partial last round that would keep at most half of the workers busy may run as half-width tiles.
   bool allow_split_tail;
+  // SMs this launch leaves free for work that runs beside it (a collective); 0 = none.
+  int reserve_sms;
   // Optional scratch for sharing out a partial last round of tiles (hybrid scheduling).
   void* tail_workspace;
   long long tail_workspace_bytes;
@@ -45,8 +47,10 @@ void set_gemm_cta_limit(int ctas);
 int last_schedule();
 void set_last_schedule(int mode);
 
-// AB200_TAIL_MODE: unset / 0 = a partial last round of tiles is shared out where that is possible;
-// 1 = never; 3 = it runs as half-width tiles whenever it fills at most half of the workers.
+// AB200_TAIL_MODE (read at every launch): unset / 0 = a last round of tiles that fills at most half of
+// the workers runs as half-width units (see launch_cfg); 1 = whole tiles only; 2 = a partial last round
+// is shared out over all workers instead (fp32 pieces summed by a finishing kernel) where a workspace
+// allows it; 3 = half-width units for every last round.
 int tail_mode_override();
 
 // Finishing pass of the hybrid schedule (defined next to the kernel, in api.cu): shared-out tiles
@@ -94,7 +98,7 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   if (Cfg::B_MN)
     rc = encode_2d(&tb, p.op_dtype, p.b, p.g.N, p.g.K, p.b_pitch * elt, Cfg::MN_ATOM, Cfg::BKE, Cfg::MN_BASE32);
   else
-    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.K, p.g.N, p.b_pitch * elt, Cfg::BKE, Cfg::BN_CTA);
+    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.K, p.g.N, p.b_pitch * elt, Cfg::BKE, Cfg::B_BOX_ROWS);
   if (rc != OK) return rc;
 
   GemmArgs g = p.g;
@@ -146,28 +150,44 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   const long long tiles = static_cast<long long>(g.tiles_m) * g.tiles_n;
   const long long work = g.stream_k ? tiles * g.k_blocks : tiles;
   int cap = max_workers[dev];
-  const int limit = gemm_cta_limit();
+  int limit = gemm_cta_limit();
+  if (p.reserve_sms > 0) {
+    const int rest = sm_count() - p.reserve_sms > Cfg::CTAS ? sm_count() - p.reserve_sms : Cfg::CTAS;
+    limit = (limit > 0 && limit < rest) ? limit : rest;
+  }
   if (limit > 0 && limit / Cfg::CTAS < cap) cap = limit / Cfg::CTAS > 0 ? limit / Cfg::CTAS : 1;
-  const int workers = static_cast<int>(work < cap ? work : cap);
+  int workers = static_cast<int>(work < cap ? work : cap);
   if (workers <= 0) return OK;
 
   // Hybrid schedule: when the last round of whole tiles would be mostly idle (at most 80 % of the
   // workers busy), its tiles' reductions are shared out over all workers instead.
   int tail_tiles = 0;
   CUtensorMap tpartial = ta;
-  // Opt-in (AB200_TAIL_MODE=3): a last round filling at most half of the workers runs as twice as
-  // many half-width tiles (one half-length round, fused epilogue, nothing to finish).  Measured on
-  // the 4096 x 4096 x 8192 weight-gradient product it is no faster than whole tiles or the shared-out
-  // round (212-216 us each, same process): sustained GEMMs run at the power limit, where idle SMs
-  // let the busy ones clock higher, so evening out the last round buys nothing there.
-  const int last_round = tiles > workers ? static_cast<int>(tiles % workers) : 0;
+  // Half-width last round: where the last round of whole tiles would fill at most half of the workers,
+  // its tiles run as twice as many units of BN / 2 columns, handed out like tiles: that round then
+  // takes about half as long (weight-gradient product of 8192 tokens, 4096 -> 4096: 256 pair tiles on
+  // 74 CTA pairs = 3 rounds + 34 tiles, 3.5 rounds instead of 4), bit-identical to whole tiles and with
+  // the fused epilogue.  Measured on that shape in bursts of 20 launches it is as fast as whole tiles
+  // (207 us both; the shared-out round of mode 2: 210 us): the GEMMs run at the power limit, where a
+  // half-empty round lets the busy SMs clock higher, so the gain shows only where the last round is
+  // emptier.  Forcing it on a full last round (AB200_TAIL_MODE=3) to halve the one epilogue nothing
+  // overlaps made the forward pass with bias, gelu and a saved tensor slower (230 vs 217 us): the
+  // half-width units fetch the tile's A rows twice.
+  // AB200_TAIL_MODE: unset / 0 this rule; 1 whole tiles only; 2 prefer the shared-out round below;
+  // 3 half-width units for every last round, full ones too.
+  const long long rounds = (tiles + cap - 1) / cap;
+  const int last_round = static_cast<int>(tiles - (rounds - 1) * cap);   // tiles in the last round
   const int tail_mode = tail_mode_override();
-  if (!g.stream_k && p.allow_split_tail && Cfg::BN >= 64 && last_round > 0 && last_round * 2 <= workers &&
-      tail_mode == 3) {
+  if (!g.stream_k && p.allow_split_tail && Cfg::kHalfUnits && tail_mode != 1 && tail_mode != 2 && cap > 1 &&
+      (last_round * 2 <= cap || tail_mode == 3)) {
     g.stream_k = 3;
     g.dp_tiles = static_cast<int>(tiles) - last_round;
+    // A single round of few tiles: its half-width units can use up to twice as many workers.
+    if (rounds == 1) workers = 2 * last_round < cap ? 2 * last_round : cap;
   }
-  if (!g.stream_k && tail_mode != 1 && p.tail_workspace != nullptr && tiles > workers && g.k_blocks >= 16) {
+  // Shared-out last round (AB200_TAIL_MODE=2, or where half-width units are not possible).
+  if (!g.stream_k && tail_mode != 1 && p.tail_workspace != nullptr && tiles > workers && g.k_blocks >= 16 &&
+      workers <= kMaxTailPieces) {
     const int rem = static_cast<int>(tiles % workers);
     // Two slots per worker (its share of the tail touches at most two tiles).
     const long long need = 2ll * workers * Cfg::TILE_M * Cfg::BN * 4;

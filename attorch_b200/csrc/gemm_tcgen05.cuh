@@ -100,6 +100,12 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + kStoreBytes + 1024 + kBarrierBytes;
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;   // power of two for BN in {16..256}
   static constexpr int MN_ATOM = 128 / ELT;      // elements in one 128-byte row of an MN-major tile
+  // A K-major B tile is fetched as two boxes of half its rows, so that a half-width unit (see
+  // SegmentIter, mode 3) fetches exactly the rows it multiplies.
+  static constexpr int B_BOX_ROWS = BN_CTA >= 16 ? BN_CTA / 2 : BN_CTA;
+  // Can a tile be computed as two units of BN / 2 columns?  Each CTA's share of a unit must be whole
+  // TMA boxes: half a K-major tile, or whole 128-byte column blocks of an MN-major one.
+  static constexpr bool kHalfUnits = BN_ >= 64 && (B_MN_ ? (BN_CTA / 2) % (128 / ELT_) == 0 : BN_CTA >= 16);
   static constexpr int MN_BOX_BYTES = BKE * 128; // one TMA box of an MN-major tile
   // MN-major tiles of 4-byte elements use the 128-byte swizzle with 32-byte units, whose pattern
   // repeats every 4 rows of K; everything else the ordinary one (16-byte units, 8 rows).
@@ -112,6 +118,11 @@ struct GemmCfg {
   static_assert(!B_MN_ || BN_CTA % (128 / ELT_) == 0, "an MN-major B tile is made of 128-byte wide boxes");
   static_assert(CTAS_ == 1 || CTAS_ == 2, "one CTA or a pair");
 };
+
+// Most workers whose pieces the finishing pass of the hybrid schedule can sum for one tile (it keeps
+// one slot index per worker in shared memory); launches with more workers use whole tiles instead.
+// B200 has 148 SMs.
+constexpr int kMaxTailPieces = 160;
 
 struct Segment {
   int m_blk, n_blk;
@@ -147,7 +158,8 @@ __host__ __device__ __forceinline__ void tile_to_blocks(int t, int tiles_m, int 
 //   stream_k = 3  the first dp_tiles tiles whole, as in mode 0; each remaining tile as two units of
 //                 BN / 2 columns (unit h = column half h % 2 of tile dp_tiles + h / 2), handed out
 //                 like tiles.  A last round that would occupy at most half of the workers then takes
-//                 half as long, and every unit still ends in the fused epilogue.
+//                 half as long, every unit still ends in the fused epilogue, and the epilogue that
+//                 nothing overlaps - the one after a worker's last main loop - is that of half a tile.
 struct SegmentIter {
   long long unit, unit_end;   // position in the shared-out (tile, k-block) units
   int tile, tile_end;         // next whole tile
@@ -183,11 +195,17 @@ struct SegmentIter {
       s.partial = 0;
       s.sk_index = 0;
     } else if (a.stream_k == 3) {
-      if (unit >= unit_end) return false;
-      t = first_shared + static_cast<int>(unit >> 1);
+      // Half-width units; one whose columns all lie beyond N (second half of a ragged last column
+      // block) is skipped - by every role alike, since all walk this same sequence.
+      for (;;) {
+        if (unit >= unit_end) return false;
+        t = first_shared + static_cast<int>(unit >> 1);
+        s.n_off = static_cast<int>(unit & 1) * (bn / 2);
+        unit += stride;
+        tile_to_blocks(t, a.tiles_m, a.tiles_n, a.group_m, s.m_blk, s.n_blk);
+        if (s.n_blk * bn + s.n_off < a.N) break;
+      }
       s.n_cols = bn / 2;
-      s.n_off = static_cast<int>(unit & 1) * (bn / 2);
-      unit += stride;
       s.kb0 = 0;
       s.kb1 = a.k_blocks;
       s.partial = 0;
@@ -443,18 +461,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       while (ok && it.next(args, seg, BN)) {
         const int m0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM;      // this CTA's rows of A
-        // This CTA's columns of B.  A half-width unit needs only the first half of what the boxes
-        // fetch; the rest lands in shared memory unread (same byte count for the barrier).
-        const int n0 = seg.n_blk * BN + seg.n_off + static_cast<int>(cta) * (seg.n_cols / CTAS);
+        // This CTA's columns of B: BN_CTA of them, or half as many for a half-width unit, which
+        // fetches (and expects the bytes of) only those.
+        const int b_cols = seg.n_cols / CTAS;
+        const int n0 = seg.n_blk * BN + seg.n_off + static_cast<int>(cta) * b_cols;
+        const uint32_t stage_tx = Cfg::A_BYTES + static_cast<uint32_t>(b_cols) * 128u;
         for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
           if (!wait(empty_bar(s), ph ^ 1u, DEV_TIMEOUT_PRODUCER)) { ok = false; break; }
           // The pair's loads all complete on the leader's barrier, which expects both CTAs' bytes.
           uint32_t full = full_bar(s);
           if constexpr (kPair) {
-            if (cta == 0) ptx::mbar_arrive_expect_tx(full, Cfg::STAGE_BYTES * CTAS);
+            if (cta == 0) ptx::mbar_arrive_expect_tx(full, stage_tx * CTAS);
             full = ptx::map_to_cta(full, 0);
           } else {
-            ptx::mbar_arrive_expect_tx(full, Cfg::STAGE_BYTES);
+            ptx::mbar_arrive_expect_tx(full, stage_tx);
           }
           const uint32_t a_dst = smem_base + s * Cfg::STAGE_BYTES;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
@@ -469,9 +489,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if constexpr (Cfg::B_MN) {
 #pragma unroll
             for (int j = 0; j < Cfg::BN_CTA / Cfg::MN_ATOM; ++j)
-              ptx::tma_load_2d<kPair>(b_dst + j * Cfg::MN_BOX_BYTES, &tmap_b, full, n0 + j * Cfg::MN_ATOM, k0);
+              if (j * Cfg::MN_ATOM < b_cols)
+                ptx::tma_load_2d<kPair>(b_dst + j * Cfg::MN_BOX_BYTES, &tmap_b, full, n0 + j * Cfg::MN_ATOM, k0);
           } else {
-            ptx::tma_load_2d<kPair>(b_dst, &tmap_b, full, k0, n0);
+#pragma unroll
+            for (int j = 0; j < Cfg::BN_CTA / Cfg::B_BOX_ROWS; ++j)
+              if (j * Cfg::B_BOX_ROWS < b_cols)
+                ptx::tma_load_2d<kPair>(b_dst + j * Cfg::B_BOX_ROWS * 128, &tmap_b, full, k0, n0 + j * Cfg::B_BOX_ROWS);
           }
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }

@@ -234,7 +234,6 @@ struct HybridFinishArgs {
   const void* residual; long long ld_res;
 };
 
-constexpr int kMaxTailPieces = 160;   // at most one piece per worker; B200 has 148 SMs
 
 __global__ void __launch_bounds__(256) hybrid_finish_kernel(const HybridFinishArgs a) {
   // Slots of the pieces of this tile, in worker order.

@@ -6,11 +6,18 @@ needs at scale: one process per GPU, the batch (token) dimension split evenly ac
 replicated, and a SUM all-reduce of every layer's ``dW`` / ``db`` - the only collective, issued with
 ``torch.distributed`` (NCCL over NVLink / NVSwitch on GPUs, gloo on CPUs for tests).
 
-Each layer writes its weight and bias gradient straight into a slice of one flat bucket
-(no copy), and as soon as the kernels that produce them are enqueued the bucket slice is
-all-reduced on a side stream while the layer's ``dX`` product - and the backward of the layers
-before it - still run on the compute stream.  Because the upstream gradient is given per token,
-SUM reproduces the single-GPU full-batch gradient.
+Each layer's kernels write its weight and bias gradient straight into a slice of one flat bucket
+(no copy), and every parameter's ``.grad`` is a view of that bucket, so after ``finish()`` an
+optimizer reads the sum over ranks in place.  As soon as the kernels that produce a slice are
+enqueued the slice is all-reduced on a side stream while the layer's ``dX`` product - and the
+backward of the layers before it - still run on the compute stream.  Because the upstream gradient
+is given per token, SUM reproduces the single-GPU full-batch gradient.
+
+The exchange may use a narrower type than the parameters (``grad_dtype``): under bf16 autocast with
+fp32 master weights the kernels then write ``dW`` / ``db`` in bf16, the all-reduce moves half the
+bytes, and the result is widened into the fp32 ``.grad`` on the side stream.  That is the
+reference's own arithmetic (its backward computes ``dW`` in the autocast dtype,
+attorch/linear_layer.py:152-156, and the engine casts it to the parameter's dtype).
 
 A step that is replayed from CUDA graphs cannot issue NCCL calls from inside backward; for it the
 harness can hold back the first layer's ``dX`` (``defer_first_input_grad``): the step becomes "graph 1:
@@ -26,7 +33,10 @@ import torch.distributed as dist
 from torch import Tensor
 
 from . import _lib
+from . import linear_layer as _layer
 from .linear_layer import Linear
+
+_DTYPE_IDS = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
 
 
 def shard_rows(tensor: Tensor, rank: int, world_size: int) -> Tensor:
@@ -41,7 +51,7 @@ def shard_rows(tensor: Tensor, rank: int, world_size: int) -> Tensor:
 class GradientBuckets:
     """
     One flat gradient buffer per model; every Linear gets views of it as its ``dW`` / ``db``
-    destinations and a callback that all-reduces its slice.
+    destinations, its parameters' ``.grad`` alias it, and a callback all-reduces the layer's slice.
 
     Args:
         layers: The Linear layers, in forward order.
@@ -59,32 +69,39 @@ class GradientBuckets:
             step can then be two replayable pieces with the exchange started in between:
             forward + backward without that dX; ``start_exchange()``; ``run_deferred()``;
             ``finish()``.  The input's ``.grad`` is complete only after ``run_deferred()``.
+        grad_dtype: Element type the gradients are computed and exchanged in; None for the
+            parameters' own.  If it differs, ``.grad`` (in the parameters' dtype) receives the
+            widened sum after the exchange.
     """
     def __init__(self, layers: Iterable[Linear], process_group=None, overlap: bool = True,
-                 comm_sms: int = 16, dw_chunks: int = 2, defer_first_input_grad: bool = False) -> None:
+                 comm_sms: int = 16, dw_chunks: int = 2, defer_first_input_grad: bool = False,
+                 grad_dtype: Optional[torch.dtype] = None) -> None:
         self.layers: List[Linear] = list(layers)
         self.group = process_group
         self.world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
         first = self.layers[0].weight
         self.device = first.device
         self.dtype = first.dtype
+        self.grad_dtype = grad_dtype if grad_dtype is not None else self.dtype
         total = sum(layer.weight.numel() + (layer.bias.numel() if layer.bias is not None else 0)
                     for layer in self.layers)
-        self.flat = torch.zeros(total, dtype=self.dtype, device=self.device)
+        # What the kernels write and the collective reduces.
+        self.flat = torch.zeros(total, dtype=self.grad_dtype, device=self.device)
+        # What .grad aliases: the same buffer, or a second one in the parameters' dtype.
+        self.widen = self.grad_dtype is not self.dtype
+        self.flat_grad = torch.zeros(total, dtype=self.dtype, device=self.device) if self.widen else self.flat
+        if self.widen and self.device.type != 'cuda':
+            raise RuntimeError('a narrower exchange dtype needs the CUDA cast kernel: no CPU path')
         self.slices: List[Tensor] = []
+        self._offsets: List[int] = []
         self.overlap = overlap and self.device.type == 'cuda' and self.world_size > 1
+        self.comm_sms = comm_sms
         self.comm_stream = torch.cuda.Stream(self.device) if self.overlap else None
         self._pending: List[torch.cuda.Event] = []
-        self._gemm_ctas = 0
         self._deferred: List = []
+        self._grad_views: List = []
         if defer_first_input_grad:
             self.layers[0].defer_input_grad = self._deferred.append
-        if self.overlap:
-            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-            self._gemm_ctas = max(2, sms - comm_sms)
-        elif self.device.type == 'cuda' and self.world_size > 1:
-            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-            self._exchange_ctas = max(2, sms - comm_sms)
         offset = 0
         for index, layer in enumerate(self.layers):
             if layer.weight.dtype is not self.dtype:
@@ -92,14 +109,31 @@ class GradientBuckets:
             begin = offset
             n = layer.weight.numel()
             layer.weight_grad_out = self.flat[offset:offset + n].view_as(layer.weight)
+            weight_grad = self.flat_grad[offset:offset + n].view_as(layer.weight)
             offset += n
+            bias_grad = None
             if layer.bias is not None:
                 n = layer.bias.numel()
                 layer.bias_grad_out = self.flat[offset:offset + n]
+                bias_grad = self.flat_grad[offset:offset + n]
                 offset += n
             self.slices.append(self.flat[begin:offset])
+            self._offsets.append(begin)
+            self._grad_views.append((weight_grad, bias_grad))
             layer.grad_ready = self._make_callback(index)
             layer.dw_chunks = dw_chunks if self.overlap else 1
+        self.bind_grads()
+
+    def bind_grads(self) -> None:
+        """
+        Points every parameter's ``.grad`` at its view of the bucket.  Backward writes the bucket
+        through the layer's destination buffers and returns no gradient of its own for them, so
+        these aliases are what an optimizer reads (after ``finish()``).
+        """
+        for layer, (weight_grad, bias_grad) in zip(self.layers, self._grad_views):
+            layer.weight.grad = weight_grad
+            if layer.bias is not None:
+                layer.bias.grad = bias_grad
 
     def _make_callback(self, index: int):
         def grad_ready(block: int = 0, blocks: int = 1) -> None:
@@ -112,20 +146,30 @@ class GradientBuckets:
             per_block = layer.weight.numel() // blocks
             begin = block * per_block
             end = (block + 1) * per_block if block + 1 < blocks else whole.numel()
-            self._reduce_async(whole[begin:end])
+            self._reduce_async(self._offsets[index] + begin, self._offsets[index] + end)
         return grad_ready
 
-    def _reduce_async(self, piece: Tensor) -> None:
+    def _widen(self, begin: int, end: int) -> None:
+        """flat_grad[begin:end] <- flat[begin:end] in the parameters' dtype, on the current stream."""
+        src, dst = self.flat[begin:end], self.flat_grad[begin:end]
+        _lib.check(_lib.load().ab200_cast_2d(
+            src.data_ptr(), dst.data_ptr(), 1, end - begin, end - begin, 1,
+            _DTYPE_IDS[self.grad_dtype], _DTYPE_IDS[self.dtype],
+            torch.cuda.current_stream(self.device).cuda_stream), 'ab200_cast_2d')
+
+    def _reduce_async(self, begin: int, end: int) -> None:
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ready)
-            dist.all_reduce(piece, op=dist.ReduceOp.SUM, group=self.group)
+            dist.all_reduce(self.flat[begin:end], op=dist.ReduceOp.SUM, group=self.group)
+            if self.widen:
+                self._widen(begin, end)
             done = torch.cuda.Event()
             done.record(self.comm_stream)
         self._pending.append(done)
         # The GEMMs enqueued from here to finish() run beside the collective.
-        _lib.load().ab200_set_gemm_cta_limit(self._gemm_ctas)
+        _layer.set_reserved_sms(self.device.index, self.comm_sms)
 
     def start_exchange(self) -> None:
         """
@@ -142,13 +186,15 @@ class GradientBuckets:
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ready)
             dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+            if self.widen:
+                self._widen(0, self.flat.numel())
             done = torch.cuda.Event()
             done.record(self.comm_stream)
         self._pending.append(done)
 
-    def exchange_cta_limit(self) -> int:
-        """CTAs a GEMM should be limited to while it runs beside the exchange (0: no limit)."""
-        return getattr(self, '_exchange_ctas', self._gemm_ctas)
+    def exchange_sms(self) -> int:
+        """SMs a GEMM should leave free while it runs beside the exchange (0: none)."""
+        return self.comm_sms if (self.device.type == 'cuda' and self.world_size > 1) else 0
 
     def run_deferred(self) -> None:
         """Launches the products ``defer_first_input_grad`` held back, on the current stream."""
@@ -159,23 +205,31 @@ class GradientBuckets:
     def finish(self) -> None:
         """
         Completes the gradient exchange of one step: after it returns (in stream order on the
-        current stream) every layer's ``.grad`` holds the sum over ranks.
+        current stream) every parameter's ``.grad`` holds the sum over ranks.
         """
-        if self.world_size == 1:
-            return
-        if self.overlap or self._pending:
+        if self._pending:
             current = torch.cuda.current_stream(self.device)
             for done in self._pending:
                 current.wait_event(done)
             self._pending.clear()
             if self.overlap:
-                _lib.load().ab200_set_gemm_cta_limit(0)
-        else:
+                _layer.set_reserved_sms(self.device.index, 0)
+            return
+        if self.world_size > 1:
             dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+        if self.widen:
+            self._widen(0, self.flat.numel())
 
     def zero_grad(self) -> None:
-        """Drops the ``.grad`` aliases so that the next backward writes the bucket afresh."""
-        for layer in self.layers:
-            layer.weight.grad = None
+        """
+        Prepares the next step.  The kernels overwrite the bucket (they do not accumulate), so
+        nothing needs clearing; the ``.grad`` aliases are kept, or restored if something dropped them.
+        """
+        for layer, (weight_grad, bias_grad) in zip(self.layers, self._grad_views):
+            grad = layer.weight.grad
+            if grad is None or grad.data_ptr() != weight_grad.data_ptr():
+                layer.weight.grad = weight_grad
             if layer.bias is not None:
-                layer.bias.grad = None
+                grad = layer.bias.grad
+                if grad is None or grad.data_ptr() != bias_grad.data_ptr():
+                    layer.bias.grad = bias_grad

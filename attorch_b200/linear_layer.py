@@ -41,6 +41,27 @@ def set_save_derivative(enabled: bool) -> bool:
     return previous
 
 
+# Per device index: SMs the persistent GEMM kernels leave free (for a collective that runs beside
+# them); handed to every GEMM call in bits 16-23 of its flags.
+_reserved_sms: Dict[int, int] = {}
+
+
+def set_reserved_sms(device_index: int, sms: int) -> int:
+    """
+    Makes every GEMM launched on that device from now on leave ``sms`` SMs free (0: none);
+    returns the previous value.  A data-parallel step sets it while its gradient exchange is in
+    flight: a persistent GEMM that held every SM would make the collective wait for it to end.
+    """
+    previous = _reserved_sms.get(device_index, 0)
+    _reserved_sms[device_index] = max(0, min(255, int(sms)))
+    return previous
+
+
+def _flags_for(device: torch.device) -> int:
+    reserve = _reserved_sms.get(device.index, 0) if _reserved_sms else 0
+    return _gemm_flags | (reserve << _lib.FLAG_RESERVE_SMS_SHIFT)
+
+
 def set_gemm_flags(flags: int) -> int:
     """Sets the AB200_FLAG_* bits passed to the GEMM entry points; returns the previous value."""
     global _gemm_flags
@@ -244,7 +265,7 @@ class LinearAutoGrad(torch.autograd.Function):
                 _dtype_id(bias_op.dtype) if bias_op is not None else 0,
                 act_id(name), 0.0 if param is None else param,
                 _ptr(workspace), ws_bytes, _ptr(scratch['status']), stream,
-                _gemm_flags | (_lib.FLAG_SAVE_DERIVATIVE if saves_derivative else 0)),
+                _flags_for(input.device) | (_lib.FLAG_SAVE_DERIVATIVE if saves_derivative else 0)),
                 'ab200_linear_forward_residual')
 
         ctx.residual_requires_grad = residual is not None and residual.requires_grad
@@ -345,7 +366,7 @@ class LinearAutoGrad(torch.autograd.Function):
                         batch_dim, rows, out_feat_dim,
                         x_part.stride(0), x_part.stride(1), pre_act_grad.stride(0), pre_act_grad.stride(1),
                         dw_part.stride(0), _dtype_id(op_dtype), _dtype_id(weight_grad.dtype),
-                        _ptr(workspace), ws_bytes, status, stream, _gemm_flags),
+                        _ptr(workspace), ws_bytes, status, stream, _flags_for(device)),
                         'ab200_linear_backward_weight')
                     if ctx.grad_ready is not None:
                         ctx.grad_ready(c, chunks)
@@ -368,7 +389,7 @@ class LinearAutoGrad(torch.autograd.Function):
                             batch_dim, in_feat_dim, out_feat_dim,
                             dz.stride(0), dz.stride(1), w.stride(0), w.stride(1),
                             in_feat_dim, _dtype_id(op_dtype), dx_dtype,
-                            _ptr(space), nbytes, _ptr(run_scratch['status']), run_stream, _gemm_flags),
+                            _ptr(space), nbytes, _ptr(run_scratch['status']), run_stream, _flags_for(device)),
                             'ab200_linear_backward_input')
 
                 if ctx.defer_input_grad is not None:
@@ -377,8 +398,15 @@ class LinearAutoGrad(torch.autograd.Function):
                     launch_input_grad()
                 input_grad = input_grad.view(ctx.input_shape)
 
-        # One slot per forward argument (attorch/linear_layer.py:158-161 pads with None).
+        # One slot per forward argument (attorch/linear_layer.py:158-161 pads with None).  A gradient
+        # that was written into a caller-supplied buffer is not returned as well: autograd would
+        # accumulate a copy of it into ``.grad`` (the buffer's owner, e.g. a gradient bucket, binds
+        # ``.grad`` to the buffer itself).
         residual_grad = output_grad.to(ctx.residual_dtype) if ctx.residual_requires_grad else None
+        if weight_grad_out is not None:
+            weight_grad = None
+        if bias_grad_out is not None:
+            bias_grad = None
         return input_grad, weight_grad, bias_grad, None, None, None, None, None, None, residual_grad
 
 

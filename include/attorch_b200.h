@@ -91,6 +91,11 @@ extern "C" {
 #define AB200_FLAG_SAVE_DERIVATIVE 64 /* forward: pre_act receives act'(Z) instead of Z            */
 #define AB200_FLAG_WHOLE_TILES 128  /* never share out or halve a partial last round of tiles   */
 #define AB200_FLAG_DROPOUT_PACKED 256 /* activation layers: the cheaper dropout stream (see below) */
+/* Bits 16-23 of the flags of a GEMM entry point: the number of SMs (0-255) the persistent kernel of
+ * that call leaves free, for a collective that runs beside it (same purpose as
+ * ab200_set_gemm_cta_limit, but per call instead of process-wide). */
+#define AB200_FLAG_RESERVE_SMS_SHIFT 16
+#define AB200_FLAG_RESERVE_SMS(n) (((n) & 0xFF) << AB200_FLAG_RESERVE_SMS_SHIFT)
 
 /* Which kernel the last call on this host thread chose: 1 tcgen05 tile-parallel, 2 tcgen05
  * swap-AB stream-K, 3 generic CUDA-core.  For tests and benchmarks. */

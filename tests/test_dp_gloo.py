@@ -78,6 +78,12 @@ def _worker(rank: int, world_size: int, port: int, overlap_requested: bool, defe
         torch.testing.assert_close(layers[0].bias_grad_out, f_db1, rtol=1e-5, atol=1e-5)
         torch.testing.assert_close(layers[1].weight_grad_out, f_dw2, rtol=1e-5, atol=1e-5)
         torch.testing.assert_close(layers[1].bias_grad_out, f_db2, rtol=1e-5, atol=1e-5)
+        # What an optimizer reads: every .grad is the bucket itself, so it holds the sum over ranks.
+        assert layers[0].weight.grad.data_ptr() == buckets.flat.data_ptr()
+        torch.testing.assert_close(layers[0].weight.grad, f_dw1, rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(layers[1].bias.grad, f_db2, rtol=1e-5, atol=1e-5)
+        buckets.zero_grad()
+        assert layers[1].weight.grad.data_ptr() == layers[1].weight_grad_out.data_ptr()
     finally:
         dist.destroy_process_group()
 
@@ -104,5 +110,73 @@ def test_single_process_bucket_is_a_no_op():
     layer.weight_grad_out.fill_(2.0)
     buckets.finish()
     assert torch.all(layer.weight_grad_out == 2.0)
+
+
+def test_grads_alias_the_bucket():
+    """
+    ``.grad`` of every parameter is a view of the flat bucket from construction on (backward writes
+    the bucket and returns no gradient of its own for these parameters, so autograd never replaces
+    the alias with a copy), and ``zero_grad`` restores an alias that something dropped.
+    """
+    layers = [attorch_b200.Linear(4, 6, device='cpu'), attorch_b200.Linear(6, 2, bias=False, device='cpu')]
+    buckets = GradientBuckets(layers)
+    assert buckets.flat.numel() == 4 * 6 + 6 + 6 * 2
+    assert layers[0].weight.grad.data_ptr() == buckets.flat.data_ptr()
+    assert layers[0].bias.grad.data_ptr() == buckets.flat[24:].data_ptr()
+    assert layers[1].weight.grad.data_ptr() == buckets.flat[30:].data_ptr()
+    layers[0].weight_grad_out.fill_(3.0)
+    assert torch.all(layers[0].weight.grad == 3.0)
+    layers[0].weight.grad = None
     buckets.zero_grad()
-    assert layer.weight.grad is None
+    assert layers[0].weight.grad.data_ptr() == buckets.flat.data_ptr()
+
+
+def test_narrow_exchange_dtype_needs_cuda():
+    layer = attorch_b200.Linear(4, 6, device='cpu')
+    with pytest.raises(RuntimeError, match='no CPU path'):
+        GradientBuckets([layer], grad_dtype=torch.bfloat16)
+
+
+def _leaving_worker(rank: int, world_size: int, port: int, result_queue) -> None:
+    """Rank 1 leaves between steps; rank 0's next collective must end with an error, not hang."""
+    import datetime
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world_size, timeout=datetime.timedelta(seconds=5))
+    layer = attorch_b200.Linear(8, 4, device='cpu')
+    buckets = GradientBuckets([layer], overlap=False)
+    layer.weight_grad_out.fill_(float(rank + 1))
+    layer.bias_grad_out.fill_(1.0)
+    buckets.finish()                                   # step 1: both ranks take part
+    assert torch.all(layer.weight.grad == 3.0)
+    if rank == 1:
+        # Leaves between steps with nothing in flight (no destroy_process_group: it is gone).
+        result_queue.put(('left', rank))
+        result_queue.close()
+        result_queue.join_thread()
+        os._exit(0)
+    try:
+        layer.weight_grad_out.fill_(1.0)
+        buckets.finish()                               # step 2: the peer is gone
+        result_queue.put(('no error', rank))
+    except Exception as error:                         # gloo reports the lost peer or the time-out
+        result_queue.put(('error', type(error).__name__))
+    result_queue.close()
+    result_queue.join_thread()
+    os._exit(0)
+
+
+def test_rank_leaving_between_steps_ends_the_next_collective_with_an_error():
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaving_worker, args=(r, 2, port, queue)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict()
+    for _ in range(2):
+        kind, what = queue.get(timeout=120)
+        results[kind] = what
+    for p in procs:
+        p.join(timeout=60)
+    assert 'left' in results and 'error' in results, results

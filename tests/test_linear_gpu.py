@@ -446,13 +446,14 @@ def test_weight_gradient_in_row_blocks():
         assert torch.equal(a, c)
 
 
-def test_shared_out_last_round_of_tiles():
+def test_shared_out_last_round_of_tiles(monkeypatch):
     """
-    90 pair tiles on 74 CTA pairs: the 16 tiles of the second round have their reductions shared
-    out over all SMs (per-worker partial tiles summed in worker order by a finishing kernel).
-    Parity with the oracle, agreement of the forward output with the whole-tile schedule, and
-    bit-repeatability.
+    90 pair tiles on 74 CTA pairs with AB200_TAIL_MODE=2: the 16 tiles of the second round have their
+    reductions shared out over all SMs (per-worker partial tiles summed in worker order by a
+    finishing kernel).  Parity with the oracle, agreement of the forward output with the whole-tile
+    schedule, and bit-repeatability.
     """
+    monkeypatch.setenv('AB200_TAIL_MODE', '2')
     x, w, b, dy = seeded((2560, 1024), 2304, torch.bfloat16, seed=17)
     got = check_layer(x, w, b, 'gelu', dy)
     whole = run_layer(x, w, b, 'gelu', dy, flags=_lib.FLAG_WHOLE_TILES)

@@ -1,6 +1,6 @@
 """
-GPU tests of the opt-in schedule (environment variable AB200_TAIL_MODE=3, read at every launch) that
-runs a partial last round of output tiles as half-width tiles (ab200_last_schedule() == 3), called
+GPU tests of the schedule that runs the last round of output tiles as half-width units
+(ab200_last_schedule() == 3; the default where it pays, see launch_cfg in csrc/gemm_launch.cuh), called
 through the C ABI for each of the three GEMMs of the layer:
 forward (A K-major, B MN-major), dX (both K-major), dW (both MN-major).  Results are compared with
 float64 products of the same (rounded) operands and, bit for bit, with the whole-tile schedule:
@@ -19,8 +19,8 @@ DEV = 'cuda'
 
 
 @pytest.fixture(autouse=True)
-def half_width_tail():
-    os.environ['AB200_TAIL_MODE'] = '3'
+def default_tail_mode():
+    os.environ.pop('AB200_TAIL_MODE', None)
     yield
     os.environ.pop('AB200_TAIL_MODE', None)
 
@@ -120,7 +120,32 @@ def test_benchmark_weight_gradient_shape():
     assert torch.equal(got, whole)
 
 
-def test_off_by_default():
-    os.environ.pop('AB200_TAIL_MODE', None)
+def test_whole_tiles_on_request():
+    os.environ['AB200_TAIL_MODE'] = '1'
     _, _, schedule = run('fwd', 2560, 512, 2816, torch.bfloat16, 0)
     assert schedule == 0
+
+
+@pytest.mark.parametrize('which', ['fwd', 'dx', 'dw'])
+def test_full_last_round_as_half_width_units(which):
+    """
+    148 tiles of 256 x 256 on 74 CTA pairs are two full rounds: whole tiles by default, half-width
+    units for the second round with AB200_TAIL_MODE=3.  Ragged variant: the second half of the last
+    column block lies beyond N and is skipped.
+    """
+    if sms() != 148:
+        pytest.skip('tile counts are chosen for 148 SMs')
+    shape = {'fwd': (9472, 320, 1024), 'dx': (9472, 1024, 320), 'dw': (320, 9472, 1024)}[which]
+    whole, expected, schedule = run(which, *shape, torch.bfloat16, 0)
+    assert schedule == 0
+    os.environ['AB200_TAIL_MODE'] = '3'
+    got, _, schedule = run(which, *shape, torch.bfloat16, 0)
+    assert schedule == 3
+    assert torch.equal(got, whole)
+    torch.testing.assert_close(got.double(), expected, rtol=2e-2, atol=2e-2)
+    if which == 'fwd':
+        got, expected, schedule = run('fwd', 9472, 328, 1024 - 136, torch.bfloat16, 0)
+        assert schedule == 3
+        whole, _, _ = run('fwd', 9472, 328, 1024 - 136, torch.bfloat16, _lib.FLAG_WHOLE_TILES)
+        assert torch.equal(got, whole)
+        torch.testing.assert_close(got.double(), expected, rtol=2e-2, atol=2e-2)
