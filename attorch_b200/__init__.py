@@ -21,9 +21,9 @@ from .act_layers import (CELU, ELU, GELU, SELU, ActFuncAutoGrad, Hardshrink, Har
                          Softshrink, Softsign, Tanh, Tanhshrink, set_dropout_stream)
 from .glu_layer import GLU, GLUAutoGrad
 from .linear_layer import (Linear, LinearAutoGrad, check_status, get_output_dtype, set_gemm_flags,
-                           set_save_derivative)
+                           set_reserved_sms, set_save_derivative)
 
 __all__ = ['convert', 'nn', 'GLU', 'GLUAutoGrad', 'Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags',
-           'set_save_derivative', 'set_dropout_stream', 'ActFuncAutoGrad', 'CELU', 'ELU', 'GELU', 'SELU', 'Hardshrink',
+           'set_save_derivative', 'set_reserved_sms', 'set_dropout_stream', 'ActFuncAutoGrad', 'CELU', 'ELU', 'GELU', 'SELU', 'Hardshrink',
            'Hardsigmoid', 'Hardswish', 'Hardtanh', 'LeakyReLU', 'LogSigmoid', 'Mish', 'ReLU', 'ReLU6',
            'Sigmoid', 'SiLU', 'Softplus', 'Softshrink', 'Softsign', 'Tanh', 'Tanhshrink']

@@ -183,6 +183,7 @@ const char* ab200_error_string(int code) {
     case DEV_TIMEOUT_PRODUCER: return "device: TMA producer gave up waiting for a free stage";
     case DEV_TIMEOUT_MMA: return "device: MMA issuer gave up waiting for operands or an accumulator";
     case DEV_TIMEOUT_EPILOGUE: return "device: epilogue gave up waiting for an accumulator";
+    case DEV_TIMEOUT_COLLECTIVE: return "device: all-reduce gave up waiting for another rank";
     default: return "unknown code";
   }
 }

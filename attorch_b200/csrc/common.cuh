@@ -35,6 +35,7 @@ enum DeviceStatus : int {
   DEV_TIMEOUT_PRODUCER = 1,
   DEV_TIMEOUT_MMA = 2,
   DEV_TIMEOUT_EPILOGUE = 3,
+  DEV_TIMEOUT_COLLECTIVE = 4,
 };
 
 template <class T>

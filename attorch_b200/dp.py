@@ -19,6 +19,13 @@ bytes, and the result is widened into the fp32 ``.grad`` on the side stream.  Th
 reference's own arithmetic (its backward computes ``dW`` in the autocast dtype,
 attorch/linear_layer.py:152-156, and the engine casts it to the parameter's dtype).
 
+Two transports carry the exchange.  ``'nccl'``: ``torch.distributed.all_reduce``.  ``'multimem'``:
+the library's own kernel (``ab200_multimem_all_reduce``), which lets the NVSwitch do the additions
+through an NVLink multicast mapping of the bucket (allocated with
+``torch.distributed._symmetric_memory``); it needs only a handful of SMs, so the GEMMs that run
+beside it keep almost all of them, and being an ordinary kernel it can be captured in a CUDA graph
+together with the rest of the step.
+
 A step that is replayed from CUDA graphs cannot issue NCCL calls from inside backward; for it the
 harness can hold back the first layer's ``dX`` (``defer_first_input_grad``): the step becomes "graph 1:
 forward and backward without that product", ``start_exchange()`` (one all-reduce of the whole bucket on
@@ -48,6 +55,47 @@ def shard_rows(tensor: Tensor, rank: int, world_size: int) -> Tensor:
     return tensor[rank * per_rank:(rank + 1) * per_rank]
 
 
+class _MultimemBucket:
+    """
+    A gradient bucket every rank maps through one NVLink multicast object, plus the flag block the
+    library's all-reduce kernel synchronises the ranks with.  PyTorch's symmetric-memory allocator
+    provides the mappings (plumbing); the collective itself is ``ab200_multimem_all_reduce``.
+    """
+    def __init__(self, numel: int, dtype: torch.dtype, device: torch.device, group, ctas: int) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        lib = _lib.load()
+        self.flat = symm_mem.empty(numel, dtype=dtype, device=device)
+        self.flat.zero_()
+        handle = symm_mem.rendezvous(self.flat, group)
+        if not handle.multicast_ptr:
+            raise RuntimeError('NVLink multicast is not available for this group of devices')
+        self.flags = symm_mem.empty(lib.ab200_collective_flag_bytes() // 4, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        flag_handle = symm_mem.rendezvous(self.flags, group)
+        self.multicast_ptr = int(handle.multicast_ptr)
+        self.flag_blocks = int(flag_handle.buffer_ptrs_dev)      # device array of the ranks' flag blocks
+        self.rank, self.world_size = int(handle.rank), int(handle.world_size)
+        self.dtype, self.device, self.ctas = dtype, device, ctas
+        self.element_size = self.flat.element_size()
+        self._handles = (handle, flag_handle)                    # keep the mappings alive
+        # Every rank's flags are zero before any rank's first kernel signals them.
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def can_reduce(self, begin: int, end: int) -> bool:
+        return (begin * self.element_size) % 16 == 0 and ((end - begin) * self.element_size) % 16 == 0
+
+    def all_reduce(self, begin: int, end: int) -> None:
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            status = _layer._stream_scratch(self.device)['status']
+        _lib.check(_lib.load().ab200_multimem_all_reduce(
+            self.multicast_ptr + begin * self.element_size, end - begin, _DTYPE_IDS[self.dtype], self.rank,
+            self.world_size, self.flag_blocks, self.ctas, status.data_ptr(), stream),
+            'ab200_multimem_all_reduce')
+
+
 class GradientBuckets:
     """
     One flat gradient buffer per model; every Linear gets views of it as its ``dW`` / ``db``
@@ -72,21 +120,42 @@ class GradientBuckets:
         grad_dtype: Element type the gradients are computed and exchanged in; None for the
             parameters' own.  If it differs, ``.grad`` (in the parameters' dtype) receives the
             widened sum after the exchange.
+        exchange: False builds the same buckets without any collective, as if the world size were 1
+            (to time or test a rank's local step while other ranks exist).
+        transport: ``'nccl'``, ``'multimem'`` (raises where NVLink multicast is not available) or
+            ``'auto'`` (multimem where available, else NCCL); see the module docstring.
+        comm_ctas: CTAs of the multimem kernel (it also sets ``comm_sms`` for that transport).
     """
     def __init__(self, layers: Iterable[Linear], process_group=None, overlap: bool = True,
                  comm_sms: int = 16, dw_chunks: int = 2, defer_first_input_grad: bool = False,
-                 grad_dtype: Optional[torch.dtype] = None) -> None:
+                 grad_dtype: Optional[torch.dtype] = None, exchange: bool = True, transport: str = 'nccl',
+                 comm_ctas: int = 8) -> None:
         self.layers: List[Linear] = list(layers)
         self.group = process_group
-        self.world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.world_size = dist.get_world_size(process_group) if (dist.is_initialized() and exchange) else 1
         first = self.layers[0].weight
         self.device = first.device
         self.dtype = first.dtype
         self.grad_dtype = grad_dtype if grad_dtype is not None else self.dtype
         total = sum(layer.weight.numel() + (layer.bias.numel() if layer.bias is not None else 0)
                     for layer in self.layers)
-        # What the kernels write and the collective reduces.
-        self.flat = torch.zeros(total, dtype=self.grad_dtype, device=self.device)
+        # What the kernels write and the collective reduces (padded to whole 16-byte units).
+        elt = torch.empty(0, dtype=self.grad_dtype).element_size()
+        total = -(-total * elt // 16) * 16 // elt
+        self.transport = 'nccl'
+        self._multimem = None
+        if transport not in ('nccl', 'multimem', 'auto'):
+            raise ValueError(f"transport must be 'nccl', 'multimem' or 'auto', not {transport!r}")
+        if transport != 'nccl' and self.world_size > 1 and self.device.type == 'cuda':
+            try:
+                self._multimem = _MultimemBucket(total, self.grad_dtype, self.device, process_group, comm_ctas)
+                self.transport = 'multimem'
+                comm_sms = comm_ctas
+            except Exception:
+                if transport == 'multimem':
+                    raise
+        self.flat = (self._multimem.flat if self._multimem is not None else
+                     torch.zeros(total, dtype=self.grad_dtype, device=self.device))
         # What .grad aliases: the same buffer, or a second one in the parameters' dtype.
         self.widen = self.grad_dtype is not self.dtype
         self.flat_grad = torch.zeros(total, dtype=self.dtype, device=self.device) if self.widen else self.flat
@@ -157,12 +226,19 @@ class GradientBuckets:
             _DTYPE_IDS[self.grad_dtype], _DTYPE_IDS[self.dtype],
             torch.cuda.current_stream(self.device).cuda_stream), 'ab200_cast_2d')
 
+    def _all_reduce(self, begin: int, end: int) -> None:
+        """SUM over ranks of flat[begin:end], in place, on the current stream."""
+        if self._multimem is not None and self._multimem.can_reduce(begin, end):
+            self._multimem.all_reduce(begin, end)
+        else:
+            dist.all_reduce(self.flat[begin:end], op=dist.ReduceOp.SUM, group=self.group)
+
     def _reduce_async(self, begin: int, end: int) -> None:
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ready)
-            dist.all_reduce(self.flat[begin:end], op=dist.ReduceOp.SUM, group=self.group)
+            self._all_reduce(begin, end)
             if self.widen:
                 self._widen(begin, end)
             done = torch.cuda.Event()
@@ -185,7 +261,7 @@ class GradientBuckets:
         ready.record(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ready)
-            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+            self._all_reduce(0, self.flat.numel())
             if self.widen:
                 self._widen(0, self.flat.numel())
             done = torch.cuda.Event()
@@ -196,11 +272,25 @@ class GradientBuckets:
         """SMs a GEMM should leave free while it runs beside the exchange (0: none)."""
         return self.comm_sms if (self.device.type == 'cuda' and self.world_size > 1) else 0
 
-    def run_deferred(self) -> None:
-        """Launches the products ``defer_first_input_grad`` held back, on the current stream."""
-        for launch in self._deferred:
-            launch()
-        self._deferred.clear()
+    def run_deferred(self, rows=None, keep: bool = False, reserve_sms: int = 0) -> None:
+        """
+        Launches the products ``defer_first_input_grad`` held back, on the current stream: all of
+        their rows, or rows ``[rows[0], rows[1])`` only (``keep=True`` leaves them registered for a
+        further call with the remaining rows).  ``reserve_sms`` SMs are left free for the exchange
+        that runs beside these launches.
+        """
+        previous = _layer.set_reserved_sms(self.device.index, reserve_sms) if self.device.type == 'cuda' else 0
+        try:
+            for launch in self._deferred:
+                if rows is None:
+                    launch()
+                else:
+                    launch(rows[0], rows[1])
+        finally:
+            if self.device.type == 'cuda':
+                _layer.set_reserved_sms(self.device.index, previous)
+        if not keep:
+            self._deferred.clear()
 
     def finish(self) -> None:
         """
@@ -216,7 +306,7 @@ class GradientBuckets:
                 _layer.set_reserved_sms(self.device.index, 0)
             return
         if self.world_size > 1:
-            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+            self._all_reduce(0, self.flat.numel())
         if self.widen:
             self._widen(0, self.flat.numel())
 

@@ -378,15 +378,24 @@ class LinearAutoGrad(torch.autograd.Function):
 
                 # Holds dZ and W alive but not dX: autograd must remain the only owner of the
                 # tensor it is handed, or it would copy it before the deferred product has run.
-                def launch_input_grad(dz=pre_act_grad, w=w_op):
+                # Rows [row_begin, row_end) of dX; a data-parallel step may launch the product in two
+                # pieces, the first beside its gradient exchange (on fewer SMs), the rest after it.
+                dx_row_bytes = in_feat_dim * input_grad.element_size()
+
+                def launch_input_grad(row_begin=0, row_end=None, dz=pre_act_grad, w=w_op):
+                    row_end = batch_dim if row_end is None else min(row_end, batch_dim)
+                    rows = row_end - row_begin
+                    if rows <= 0:
+                        return
                     with torch.cuda.device(device):
                         run_stream = torch.cuda.current_stream().cuda_stream
                         run_scratch = _stream_scratch(device)
-                        nbytes = _cached_size('ab200_gemm_workspace_bytes', batch_dim, in_feat_dim, out_feat_dim)
+                        nbytes = _cached_size('ab200_gemm_workspace_bytes', rows, in_feat_dim, out_feat_dim)
                         space = _workspace(device, nbytes) if nbytes else None
                         _lib.check(lib.ab200_linear_backward_input(
-                            _ptr(dz), _ptr(w), dx_ptr,
-                            batch_dim, in_feat_dim, out_feat_dim,
+                            dz.data_ptr() + row_begin * dz.stride(0) * dz.element_size(), _ptr(w),
+                            dx_ptr + row_begin * dx_row_bytes,
+                            rows, in_feat_dim, out_feat_dim,
                             dz.stride(0), dz.stride(1), w.stride(0), w.stride(1),
                             in_feat_dim, _dtype_id(op_dtype), dx_dtype,
                             _ptr(space), nbytes, _ptr(run_scratch['status']), run_stream, _flags_for(device)),

@@ -4,12 +4,12 @@ Benchmark of the fused linear layer (forward + backward) on B200.
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|act] [--impl reference]
 
 For N > 1 launch one rank per GPU with torchrun (RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the
-environment).  Rank 0 prints one JSON line.
+environment).  Rank 0 prints one JSON line, last.
 
-Workloads (synthetic, seeded; shapes of BASELINE.json's configs):
+Workloads (synthetic, seeded; shapes of the reference configurations this path is quoted on):
   c2  attorch.Linear 4096 -> 4096, bias, gelu, under bf16 autocast with fp32 parameters and fp32
       input; 8192 tokens per GPU (weak scaling: the global batch is 8192 * N); forward + backward
-      (dX, dW, db); with N > 1 the fp32 dW / db are SUM-all-reduced every step, overlapped with dX.
+      (dX, dW, db); with N > 1 dW / db are SUM-all-reduced every step, overlapped with dX.
   c5  two layers 8192 -> 8192 (gelu + bias, then bias), bf16 parameters, global batch 65536 tokens
       split over the N GPUs (strong scaling), same all-reduce.
   c3  transformer MLP pair 4096 -> 14336 (silu) -> 4096, no biases, bf16, 16384 tokens per GPU.
@@ -20,16 +20,23 @@ Workloads (synthetic, seeded; shapes of BASELINE.json's configs):
 One "step" is one forward + backward of the workload on one batch.  ``value`` is the whole-job
 TFLOP/s at 6 * M * K * N floating-point operations per layer and step with the inputs resident in
 HBM; ``e2e`` is the same through the same module with the step's input copied from pinned host
-memory and the bias gradient read back every step (copies double-buffered on a side stream).
-``--impl reference`` times the CPU computation the reference's tests compare against
-(torch.nn.Linear + activation, all host cores) on a bounded sample of the same workload.
+memory and the output and the bias gradient read back every step (copies on side streams).
+The default run (workload c2) adds sub-records to the same line: ``c5`` (its step at this N, and at
+N > 1 the same 65536 tokens on one GPU for the strong-scaling efficiency), ``dp_parity`` (all-reduced
+gradients against the full-batch gradients of the gathered shards), ``collectives`` (all-reduce times),
+and at N = 1 ``torch_gpu_baseline`` (torch.nn.Linear + gelu and bare matmuls on the same GPU), ``c3``
+and ``c4``.  ``--impl reference`` times the CPU computation the reference's tests compare against
+(torch.nn.Linear + activation, all host cores) on the same batch.
 """
 
 import argparse
 import json
 import os
+import re
+import socket
 import statistics
 import sys
+import tempfile
 import threading
 import time
 from pathlib import Path
@@ -40,10 +47,6 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 PEAK_FALLBACK = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0}
-
-# DRAM bytes per launch of the dominant kernel (forward GEMM of c2) from the ncu capture summarised
-# in profiles/c2_kernel_fwd.md (algorithmic bytes: 224 MiB = 234.9e6).
-NCU_DRAM_BYTES_PER_LAUNCH = 255.3e6   # profiles/c2_kernel_fwd.md: 150.6 MB read + 104.7 MB written
 
 WORKLOADS = {
     'c2': dict(layers=[(4096, 4096, 'gelu', True)], tokens_per_gpu=8192, global_tokens=None,
@@ -56,7 +59,9 @@ WORKLOADS = {
                global_tokens=None, param_dtype=torch.bfloat16, input_dtype=torch.bfloat16,
                autocast=None, scaling='weak'),
 }
-# Workload c4 (BASELINE.json config 4) is forward only and HBM-bound: see skinny_forward().
+# The skinny forward-only workload c4 is HBM-bound: see skinny_forward().
+
+DTYPE_NAMES = {torch.float32: 'fp32', torch.bfloat16: 'bf16', torch.float16: 'fp16'}
 
 
 def measured_peaks():
@@ -65,6 +70,31 @@ def measured_peaks():
         data = json.loads(path.read_text())
         return {k: float(data[k]) for k in PEAK_FALLBACK}, 'measured'
     return dict(PEAK_FALLBACK), 'fallback'
+
+
+def profiled_dram_bytes(summary: str = 'c2_kernel_fwd.md'):
+    """
+    DRAM bytes per launch (read + written, mean over the captured launches) of the forward GEMM of
+    workload c2, read from the committed summary of its ncu capture; None if the file or the lines
+    are missing.
+    """
+    path = ROOT / 'profiles' / summary
+    if not path.exists():
+        return None
+    total = 0.0
+    for key in ('dram__bytes_read.sum', 'dram__bytes_write.sum'):
+        match = re.search(re.escape(key) + r' \[(\w+)\]: ([^\n]+)', path.read_text())
+        if match is None:
+            return None
+        scale = {'Mbyte': 1e6, 'Gbyte': 1e9, 'Kbyte': 1e3, 'byte': 1.0}.get(match.group(1))
+        try:
+            values = [float(v) for v in match.group(2).split('|')]
+        except ValueError:
+            return None
+        if scale is None or not values:
+            return None
+        total += scale * sum(values) / len(values)
+    return total
 
 
 class ClockSampler:
@@ -125,30 +155,108 @@ class ClockSampler:
                 'reasons': sorted(self.reasons), 'samples': len(self.samples)}
 
 
+class CollectiveLog:
+    """
+    NCCL writes its INFO log to standard output, where rank 0's JSON line has to be the last line.
+    For the life of this object file descriptor 1 points to a temporary file instead; ``close()``
+    puts standard output back, copies the NCCL lines that say which algorithm ran to standard error
+    and returns them.
+    """
+    PATTERN = re.compile(r'AllReduce: (\d+) Bytes -> Algo (\w+) proto (\w+) channel\{Lo\.\.Hi\}=\{(\d+)\.\.(\d+)\}')
+
+    def __init__(self) -> None:
+        # INFO level with the INIT and TUNING subsystems: the latter logs the algorithm, protocol and
+        # channel count of every collective.  Whatever the launcher asked for on top of that is kept.
+        if os.environ.get('NCCL_DEBUG', '').upper() not in ('INFO', 'TRACE'):
+            os.environ['NCCL_DEBUG'] = 'INFO'
+        subsys = [s for s in os.environ.get('NCCL_DEBUG_SUBSYS', '').split(',') if s]
+        if not any(s.upper() == 'ALL' for s in subsys):
+            for wanted in ('INIT', 'TUNING'):
+                if not any(s.upper() == wanted for s in subsys):
+                    subsys.append(wanted)
+        os.environ['NCCL_DEBUG_SUBSYS'] = ','.join(subsys)
+        sys.stdout.flush()
+        self._saved = os.dup(1)
+        self._file = tempfile.TemporaryFile(mode='w+b')
+        os.dup2(self._file.fileno(), 1)
+
+    def _text(self) -> str:
+        sys.stdout.flush()
+        self._file.seek(0)
+        chunks = [self._file.read().decode(errors='replace')]
+        self._file.seek(0, os.SEEK_END)
+        # A launcher may have sent the log to a file of its own.
+        pattern = os.environ.get('NCCL_DEBUG_FILE')
+        if pattern:
+            path = pattern.replace('%h', socket.gethostname()).replace('%p', str(os.getpid()))
+            try:
+                chunks.append(Path(path).read_text(errors='replace'))
+            except OSError:
+                pass
+        return '\n'.join(chunks)
+
+    def all_reduce_choice(self, nbytes: int):
+        """(algorithm, protocol, channels) NCCL logged for the all-reduce closest in size to nbytes."""
+        best = None
+        for match in self.PATTERN.finditer(self._text()):
+            size = int(match.group(1))
+            if best is None or abs(size - nbytes) < abs(best[0] - nbytes):
+                best = (size, match.group(2), match.group(3), int(match.group(5)) - int(match.group(4)) + 1)
+        return None if best is None or best[0] < nbytes // 4 else best[1:]
+
+    def close(self, echo: bool) -> str:
+        text = self._text()
+        sys.stdout.flush()
+        os.dup2(self._saved, 1)
+        os.close(self._saved)
+        self._file.close()
+        keep = [line for line in text.splitlines()
+                if re.search(r'NVLS|nvls|-> Algo|coll channels|nranks|Connected all', line)]
+        seen, tail = set(), []
+        for line in keep:
+            key = re.sub(r'^\S+ ', '', line)
+            if key not in seen:
+                seen.add(key)
+                tail.append(line)
+        tail = tail[-24:]
+        if echo:
+            for line in tail:
+                print(line, file=sys.stderr)
+        return '\n'.join(tail)
+
+
 def flops_per_step(spec, tokens):
     return sum(6.0 * tokens * k * n for (k, n, _, _) in spec['layers'])
 
 
-def run_reference(args, spec, world_size, rank):
-    """CPU arm: torch.nn.Linear + activation on all host cores, bounded sample of the workload."""
-    if rank != 0:
-        return
+def cpu_arm(spec, tokens, steps, warmup):
+    """torch.nn.Linear + activation forward + backward in fp32 on all host cores, on `tokens` rows."""
     from oracle.cpu_baseline import time_torch_cpu_linear
-    sample_rows = 512
     seconds, threads = 0.0, 1
     for (k, n, act, bias) in spec['layers']:
-        r = time_torch_cpu_linear(sample_rows, k, n, act, bias, None, args.steps, args.warmup)
+        r = time_torch_cpu_linear(tokens, k, n, act, bias, None, steps, warmup)
         seconds += r['seconds_per_step']
         threads = r['threads']
-    tflops = flops_per_step(spec, sample_rows) / seconds / 1e12
-    sample = (f'{sample_rows} of the batch rows per step, torch.nn.Linear + activation fwd+bwd in fp32 '
+    return seconds, threads
+
+
+def run_reference(args, spec, world_size, rank):
+    """CPU arm: the whole batch of one GPU's step per CPU step (same configuration as the GPU arm)."""
+    if rank != 0:
+        return
+    tokens = args.tokens or spec['tokens_per_gpu'] or spec['global_tokens']
+    seconds, threads = cpu_arm(spec, tokens, args.steps, min(args.warmup, 3))
+    tflops = flops_per_step(spec, tokens) / seconds / 1e12
+    sample = (f'all {tokens} rows of one GPU\'s batch per step, torch.nn.Linear + activation fwd+bwd in fp32 '
               f'on {threads} host threads')
     line = {
         'impl': 'reference', 'metric': 'linear_fwd_bwd_tflops', 'value': tflops, 'unit': 'TFLOP/s',
         'n_gpus': world_size, 'steps': args.steps, 'warmup': args.warmup,
         'ms_per_step': seconds * 1e3, 'higher_is_better': True, 'scaling': spec['scaling'],
         'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-        'config': {'workload': args.workload, 'sample': sample},
+        'config': {'workload': args.workload,
+                   'layers': [f'{k}->{n} act={act} bias={bias}' for (k, n, act, bias) in spec['layers']],
+                   'tokens_per_gpu': tokens, 'sample': sample},
         'cpu_baseline': {'value': tflops, 'unit': 'TFLOP/s', 'cores': threads, 'kind': 'port',
                          'sample': sample},
         'e2e': {'value': tflops, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
@@ -176,7 +284,7 @@ def kernel_launcher(spec, tokens, device, lib, which='fwd'):
     ids = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
     xo = torch.randn(tokens, k0, device=device).to(op_dtype)
     wo = (torch.randn(k0, n0, device=device) / k0 ** 0.5).to(op_dtype)
-    bo = torch.randn(n0, device=device).to(op_dtype)
+    bo = torch.randn(n0, device=device).to(grad_dtype)
     yo = torch.empty(tokens, n0, device=device, dtype=op_dtype)
     zo = torch.randn(tokens, n0, device=device).to(op_dtype)
     dyo = (torch.randn(tokens, n0, device=device) * 0.01).to(op_dtype)
@@ -202,7 +310,7 @@ def kernel_launcher(spec, tokens, device, lib, which='fwd'):
     def fwd():
         _lib.check(lib.ab200_linear_forward(
             xo.data_ptr(), wo.data_ptr(), bo.data_ptr(), zo.data_ptr(), yo.data_ptr(), tokens, k0, n0,
-            k0, 1, n0, 1, n0, n0, dt_id, dt_id, dt_id, act_id(name), param or 0.0, gws.data_ptr(), gws_bytes,
+            k0, 1, n0, 1, n0, n0, dt_id, dt_id, ids[bo.dtype], act_id(name), param or 0.0, gws.data_ptr(), gws_bytes,
             status.data_ptr(), stream, fwd_flags), 'ab200_linear_forward')
         return keep
 
@@ -232,27 +340,32 @@ def kernel_launcher(spec, tokens, device, lib, which='fwd'):
     return {'fwd': fwd, 'dx': dx, 'dw': dw}[which], gemm_flops, 'flops'
 
 
+def event_time(fn, reps, warmup=3):
+    """Mean milliseconds of `fn()` over `reps` back-to-back calls, CUDA events on the current stream."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(reps):
+        fn()
+    t1.record()
+    torch.cuda.synchronize()
+    return t0.elapsed_time(t1) / reps
+
+
 def kernel_only(args, spec, tokens, device, lib):
     """A few launches of one kernel and nothing else: the target of ncu captures."""
     launch, work, unit = kernel_launcher(spec, tokens, device, lib, args.kernel_only)
-    for _ in range(max(args.warmup, 1)):
-        launch()
-    torch.cuda.synchronize()
-    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    r0.record()
-    for _ in range(args.steps):
-        launch()
-    r1.record()
-    torch.cuda.synchronize()
-    ms = r0.elapsed_time(r1) / args.steps
+    ms = event_time(launch, args.steps, max(args.warmup, 1))
     rate = {'tflops': work / (ms * 1e-3) / 1e12} if unit == 'flops' else {'gbs': work / (ms * 1e-3) / 1e9}
     print(json.dumps({'kernel_only': args.kernel_only, 'tokens': tokens, 'kernel_ms': ms, **rate}), flush=True)
 
 
-def skinny_forward(args, device, lib):
+def skinny_forward(steps, warmup, device, lib):
     """
-    BASELINE.json config 4: y = x @ W for fp16 x [M, 8192], W [8192, 28672], no bias, no activation, under
-    torch.no_grad(), through the module.  HBM-bound: the score is algorithmic bytes
+    Skinny forward-only workload c4: y = x @ W for fp16 x [M, 8192], W [8192, 28672], no bias, no
+    activation, under torch.no_grad(), through the module.  HBM-bound: the score is algorithmic bytes
     2 * (K * N + M * K + M * N) over the CUDA-event time, in GB/s.  W (448 MiB) exceeds the L2, so
     back-to-back launches are cold.
     """
@@ -267,16 +380,7 @@ def skinny_forward(args, device, lib):
     for m in (1, 8, 32, 128):
         x = torch.randn(m, K, device=device, dtype=torch.float16)
         with torch.no_grad():
-            for _ in range(max(args.warmup, 3)):
-                layer(x)
-            torch.cuda.synchronize()
-            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t0.record()
-            for _ in range(args.steps):
-                layer(x)
-            t1.record()
-            torch.cuda.synchronize()
-        ms = t0.elapsed_time(t1) / args.steps
+            ms = event_time(lambda: layer(x), steps, max(warmup, 3))
         nbytes = 2.0 * (K * N + m * K + m * N)
         path = {_lib.PATH_STREAMK: 'memset + swap-AB stream-K tcgen05 + finish',
                 _lib.PATH_TCGEN05: 'one wave of whole 128 x 256 tcgen05 tiles'}.get(lib.ab200_last_path(), 'other')
@@ -285,22 +389,20 @@ def skinny_forward(args, device, lib):
                      'frac_of_nominal_8000': nbytes / (ms * 1e-3) / 1e9 / 8000.0})
     attorch_b200.check_status()
     best = max(r['gbs'] for r in rows)
-    print(json.dumps({'metric': 'skinny_forward_weight_read_gbs', 'value': best, 'unit': 'GB/s', 'n_gpus': 1,
-                      'steps': args.steps, 'warmup': args.warmup, 'higher_is_better': True, 'dtype': 'f16',
-                      'data': 'synthetic', 'config': {'workload': 'c4', 'K': K, 'N': N, 'rows': rows,
-                                                      'call': 'attorch_b200.Linear under torch.no_grad()'},
-                      'roofline': {'bound': 'hbm', 'achieved': best, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
-                                   'frac': best / peaks['hbm_gbs'], 'traffic': None,
-                                   'peak_source': peak_source}}), flush=True)
+    return {'metric': 'skinny_forward_weight_read_gbs', 'value': best, 'unit': 'GB/s', 'n_gpus': 1,
+            'steps': steps, 'warmup': warmup, 'higher_is_better': True, 'dtype': 'f16',
+            'data': 'synthetic', 'config': {'workload': 'c4', 'K': K, 'N': N, 'rows': rows,
+                                            'call': 'attorch_b200.Linear under torch.no_grad()'},
+            'roofline': {'bound': 'hbm', 'achieved': best, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
+                         'frac': best / peaks['hbm_gbs'], 'traffic': None, 'peak_source': peak_source}}
 
 
 def activation_layer(args, device):
     """
-    The standalone activation layer with fused dropout (the row after the linear layer in the scope
-    table): GELU with drop_p = 0.1 on a bf16 [32768, 4096] tensor (268 MB, larger than L2), forward and
-    input gradient, timed through the C ABI (the kernels alone) and through attorch_b200.GELU (with
-    the host work of the module around them).  HBM-bound: algorithmic bytes are 2 n e forward (read x,
-    write y) and 3 n e backward (read dy and x, write dx).
+    The standalone activation layer with fused dropout: GELU with drop_p = 0.1 on a bf16 [32768, 4096]
+    tensor (268 MB, larger than L2), forward and input gradient, timed through the C ABI (the kernels
+    alone) and through attorch_b200.GELU (with the host work of the module around them).  HBM-bound:
+    algorithmic bytes are 2 n e forward (read x, write y) and 3 n e backward (read dy and x, write dx).
     """
     import attorch_b200
     from attorch_b200 import _lib
@@ -346,16 +448,7 @@ def activation_layer(args, device):
                              ('module_forward_backward', module_step, 5 * n * 2.0)):
         if args.only and name != args.only:
             continue
-        for _ in range(max(args.warmup, 3)):
-            fn()
-        torch.cuda.synchronize()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for _ in range(args.steps):
-            fn()
-        t1.record()
-        torch.cuda.synchronize()
-        ms = t0.elapsed_time(t1) / args.steps
+        ms = event_time(fn, args.steps, max(args.warmup, 3))
         results[name] = {'us': round(ms * 1e3, 2), 'gbs': round(nbytes / (ms * 1e-3) / 1e9, 1)}
     # Gated linear unit of the MLP pair of workload c3: silu gate over the last dimension of
     # [16384, 2 * 14336] bf16 (3 n e bytes forward, 5 n e backward for n output elements).
@@ -380,16 +473,7 @@ def activation_layer(args, device):
                              ('glu_backward', glu_backward, 5 * rows * half * 2.0)):
         if args.only and name != args.only:
             continue
-        for _ in range(max(args.warmup, 3)):
-            fn()
-        torch.cuda.synchronize()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for _ in range(args.steps):
-            fn()
-        t1.record()
-        torch.cuda.synchronize()
-        ms = t0.elapsed_time(t1) / args.steps
+        ms = event_time(fn, args.steps, max(args.warmup, 3))
         results[name] = {'us': round(ms * 1e3, 2), 'gbs': round(nbytes / (ms * 1e-3) / 1e9, 1)}
     best = results[args.only or 'kernel_forward']['gbs']
     print(json.dumps({'metric': 'activation_layer_gbs', 'value': best, 'unit': 'GB/s', 'n_gpus': 1,
@@ -402,6 +486,420 @@ def activation_layer(args, device):
           flush=True)
 
 
+class Comm:
+    """Rank, world size and the two collectives the timing protocol needs."""
+    def __init__(self, device, world_size, rank):
+        self.device, self.world_size, self.rank = device, world_size, rank
+
+    def barrier(self):
+        if self.world_size > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, value):
+        if self.world_size == 1:
+            return value
+        import torch.distributed as dist
+        t = torch.tensor([value], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+
+class StepRunner:
+    """
+    One workload on one rank: the layers, their gradient buckets, a resident batch, and a step
+    function under one of these schedules.
+      graph          N = 1: the whole step is one captured CUDA graph (eager with --no-graph).
+      graph_split    N > 1, one layer: graph 1 = casts, forward, activation backward, dW; then the
+                     all-reduce of the bucket starts on a side stream; graph 2 = dX on the SMs NCCL's
+                     kernel leaves free (as many as NCCL_MAX_CTAS allows it).  NCCL itself is not
+                     captured.  (Launching only the first rows of dX beside the exchange and the rest on
+                     all SMs afterwards measured slower at 2 GPUs: 0.76-0.79 ms against 0.744 ms.)
+      eager_overlap  N > 1, any model: eager launches, each layer's all-reduce issued from inside
+                     backward per block of dW, overlapping the rest of backward.
+      graph_serial   N > 1: one graph of the local step, then one all-reduce (no overlap).
+      graph_overlap  N > 1 with the library's own all-reduce kernel (NVLink multicast): like
+                     eager_overlap, but the kernel is capturable, so the whole step - exchange on its
+                     side stream included - is one CUDA graph again.  The default where multicast works.
+    `local_only` builds the same step without any exchange although other ranks exist.
+    """
+    def __init__(self, name, spec, comm, lib, tokens=None, schedule=None, no_graph=False, local_only=False):
+        import attorch_b200
+        from attorch_b200.dp import GradientBuckets
+        self.ab = attorch_b200
+        self.name, self.spec, self.comm, self.lib = name, spec, comm, lib
+        device, world_size, rank = comm.device, comm.world_size, comm.rank
+        self.device = device
+        self.distributed = world_size > 1 and not local_only
+        self.tokens = tokens or spec['tokens_per_gpu'] or spec['global_tokens'] // (world_size if self.distributed else 1)
+        torch.manual_seed(0)
+        self.layers = [attorch_b200.Linear(k, n, bias=bias, act_func=act, device=device, dtype=spec['param_dtype'])
+                       for (k, n, act, bias) in spec['layers']]
+        grad_dtype = {'bf16': torch.bfloat16, 'fp16': torch.float16, 'fp32': torch.float32, '': None}[
+            os.environ.get('AB200_GRAD_DTYPE', '')]
+        if grad_dtype is None and self.distributed and spec['autocast'] is not None:
+            grad_dtype = spec['autocast']      # exchange in the autocast dtype, widen into the fp32 .grad
+        if not self.distributed:
+            schedule = 'eager' if no_graph else 'graph'
+        elif schedule is None:
+            schedule = os.environ.get('AB200_SCHEDULE')
+        transport = os.environ.get('AB200_TRANSPORT', 'auto') if self.distributed else 'nccl'
+        self.buckets = None
+        if self.distributed and transport != 'nccl' and schedule in (None, 'graph_overlap'):
+            # The library's own all-reduce: 8 CTAs, the whole bucket of a layer in one call.
+            ctas = int(os.environ.get('AB200_COMM_CTAS', '8'))
+            buckets = GradientBuckets(self.layers, overlap=True, dw_chunks=int(os.environ.get('AB200_DW_CHUNKS', '1')),
+                                      grad_dtype=grad_dtype, transport=transport, comm_ctas=ctas)
+            if buckets.transport == 'multimem':
+                self.buckets, schedule, self.comm_sms = buckets, 'graph_overlap', ctas
+        if self.buckets is None:
+            if self.distributed and schedule in (None, 'graph_overlap'):
+                schedule = 'graph_split' if len(self.layers) == 1 else 'eager_overlap'
+            self.comm_sms = int(os.environ.get('AB200_COMM_SMS', '32')) if self.distributed else 0
+            self.buckets = GradientBuckets(
+                self.layers, overlap=(schedule == 'eager_overlap'), comm_sms=self.comm_sms,
+                dw_chunks=int(os.environ.get('AB200_DW_CHUNKS', '2')),
+                defer_first_input_grad=(schedule == 'graph_split'),
+                grad_dtype=grad_dtype if self.distributed else None, exchange=self.distributed)
+        self.schedule = schedule
+        self.k_in, self.n_out = spec['layers'][0][0], spec['layers'][-1][1]
+        gen = torch.Generator(device=device).manual_seed(1 + rank)
+        self.x = torch.randn(self.tokens, self.k_in, device=device, generator=gen).to(spec['input_dtype'])
+        self.x.requires_grad_(True)
+        out_dtype = spec['autocast'] or spec['param_dtype']
+        self.dy = (torch.randn(self.tokens, self.n_out, device=device, generator=gen) * 0.01).to(out_dtype)
+        self.graphs = None
+        self.output = None
+
+    # -- pieces of a step
+    def compute(self, x):
+        self.buckets.zero_grad()
+        x.grad = None
+        spec = self.spec
+        with torch.autocast('cuda', dtype=spec['autocast'] or torch.bfloat16, enabled=spec['autocast'] is not None):
+            h = x
+            for layer in self.layers:
+                h = layer(h)
+        self.output = h.detach()      # not h itself: that would keep this step's autograd graph alive
+        h.backward(self.dy)
+
+    def step(self, x):
+        """One eager step (every schedule can run eagerly: warm-up, launch counting, end-to-end loop)."""
+        self.compute(x)
+        if self.schedule == 'graph_split':
+            self.buckets.start_exchange()
+            self.buckets.run_deferred(reserve_sms=self.comm_sms)
+        self.buckets.finish()
+
+    def time_exchange(self):
+        """The exchange alone and the deferred dX alone (ms, max over ranks): how much there is to hide, and where."""
+        if self.schedule != 'graph_split':
+            return None
+        for _ in range(2):
+            self.step(self.x)
+        torch.cuda.synchronize()
+
+        def exchange():
+            self.buckets.start_exchange()
+            self.buckets.finish()
+
+        self.compute(self.x)          # leaves the dX launcher registered
+
+        def product():
+            self.buckets.run_deferred(keep=True)
+
+        self.comm.barrier()
+        exchange_ms = self.comm.max_over_ranks(event_time(exchange, 5, 2))
+        product_ms = self.comm.max_over_ranks(event_time(product, 5, 2))
+        self.buckets.run_deferred()
+        return {'exchange_alone_ms': exchange_ms, 'deferred_dx_alone_ms': product_ms}
+
+    def capture(self):
+        """Captures the local pieces of a step as CUDA graphs; returns False if capture is not used."""
+        if self.schedule in ('eager', 'eager_overlap'):
+            return False
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self.step(self.x)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graphs = [torch.cuda.CUDAGraph()]
+        with torch.cuda.graph(graphs[0]):
+            if self.schedule == 'graph_overlap':
+                self.step(self.x)       # the exchange (on its side stream) is part of the graph
+            else:
+                self.compute(self.x)
+        if self.schedule == 'graph_split':
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=graphs[0].pool()):
+                self.buckets.run_deferred(reserve_sms=self.comm_sms)
+            graphs.append(graph)
+        self.graphs = graphs
+        self.run()
+        torch.cuda.synchronize()
+        self.ab.check_status()
+        return True
+
+    def run(self):
+        if self.graphs is None:
+            self.step(self.x)
+            return
+        self.graphs[0].replay()
+        if self.schedule == 'graph_overlap':
+            return
+        if self.schedule == 'graph_split':
+            self.buckets.start_exchange()
+            for graph in self.graphs[1:]:
+                graph.replay()
+        self.buckets.finish()
+
+    def timed(self, steps, sample_clocks_on=-1):
+        """Times `steps` runs: (ms per step as the max over ranks, host ms per step, clock summary)."""
+        for _ in range(3):
+            self.run()
+        self.comm.barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(sample_clocks_on) as clocks:
+            self.comm.barrier()
+            start.record()
+            host_t0 = time.perf_counter()
+            for _ in range(steps):
+                self.run()
+            host_ms = (time.perf_counter() - host_t0) * 1e3 / steps
+            stop.record()
+            self.comm.barrier()
+        ms = self.comm.max_over_ranks(start.elapsed_time(stop)) / steps
+        self.ab.check_status()
+        return ms, host_ms, clocks.summary()
+
+    def launches_per_step(self):
+        before = self.lib.ab200_launch_count()
+        self.step(self.x)
+        torch.cuda.synchronize()
+        return self.lib.ab200_launch_count() - before
+
+    def collective_bytes(self):
+        return self.buckets.flat.numel() * self.buckets.flat.element_size()
+
+
+def torch_gpu_baseline(spec, tokens, device, steps, warmup):
+    """
+    The same step in PyTorch on the same GPU: torch.nn.Linear + F.gelu under bf16 autocast with fp32
+    parameters and input, forward + backward (cuBLAS GEMMs, PyTorch's cast / activation / reduction
+    kernels), and the three bare matmuls of the step alone.  Same CUDA-event protocol.
+    """
+    import torch.nn.functional as F
+    k, n, act, bias = spec['layers'][0]
+    layer = torch.nn.Linear(k, n, bias=bias, device=device, dtype=spec['param_dtype'])
+    x = torch.randn(tokens, k, device=device, dtype=spec['input_dtype'], requires_grad=True)
+    dy = (torch.randn(tokens, n, device=device) * 0.01).to(spec['autocast'] or spec['param_dtype'])
+    act_fn = {None: (lambda t: t), 'gelu': F.gelu, 'silu': F.silu, 'relu': F.relu}[act]
+
+    def step():
+        x.grad = None
+        layer.zero_grad(set_to_none=True)
+        with torch.autocast('cuda', dtype=spec['autocast'] or torch.bfloat16, enabled=spec['autocast'] is not None):
+            y = act_fn(layer(x))
+        y.backward(dy)
+
+    eager_ms = event_time(step, steps, warmup)
+    graph_ms = None
+    try:
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        graph_ms = event_time(graph.replay, steps, warmup)
+    except Exception as error:
+        print(f'torch baseline: graph capture failed ({error})', file=sys.stderr)
+        torch.cuda.synchronize()
+    op = spec['autocast'] or spec['param_dtype']
+    xb = torch.randn(tokens, k, device=device).to(op)
+    wb = torch.randn(n, k, device=device).to(op)       # torch.nn.Linear layout [out, in]
+    dz = torch.randn(tokens, n, device=device).to(op)
+    yb = torch.empty(tokens, n, device=device, dtype=op)
+    dxb = torch.empty(tokens, k, device=device, dtype=op)
+    dwb = torch.empty(n, k, device=device, dtype=op)
+    matmuls = {'forward': event_time(lambda: torch.matmul(xb, wb.t(), out=yb), steps, warmup),
+               'dX': event_time(lambda: torch.matmul(dz, wb, out=dxb), steps, warmup),
+               'dW': event_time(lambda: torch.matmul(dz.t(), xb, out=dwb), steps, warmup)}
+    flops = flops_per_step(spec, tokens)
+    best = min(v for v in (eager_ms, graph_ms) if v is not None)
+    return {'what': 'torch.nn.Linear + F.gelu forward + backward under bf16 autocast, fp32 parameters and '
+                    'input, same GPU, same protocol',
+            'ms_per_step_eager': eager_ms, 'ms_per_step_graph': graph_ms, 'tflops': flops / (best * 1e-3) / 1e12,
+            'bare_matmul_ms': matmuls, 'bare_matmul_sum_ms': sum(matmuls.values()),
+            'bare_matmul_tflops': flops / (sum(matmuls.values()) * 1e-3) / 1e12}
+
+
+def dp_parity(comm):
+    """
+    Data-parallel gradients against full-batch gradients, on the GPUs, outside any timed region: every
+    rank runs one step on its shard of a small batch (bf16 autocast, fp32 parameters, upstream gradient
+    N(0, 1) * 0.01 as in workload c2; fp32 and bf16 exchange); the shards are all-gathered and every rank computes the full-batch dW / db with the same
+    kernels; the all-reduced ``.grad`` must equal them within rtol = atol = 1e-2.
+    """
+    import torch.distributed as dist
+
+    import attorch_b200
+    from attorch_b200.dp import GradientBuckets
+    device, world_size, rank = comm.device, comm.world_size, comm.rank
+    rows, k, n = 512, 1024, 768
+    report = {'shape': [rows * world_size, k, n], 'rtol_atol': 1e-2}
+    cases = [(None, 'nccl', 'fp32_exchange'), (torch.bfloat16, 'nccl', 'bf16_exchange')]
+    if os.environ.get('AB200_TRANSPORT', 'auto') != 'nccl':
+        cases.append((torch.bfloat16, 'auto', 'bf16_exchange_own_kernel'))
+    for exchange_dtype, transport, tag in cases:
+        torch.manual_seed(3)
+        layer = attorch_b200.Linear(k, n, bias=True, act_func='gelu', device=device, dtype=torch.float32)
+        full = attorch_b200.Linear(k, n, bias=True, act_func='gelu', device=device, dtype=torch.float32)
+        full.load_state_dict(layer.state_dict())
+        buckets = GradientBuckets([layer], overlap=True, comm_sms=32, dw_chunks=2, grad_dtype=exchange_dtype,
+                                  transport=transport)
+        gen = torch.Generator(device=device).manual_seed(100 + rank)
+        x = torch.randn(rows, k, device=device, generator=gen)
+        dy = (torch.randn(rows, n, device=device, generator=gen) * 0.01).bfloat16()
+        xg = x.clone().requires_grad_(True)
+        with torch.autocast('cuda', dtype=torch.bfloat16):
+            y = layer(xg)
+        y.backward(dy)
+        buckets.finish()
+        xs = [torch.empty_like(x) for _ in range(world_size)]
+        dys = [torch.empty_like(dy) for _ in range(world_size)]
+        dist.all_gather(xs, x)
+        dist.all_gather(dys, dy)
+        xf = torch.cat(xs).requires_grad_(True)
+        with torch.autocast('cuda', dtype=torch.bfloat16):
+            yf = full(xf)
+        yf.backward(torch.cat(dys))
+        torch.cuda.synchronize()
+        attorch_b200.check_status()
+        ok, worst = True, 0.0
+        for got, want in ((layer.weight.grad, full.weight.grad), (layer.bias.grad, full.bias.grad)):
+            err = (got.float() - want.float()).abs()
+            bound = 1e-2 + 1e-2 * want.float().abs()
+            worst = max(worst, float((err / bound).max().item()))
+            ok = ok and bool((err <= bound).all().item())
+        # The shard's own dX must equal the rows of the full-batch dX it owns.
+        own = xf.grad[rank * rows:(rank + 1) * rows]
+        ok = ok and bool(torch.allclose(xg.grad, own, rtol=1e-2, atol=1e-2))
+        flag = torch.tensor([1 if ok else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        report[tag] = {'ok': bool(flag.item() == 1), 'worst_error_over_bound_rank0': worst,
+                       'transport': buckets.transport}
+        del buckets, layer, full
+    report['ok'] = all(report[t]['ok'] for (_, _, t) in cases)
+    return report
+
+
+def all_reduce_times(comm):
+    """
+    All-reduce of 32 / 64 / 256 MiB on otherwise idle GPUs, NCCL and (where NVLink multicast works) the
+    library's own kernel on 8 CTAs: ms and bus bandwidth (max over ranks).
+    """
+    import torch.distributed as dist
+
+    from attorch_b200.dp import _MultimemBucket
+    out = []
+    n = comm.world_size
+    for mib, dtype in ((32, torch.bfloat16), (64, torch.float32), (256, torch.bfloat16)):
+        elt = torch.empty(0, dtype=dtype).element_size()
+        numel = mib * 1024 * 1024 // elt
+        nbytes = numel * elt
+        buf = torch.zeros(numel, dtype=dtype, device=comm.device)
+        comm.barrier()
+        ms = comm.max_over_ranks(event_time(lambda: dist.all_reduce(buf), 10, 3))
+        row = {'mib': mib, 'dtype': DTYPE_NAMES[dtype], 'nccl_ms': ms,
+               'nccl_busbw_gbs': nbytes * 2.0 * (n - 1) / n / (ms * 1e-3) / 1e9}
+        del buf
+        if os.environ.get('AB200_TRANSPORT', 'auto') != 'nccl':
+            try:
+                bucket = _MultimemBucket(numel, dtype, comm.device, None, int(os.environ.get('AB200_COMM_CTAS', '8')))
+                comm.barrier()
+                ms = comm.max_over_ranks(event_time(lambda: bucket.all_reduce(0, numel), 10, 3))
+                row.update({'own_kernel_ms': ms, 'own_kernel_ctas': bucket.ctas,
+                            'own_kernel_busbw_gbs': nbytes * 2.0 * (n - 1) / n / (ms * 1e-3) / 1e9})
+                del bucket
+            except Exception as error:
+                row['own_kernel'] = f'unavailable: {error}'
+        out.append(row)
+    return out
+
+
+def end_to_end(runner, comm, steps):
+    """
+    The same step fed from host memory: every step copies its input from pinned host memory (next
+    step's copy overlapping this step's compute on a side stream) and reads the step's output and the
+    last layer's bias gradient back into pinned host memory (on another side stream, overlapping the
+    next step).  Returns (ms per step, host-to-device bytes, device-to-host bytes per step).
+    """
+    spec, device = runner.spec, runner.device
+    host_x = [torch.randn(runner.tokens, runner.k_in).to(spec['input_dtype']).pin_memory() for _ in range(2)]
+    dev_x = [torch.empty_like(runner.x).requires_grad_(True) for _ in range(2)]
+    out_dtype = spec['autocast'] or spec['param_dtype']
+    host_y = torch.empty(runner.tokens, runner.n_out, dtype=out_dtype).pin_memory()
+    last = runner.layers[-1]
+    small = last.bias if last.bias is not None else last.weight[0]
+    host_small = torch.empty(small.shape, dtype=small.dtype).pin_memory()
+    copy_stream = torch.cuda.Stream(device)
+    back_stream = torch.cuda.Stream(device)
+    copied = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    produced = torch.cuda.Event()
+    read_back = torch.cuda.Event()
+
+    def loop(n_steps):
+        compute = torch.cuda.current_stream()
+        with torch.cuda.stream(copy_stream):
+            dev_x[0].data.copy_(host_x[0], non_blocking=True)
+            copied[0].record(copy_stream)
+        for i in range(n_steps):
+            cur, nxt = i % 2, (i + 1) % 2
+            if i + 1 < n_steps:
+                with torch.cuda.stream(copy_stream):
+                    if i >= 1:
+                        copy_stream.wait_event(consumed[nxt])
+                    dev_x[nxt].data.copy_(host_x[nxt], non_blocking=True)
+                    copied[nxt].record(copy_stream)
+            compute.wait_event(copied[cur])
+            runner.step(dev_x[cur])
+            consumed[cur].record(compute)
+            produced.record(compute)
+            output = runner.output.view(runner.tokens, runner.n_out)
+            grad = last.bias.grad if last.bias is not None else last.weight.grad[0]
+            with torch.cuda.stream(back_stream):
+                back_stream.wait_event(produced)
+                host_y.copy_(output, non_blocking=True)
+                host_small.copy_(grad, non_blocking=True)
+                read_back.record(back_stream)
+            # Keeps the output's memory from being handed to the next step before it has been read.
+            output.record_stream(back_stream)
+            grad.record_stream(back_stream)
+        compute.wait_event(read_back)
+        compute.synchronize()
+
+    loop(3)
+    comm.barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    loop(steps)
+    t1.record()
+    comm.barrier()
+    ms = comm.max_over_ranks(t0.elapsed_time(t1)) / steps
+    h2d = host_x[0].numel() * host_x[0].element_size()
+    d2h = host_y.numel() * host_y.element_size() + host_small.numel() * host_small.element_size()
+    return ms, h2d, d2h
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     parser.add_argument('--gpus', type=int, default=1)
@@ -412,8 +910,10 @@ def main():
                         help='workload act: time just this entry (e.g. kernel_forward, glu_backward)')
     parser.add_argument('--impl', choices=['b200', 'reference'], default='b200')
     parser.add_argument('--no-cpu-baseline', action='store_true')
+    parser.add_argument('--no-extras', action='store_true',
+                        help='only the timed workload: no sub-records for the other workloads and baselines')
     parser.add_argument('--no-graph', action='store_true',
-                        help='launch every step eagerly instead of replaying one captured CUDA graph')
+                        help='launch every step eagerly instead of replaying captured CUDA graphs')
     parser.add_argument('--kernel-only', choices=['fwd', 'dx', 'dw', 'act_bwd'], default=None,
                         help='launch only this kernel of the first layer (for ncu captures)')
     parser.add_argument('--tokens', type=int, default=None,
@@ -427,7 +927,7 @@ def main():
         from attorch_b200 import _lib
         torch.cuda.set_device(0)
         if args.workload == 'c4':
-            skinny_forward(args, torch.device('cuda', 0), _lib.load())
+            print(json.dumps(skinny_forward(args.steps, args.warmup, torch.device('cuda', 0), _lib.load())), flush=True)
         else:
             activation_layer(args, torch.device('cuda', 0))
         return
@@ -444,239 +944,196 @@ def main():
 
     import attorch_b200
     from attorch_b200 import _lib
-    from attorch_b200.dp import GradientBuckets
 
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device: the layer has no CPU fallback')
     lib = _lib.load()
     torch.cuda.set_device(local_rank)
     device = torch.device('cuda', local_rank)
+    log = None
     if world_size > 1:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        # The GEMM that runs beside the exchange leaves exactly the SMs NCCL's kernel occupies.
+        os.environ.setdefault('NCCL_MAX_CTAS', os.environ.get('AB200_COMM_SMS', '32'))
+        log = CollectiveLog()
         dist.init_process_group('nccl', device_id=device)
-
-    tokens = args.tokens or spec['tokens_per_gpu'] or spec['global_tokens'] // world_size
-    total_tokens = tokens * world_size
-    torch.manual_seed(0)
-    layers = [attorch_b200.Linear(k, n, bias=bias, act_func=act, device=device,
-                                  dtype=spec['param_dtype'])
-              for (k, n, act, bias) in spec['layers']]
-    # One GPU: a step is one captured CUDA graph.  Several GPUs: NCCL cannot be captured here (see
-    # below), so either the step is launched eagerly with the gradient exchange issued per block of dW
-    # from inside backward, overlapping the rest of it (--no-graph; the default where a rank has at
-    # least 4 host threads to itself), or the local computation is replayed from a graph and followed by
-    # one all-reduce of the bucket.  Measured at 2 GPUs: eager overlapped 0.839-0.894 ms, graph + one
-    # all-reduce 0.886-0.887 ms, eager without overlap 0.877 ms; at 8 GPUs eager overlapped 0.959 ms
-    # (1.001 ms on a box with 2 host threads per rank, where enqueueing takes 0.91 ms per step).
-    # AB200_DEFER_DX=1 selects a third schedule: two graphs per step with the all-reduce started between
-    # them, so that it overlaps the first layer's dX (which runs on 16 fewer SMs).  It measured slower
-    # at 2 GPUs (0.914-0.924 ms): the exchange and the GEMM slow each other down more than the overlap
-    # saves.
-    if world_size > 1 and (os.cpu_count() or 1) // world_size >= 4 and not os.environ.get('AB200_FORCE_GRAPH') \
-            and os.environ.get('AB200_DEFER_DX', '0') != '1':
-        args.no_graph = True
-    defer = world_size > 1 and not args.no_graph and os.environ.get('AB200_DEFER_DX', '0') == '1'
-    overlap = args.no_graph and os.environ.get('AB200_DP_OVERLAP', '1') != '0'
-    buckets = GradientBuckets(layers, comm_sms=int(os.environ.get('AB200_COMM_SMS', '16')),
-                              overlap=overlap, defer_first_input_grad=defer,
-                              dw_chunks=int(os.environ.get('AB200_DW_CHUNKS', '2')))
-    k_in, n_out = spec['layers'][0][0], spec['layers'][-1][1]
-    gen = torch.Generator(device=device).manual_seed(1 + rank)
-    x_dev = torch.randn(tokens, k_in, device=device, generator=gen).to(spec['input_dtype'])
-    x_dev.requires_grad_(True)
-    out_dtype = spec['autocast'] or spec['param_dtype']
-    dy = (torch.randn(tokens, n_out, device=device, generator=gen) * 0.01).to(out_dtype)
-
-    def compute(x):
-        buckets.zero_grad()
-        x.grad = None
-        with torch.autocast('cuda', dtype=spec['autocast'] or torch.bfloat16,
-                            enabled=spec['autocast'] is not None):
-            h = x
-            for layer in layers:
-                h = layer(h)
-        h.backward(dy)
-
-    def deferred_products():
-        # The GEMMs held back run beside the exchange: leave NCCL some SMs.
-        lib.ab200_set_gemm_cta_limit(buckets.exchange_cta_limit())
-        try:
-            buckets.run_deferred()
-        finally:
-            lib.ab200_set_gemm_cta_limit(0)
-
-    def step(x):
-        compute(x)
-        if defer:
-            buckets.start_exchange()
-            deferred_products()
-        buckets.finish()
-
-    def barrier():
-        if world_size > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(ms):
-        if world_size == 1:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    comm = Comm(device, world_size, rank)
 
     if args.kernel_only:
+        tokens = args.tokens or spec['tokens_per_gpu'] or spec['global_tokens'] // world_size
         kernel_only(args, spec, tokens, device, lib)
         return
 
     # ---------------------------------------------------------------- device-resident timing
+    runner = StepRunner(args.workload, spec, comm, lib, tokens=args.tokens, no_graph=args.no_graph)
+    tokens, total_tokens = runner.tokens, runner.tokens * world_size
     for _ in range(args.warmup):
-        step(x_dev)
-    barrier()
+        runner.step(runner.x)
+    comm.barrier()
     attorch_b200.check_status()
-
-    # One step (forward, backward, gradient exchange) captured once as a CUDA graph and replayed:
-    # the same kernels on the same buffers, without the host-side gaps between launches.
-    run_step, graphed = (lambda: step(x_dev)), False
-    if not args.no_graph:
-        # Only the local computation is captured: capturing the NCCL all-reduce as well (on the
-        # harness's side stream) did not return within 600 s on this pool.
-        try:
-            side = torch.cuda.Stream(device)
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                for _ in range(3):
-                    step(x_dev)
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                compute(x_dev)
-            tail_graph = None
-            if defer:
-                tail_graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(tail_graph, pool=graph.pool()):
-                    deferred_products()
-
-            def run_step():
-                graph.replay()
-                if tail_graph is not None:
-                    buckets.start_exchange()
-                    tail_graph.replay()
-                buckets.finish()
-            run_step()
-            torch.cuda.synchronize()
-            attorch_b200.check_status()
-            graphed = True
-        except Exception as error:  # capture unsupported here: time the eager loop instead
-            print(f'CUDA graph capture failed, timing eager launches: {error}', file=sys.stderr)
-            torch.cuda.synchronize()
-    for _ in range(3):
-        run_step()
-    barrier()
-    launches_before = lib.ab200_launch_count()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank if rank == 0 else -1) as clocks:
-        barrier()
-        start.record()
-        host_t0 = time.perf_counter()
-        for _ in range(args.steps):
-            run_step()
-        host_ms_per_step = (time.perf_counter() - host_t0) * 1e3 / args.steps
-        stop.record()
-        barrier()
-    launches = lib.ab200_launch_count() - launches_before
-    if graphed:
-        # Replays do not pass through the library's host code: count one eager step instead.
-        before = lib.ab200_launch_count()
-        step(x_dev)
+    calibration = runner.time_exchange()
+    graphed = False
+    try:
+        graphed = runner.capture()
+    except Exception as error:  # capture unsupported here: time the eager loop instead
+        print(f'CUDA graph capture failed, timing eager launches: {error}', file=sys.stderr)
+        runner.graphs = None
         torch.cuda.synchronize()
-        launches = (lib.ab200_launch_count() - before) * args.steps
-    ms_total = max_over_ranks(start.elapsed_time(stop))
-    attorch_b200.check_status()
-    ms_per_step = ms_total / args.steps
+    ms_per_step, host_ms_per_step, clocks = runner.timed(args.steps, local_rank if rank == 0 else -1)
+    launches = runner.launches_per_step() * args.steps
     step_flops = flops_per_step(spec, tokens)
     value = step_flops * world_size / (ms_per_step * 1e-3) / 1e12
+    collective_bytes = runner.collective_bytes()
+    schedule, comm_sms = runner.schedule, runner.comm_sms
+    exchange_dtype, param_dtype, widened = runner.buckets.grad_dtype, runner.buckets.dtype, runner.buckets.widen
+    transport = runner.buckets.transport
+
+    # The same local computation without any exchange (at N = 1 this is the step itself): what is
+    # left of a data-parallel step after subtracting it is communication that was not hidden.
+    local_ms = ms_per_step
+    if world_size > 1:
+        solo = StepRunner(args.workload, spec, comm, lib, tokens=tokens, local_only=True)
+        for _ in range(3):
+            solo.step(solo.x)
+        solo.capture()
+        local_ms, _, _ = solo.timed(args.steps)
+        del solo
+        torch.cuda.empty_cache()
 
     # ---------------------------------------------------------------- end to end with host buffers
-    host_x = [torch.randn(tokens, k_in).to(spec['input_dtype']).pin_memory() for _ in range(2)]
-    dev_x = [torch.empty_like(x_dev).requires_grad_(True) for _ in range(2)]
-    # The step's result that is read back: the last layer's bias gradient, or, for a layer without
-    # bias, the first row of its weight gradient.
-    def result_tensor():
-        last = layers[-1]
-        return last.bias.grad if last.bias is not None else last.weight.grad[0]
-    bias_grad_host = torch.empty(n_out, dtype=spec['param_dtype']).pin_memory()
-    copy_stream = torch.cuda.Stream(device)
-    copied = [torch.cuda.Event() for _ in range(2)]
-    consumed = [torch.cuda.Event() for _ in range(2)]
-
-    def e2e_loop(n_steps):
-        compute = torch.cuda.current_stream()
-        with torch.cuda.stream(copy_stream):
-            dev_x[0].data.copy_(host_x[0], non_blocking=True)
-            copied[0].record(copy_stream)
-        for i in range(n_steps):
-            cur, nxt = i % 2, (i + 1) % 2
-            if i + 1 < n_steps:
-                with torch.cuda.stream(copy_stream):
-                    if i >= 1:
-                        copy_stream.wait_event(consumed[nxt])
-                    dev_x[nxt].data.copy_(host_x[nxt], non_blocking=True)
-                    copied[nxt].record(copy_stream)
-            compute.wait_event(copied[cur])
-            step(dev_x[cur])
-            consumed[cur].record(compute)
-            bias_grad_host.copy_(result_tensor(), non_blocking=True)
-        compute.synchronize()
-
-    e2e_loop(3)
-    barrier()
     e2e_steps = max(10, min(args.steps, 40))
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    e2e_loop(e2e_steps)
-    t1.record()
-    barrier()
-    e2e_ms = max_over_ranks(t0.elapsed_time(t1)) / e2e_steps
+    e2e_ms, h2d_bytes, d2h_bytes = end_to_end(runner, comm, e2e_steps)
     e2e_value = step_flops * world_size / (e2e_ms * 1e-3) / 1e12
     attorch_b200.check_status()
+    del runner
+    torch.cuda.empty_cache()
 
     # ---------------------------------------------------------------- roofline of the dominant kernel
     # The tcgen05 GEMM, launched through the C ABI exactly as the layer launches it (forward of the
-    # first layer: X[M, K] * W[K, N] with bias, gelu and the pre-activation store), event-timed on
+    # first layer: X[M, K] * W[K, N] with bias, gelu and the saved-derivative store), event-timed on
     # the launching stream.
     peaks, peak_source = measured_peaks()
     k0, n0 = spec['layers'][0][0], spec['layers'][0][1]
     launch_fwd, _, _ = kernel_launcher(spec, tokens, device, lib, 'fwd')
-
-    for _ in range(5):
-        launch_fwd()
-    torch.cuda.synchronize()
-    reps = 30
-    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    r0.record()
-    for _ in range(reps):
-        launch_fwd()
-    r1.record()
-    torch.cuda.synchronize()
-    kernel_ms = r0.elapsed_time(r1) / reps
+    kernel_ms = event_time(launch_fwd, 30, 5)
+    del launch_fwd
     achieved = 2.0 * tokens * k0 * n0 / (kernel_ms * 1e-3) / 1e12
     roofline = {'bound': 'tensor', 'achieved': achieved, 'peak': peaks['bf16_tflops'], 'unit': 'TFLOP/s',
                 'frac': achieved / peaks['bf16_tflops'],
-                'traffic': NCU_DRAM_BYTES_PER_LAUNCH if (args.workload == 'c2' and tokens == 8192) else None,
+                'traffic': profiled_dram_bytes() if (args.workload == 'c2' and tokens == 8192) else None,
+                'traffic_source': 'ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, from the committed '
+                                  'summary profiles/c2_kernel_fwd.md',
+                'algorithmic_bytes': 2.0 * (tokens * k0 + k0 * n0 + 2 * tokens * n0),
                 'kernel': 'gemm_tcgen05_kernel (forward: bias + gelu + saved-derivative epilogue)',
                 'kernel_ms': kernel_ms, 'peak_source': f'{peak_source} (cuBLAS bf16 burst)',
                 'frac_of_nominal_2250': achieved / 2250.0}
+    kernels = {}
+    if not args.no_extras:
+        for which in ('dx', 'dw', 'act_bwd'):
+            launch, work, unit = kernel_launcher(spec, tokens, device, lib, which)
+            ms = event_time(launch, 20, 3)
+            kernels[which] = {'ms': ms, ('tflops' if unit == 'flops' else 'gbs'):
+                              work / (ms * 1e-3) / (1e12 if unit == 'flops' else 1e9)}
+            del launch
+            torch.cuda.empty_cache()
 
-    if rank != 0:
+    # ---------------------------------------------------------------- sub-records
+    extras = {}
+    collective = {'kind': 'none'}
+    if world_size > 1:
+        choice = log.all_reduce_choice(collective_bytes)
+        collective = {
+            'kind': 'all-reduce (SUM) of dW/db', 'transport': transport, 'schedule': schedule,
+            'dtype': DTYPE_NAMES[exchange_dtype], 'bytes': collective_bytes,
+            'widened_to': DTYPE_NAMES[param_dtype] if widened else None,
+            'sms_left_free_beside_it': comm_sms, **(calibration or {})}
+        if transport == 'multimem':
+            collective.update({
+                'algorithm': 'own kernel: multimem.ld_reduce + multimem.st through NVSwitch (NVLink multicast), '
+                             'two cross-rank barriers', 'ctas': comm_sms})
+        else:
+            collective.update({
+                'algorithm': 'NCCL ' + (choice[0] if choice else '(algorithm not logged)'),
+                'protocol': choice[1] if choice else None, 'channels': choice[2] if choice else None,
+                'nccl_max_ctas': os.environ.get('NCCL_MAX_CTAS')})
+    if not args.no_extras:
         if world_size > 1:
-            dist.destroy_process_group()
+            extras['dp_parity'] = dp_parity(comm)
+            extras['collectives'] = all_reduce_times(comm)
+            torch.cuda.empty_cache()
+        if args.workload == 'c2':
+            # Two layers 8192 -> 8192, global batch 65536 split by rows (strong scaling).
+            c5_spec = WORKLOADS['c5']
+            c5 = StepRunner('c5', c5_spec, comm, lib)
+            for _ in range(3):
+                c5.step(c5.x)
+            c5_graphed = False
+            try:
+                c5_graphed = c5.capture()
+            except Exception as error:
+                print(f'c5: CUDA graph capture failed ({error})', file=sys.stderr)
+                c5.graphs = None
+                torch.cuda.synchronize()
+            c5_steps = max(5, min(args.steps, 10))
+            c5_ms, _, _ = c5.timed(c5_steps)
+            c5_flops = flops_per_step(c5_spec, c5_spec['global_tokens'])
+            record = {'ms_per_step': c5_ms, 'tflops_total': c5_flops / (c5_ms * 1e-3) / 1e12,
+                      'tflops_per_gpu': c5_flops / world_size / (c5_ms * 1e-3) / 1e12,
+                      'frac_of_nominal_2250_per_gpu': c5_flops / world_size / (c5_ms * 1e-3) / 1e12 / 2250.0,
+                      'tokens_per_gpu': c5.tokens, 'steps': c5_steps, 'schedule': c5.schedule,
+                      'cuda_graph': c5_graphed,
+                      'collective_bytes': c5.collective_bytes() if world_size > 1 else 0,
+                      'scaling': 'strong'}
+            del c5
+            torch.cuda.empty_cache()
+            if world_size > 1:
+                # The whole 65536-token batch on one GPU (every rank runs it alone, no exchange).
+                one = StepRunner('c5', c5_spec, comm, lib, tokens=c5_spec['global_tokens'], local_only=True)
+                for _ in range(2):
+                    one.step(one.x)
+                one.capture()
+                one_ms, _, _ = one.timed(3)
+                del one
+                torch.cuda.empty_cache()
+                record['n1_ms_per_step_same_box'] = one_ms
+                record['strong_scaling_efficiency'] = one_ms / (world_size * c5_ms)
+            extras['c5'] = record
+        if world_size == 1 and args.workload == 'c2':
+            base = torch_gpu_baseline(spec, tokens, device, args.steps, args.warmup)
+            base['this_library_over_torch'] = value / base['tflops']
+            extras['torch_gpu_baseline'] = base
+            torch.cuda.empty_cache()
+            c3_spec = WORKLOADS['c3']
+            c3 = StepRunner('c3', c3_spec, comm, lib)
+            for _ in range(3):
+                c3.step(c3.x)
+            c3.capture()
+            c3_ms, _, _ = c3.timed(max(5, min(args.steps, 10)))
+            c3_flops = flops_per_step(c3_spec, c3.tokens)
+            extras['c3'] = {'ms_per_step': c3_ms, 'tflops': c3_flops / (c3_ms * 1e-3) / 1e12,
+                            'frac_of_nominal_2250': c3_flops / (c3_ms * 1e-3) / 1e12 / 2250.0,
+                            'tokens': c3.tokens, 'layers': ['4096->14336 silu', '14336->4096']}
+            del c3
+            torch.cuda.empty_cache()
+            c4 = skinny_forward(30, 5, device, lib)
+            extras['c4'] = {'unit': 'GB/s of weight read, against 8000 nominal and the measured copy bandwidth',
+                            'rows': c4['config']['rows']}
+            torch.cuda.empty_cache()
+
+    comm_log_tail = ''
+    if world_size > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+        comm_log_tail = log.close(echo=(rank == 0))
+    if rank != 0:
         return
 
     line = {
         'metric': 'linear_fwd_bwd_tflops', 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world_size,
         'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms_per_step,
         'host_enqueue_ms_per_step': host_ms_per_step,
+        'local_ms_per_step_without_exchange': local_ms,
+        'exposed_communication_ms_per_step': max(0.0, ms_per_step - local_ms),
         'higher_is_better': True, 'scaling': spec['scaling'], 'vs_baseline': None,
         'dtype': 'bf16', 'data': 'synthetic',
         'config': {'workload': args.workload,
@@ -686,37 +1143,30 @@ def main():
                    'input': str(spec['input_dtype']).replace('torch.', ''),
                    'autocast': str(spec['autocast']).replace('torch.', ''),
                    'parallelism': f'dp{world_size}',
-                   'collective': ('none' if world_size == 1 else
-                                  'NCCL all-reduce of dW/db, ' + (
-                                      'issued per dW block inside backward, overlapped' if overlap else
-                                      'one call between the two captured graphs of a step, overlapping the first '
-                                      "layer's dX" if defer and graphed else 'one call after the step')),
+                   'collective': collective,
                    'cuda_graph': graphed,
                    'l2': 'per-step working set (operands, activations, gradients) exceeds the 126 MB L2; no flush',
                    'tflops_per_gpu': value / world_size,
                    'frac_of_nominal_2250_per_gpu': value / world_size / 2250.0},
-        'clocks': clocks.summary(),
+        'clocks': clocks,
         'e2e': {'value': e2e_value, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms,
-                'h2d_bytes_per_step': host_x[0].numel() * host_x[0].element_size(),
-                'd2h_bytes_per_step': bias_grad_host.numel() * bias_grad_host.element_size()},
+                'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': d2h_bytes,
+                'read_back': 'the step\'s output and the last layer\'s bias gradient'},
         'gpu_launches': int(launches),
         'roofline': roofline,
+        'kernels': kernels,
+        **extras,
     }
+    if world_size > 1:
+        line['comm_log_tail'] = comm_log_tail
     if world_size == 1 and not args.no_cpu_baseline:
-        from oracle.cpu_baseline import time_torch_cpu_linear
-        sample_rows, seconds, threads = 512, 0.0, 1
-        for (k, n, act, bias) in spec['layers']:
-            r = time_torch_cpu_linear(sample_rows, k, n, act, bias, None, steps=10, warmup=2)
-            seconds += r['seconds_per_step']
-            threads = r['threads']
+        seconds, threads = cpu_arm(spec, tokens, steps=5, warmup=1)
         line['cpu_baseline'] = {
-            'value': flops_per_step(spec, sample_rows) / seconds / 1e12, 'unit': 'TFLOP/s', 'cores': threads,
+            'value': flops_per_step(spec, tokens) / seconds / 1e12, 'unit': 'TFLOP/s', 'cores': threads,
             'kind': 'port',
-            'sample': f'{sample_rows} of the batch rows per step, 10 steps, torch.nn.Linear + activation '
+            'sample': f'all {tokens} rows of the batch per step, 5 steps, torch.nn.Linear + activation '
                       f'fwd+bwd in fp32 on {threads} host threads'}
     print(json.dumps(line), flush=True)
-    if world_size > 1:
-        dist.destroy_process_group()
 
 
 if __name__ == '__main__':

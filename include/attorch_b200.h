@@ -51,6 +51,7 @@ extern "C" {
 #define AB200_DEV_TIMEOUT_PRODUCER 1
 #define AB200_DEV_TIMEOUT_MMA 2
 #define AB200_DEV_TIMEOUT_EPILOGUE 3
+#define AB200_DEV_TIMEOUT_COLLECTIVE 4
 
 /* Activation ids: the act_func strings of attorch/linear_layer.py:42-49 in the order of the
  * dispatcher attorch/act_kernels.py:654-727.  Ids 17..21 take `act_param`. */
@@ -321,6 +322,34 @@ int ab200_glu_backward(const void* dy, const void* x, void* dx, int64_t outer, i
  */
 int ab200_cast_2d(const void* src, void* dst, int64_t rows, int64_t cols, int64_t src_stride_r,
                   int64_t src_stride_c, int src_dtype, int dst_dtype, void* stream);
+
+/*
+ * In-place SUM all-reduce of a gradient bucket over the GPUs of one NVSwitch domain (one process per
+ * GPU), through NVLink multicast: the switch adds the ranks' copies (multimem.ld_reduce) and writes the
+ * sums back to all of them (multimem.st); see csrc/allreduce_multimem.cu.  No counterpart in the
+ * reference, which has no distributed code; it serves the data-parallel step, where dW / db of every
+ * layer are summed over the ranks that share a batch (what `torch.distributed.all_reduce` would do).
+ *   multicast_ptr  the multicast address of the buffer: `numel` elements of `dtype`, 16-byte aligned,
+ *                  numel * element size a multiple of 16 bytes.  Every rank has bound its own buffer of
+ *                  that size to one multicast object and calls with the same arguments but `rank`.
+ *   flag_blocks    DEVICE array of world_size pointers: entry r is rank r's flag block as mapped into
+ *                  this rank's address space (peer-accessible memory of ab200_collective_flag_bytes()
+ *                  bytes, zeroed once before the first call and then left to the library).
+ *   ctas           CTAs (= SMs) the kernel uses, at most AB200_COLLECTIVE_MAX_CTAS; <= 0 picks 8.  The
+ *                  additions run in the switch, so few are enough; every rank must pass the same value.
+ *   status         device word as for the GEMMs: a rank that waits longer than 2 s for another stores
+ *                  AB200_DEV_TIMEOUT_COLLECTIVE there and returns.
+ * Every rank must make the same sequence of calls on the same flag blocks (the barriers count
+ * launches), and the buffer's contents must be final on the calling stream before the call.  All ranks
+ * end with bit-identical sums.  world_size == 1 returns at once.
+ */
+#define AB200_COLLECTIVE_MAX_CTAS 32
+#define AB200_COLLECTIVE_MAX_RANKS 16
+int ab200_multimem_all_reduce(void* multicast_ptr, int64_t numel, int dtype, int rank, int world_size,
+                              void* const* flag_blocks, int ctas, int* status, void* stream);
+
+/* Size in bytes of one rank's flag block for ab200_multimem_all_reduce. */
+int64_t ab200_collective_flag_bytes(void);
 
 #ifdef __cplusplus
 }
