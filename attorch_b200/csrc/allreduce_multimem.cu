@@ -26,8 +26,8 @@
 namespace ab200 {
 namespace {
 
-constexpr int kThreads = 512;
-constexpr int kUnroll = 4;
+constexpr int kThreads = 1024;
+constexpr int kUnroll = 8;
 
 __device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t value) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(value) : "memory");

@@ -14,7 +14,9 @@ attorch/glu_kernels.py:13-16 and 56-59).
 
 Each case is stored as one .npz with the inputs (or the seed that regenerates them plus a
 checksum) and the reference's output, dX, dW and db; the standalone activation layers go into
-act_layers_fp32.npz, the gated linear unit into glu_fp32.npz.  bf16 is not generated: the interpreter's bf16 dot product returns garbage.
+act_layers_fp32.npz, the gated linear unit into glu_fp32.npz, bf16 runs of both (element-wise
+kernels only) into elementwise_bf16.npz.  The linear layer itself is not generated in bf16: the
+interpreter's bf16 dot product returns garbage.
 """
 
 import argparse
@@ -164,6 +166,7 @@ def main():
 
     act_layer_goldens(attorch)
     glu_goldens(attorch)
+    elementwise_bf16_goldens(attorch)
 
 
 ACT_LAYERS = [('Sigmoid', {}), ('LogSigmoid', {}), ('Tanh', {}), ('ReLU', {}), ('GELU', {}),
@@ -234,6 +237,60 @@ def glu_goldens(attorch):
             data[f'dx_{tag}'] = xin.grad.numpy()
     np.savez_compressed(OUT_DIR / 'glu_fp32.npz', **data)
     print('wrote glu_fp32.npz')
+
+
+def elementwise_bf16_goldens(attorch):
+    """
+    bf16 vectors of the reference's element-wise kernels (the interpreter's bf16 dot product is broken,
+    its element-wise arithmetic is not): every standalone activation layer - whose backward is the
+    act_func_backward_kernel the linear layer's backward launches too (attorch/linear_layer.py:143-146) -
+    and the gated linear unit, on bf16 inputs that contain the piecewise switch points.  These pin
+    the arithmetic in front of the final store.  Two properties of the interpreter limit what they pin:
+    it converts fp32 to bf16 by dropping the low 16 bits (a GPU rounds to nearest even), and it gets
+    products of two bf16 tensors wrong (the second half of every GLU gradient and everything hardshrink
+    touches in the GLU come out with magnitudes of 1e30; the tests leave those entries alone).  Values
+    are saved as fp32 arrays holding bf16 numbers.
+    """
+    gen = torch.Generator().manual_seed(6)
+    x = (torch.randn(6, 40, generator=gen) * 2).bfloat16()
+    x[0, :12] = torch.tensor([-6.0, -3.0, -1.0, -0.5, 0.0, 0.5, 1.0, 3.0, 6.0, 7.0, -7.0, 2.0]).bfloat16()
+    dy = torch.randn(6, 40, generator=gen).bfloat16()
+    data = {'x': x.float().numpy(), 'dy': dy.float().numpy()}
+    skipped = []
+    for index, (name, kwargs) in enumerate(ACT_LAYERS):
+        layer = getattr(attorch, name)(**kwargs)
+        xin = x.clone().requires_grad_(True)
+        try:
+            y = layer(xin)
+            y.backward(dy)
+        except Exception as error:   # triton 3.6: the interpreter cannot make the bf16 constants some kernels use
+            if 'get_bf16' not in repr(error):
+                raise
+            skipped.append(f'{index:02d}_{name}')
+            continue
+        assert y.dtype is torch.bfloat16
+        data[f'y_{index:02d}_{name}'] = y.detach().float().numpy()
+        data[f'dx_{index:02d}_{name}'] = xin.grad.float().numpy()
+    gx = (torch.randn(6, 10, generator=gen) * 2).bfloat16()
+    gdy = torch.randn(6, 5, generator=gen).bfloat16()
+    data['glu_x'], data['glu_dy'] = gx.float().numpy(), gdy.float().numpy()
+    for act_func in [a for a in ALL_ACT_FUNCS if a is not None]:
+        xin = gx.clone().requires_grad_(True)
+        tag = act_func.replace('.', 'p')
+        try:
+            y = attorch.GLU(dim=-1, act_func=act_func)(xin)
+            y.backward(gdy)
+        except Exception as error:
+            if 'get_bf16' not in repr(error):
+                raise
+            skipped.append(f'glu_{tag}')
+            continue
+        assert y.dtype is torch.bfloat16
+        data[f'glu_y_{tag}'] = y.detach().float().numpy()
+        data[f'glu_dx_{tag}'] = xin.grad.float().numpy()
+    data['skipped'] = np.array(','.join(skipped))
+    np.savez_compressed(OUT_DIR / 'elementwise_bf16.npz', **data)
+    print('wrote elementwise_bf16.npz; the interpreter could not run:', skipped)
 
 
 if __name__ == '__main__':

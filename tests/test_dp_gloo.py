@@ -54,7 +54,7 @@ def _worker(rank: int, world_size: int, port: int, overlap_requested: bool, defe
         assert buckets.world_size == world_size
         assert (layers[0].defer_input_grad is not None) == defer and layers[1].defer_input_grad is None
         assert not buckets.overlap            # side streams exist only on CUDA
-        assert buckets.flat.numel() == 24 * 32 + 32 + 32 * 16 + 16
+        assert buckets.flat.numel() == 24 * 32 + 32 + 32 * 16 + 16       # already whole 16-byte units
         # The gradient destinations alias the flat bucket.
         assert layers[0].weight_grad_out.data_ptr() == buckets.flat.data_ptr()
         xs, dys = shard_rows(x, rank, world_size), shard_rows(dy, rank, world_size)
@@ -120,7 +120,7 @@ def test_grads_alias_the_bucket():
     """
     layers = [attorch_b200.Linear(4, 6, device='cpu'), attorch_b200.Linear(6, 2, bias=False, device='cpu')]
     buckets = GradientBuckets(layers)
-    assert buckets.flat.numel() == 4 * 6 + 6 + 6 * 2
+    assert buckets.flat.numel() == 44          # 4 * 6 + 6 + 6 * 2 = 42 fp32, padded to whole 16-byte units
     assert layers[0].weight.grad.data_ptr() == buckets.flat.data_ptr()
     assert layers[0].bias.grad.data_ptr() == buckets.flat[24:].data_ptr()
     assert layers[1].weight.grad.data_ptr() == buckets.flat[30:].data_ptr()

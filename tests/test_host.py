@@ -62,7 +62,7 @@ def test_header_constants_match_python():
 def test_version_and_error_strings(lib):
     assert lib.ab200_version() == 1000
     assert _lib.error_string(0) == 'ok'
-    for code in range(-11, 4):
+    for code in range(-11, 5):
         assert _lib.error_string(code) != 'unknown code'
     assert _lib.error_string(99) == 'unknown code'
 
@@ -93,6 +93,23 @@ def test_argument_validation_without_gpu(lib):
     assert lib.ab200_cast_2d(fake, fake, -1, 2, 2, 1, 0, 2, None) == -2
     assert lib.ab200_linear_backward_input(fake, fake, None, 4, 8, 8, 8, 1, 8, 1, 8, 2, 2, None, 0, None, None, 0) == -1
     assert lib.ab200_linear_backward_weight(fake, fake, fake, 4, 8, 8, 8, 1, 8, 1, 4, 2, 2, None, 0, None, None, 0) == -5
+
+
+def test_collective_argument_validation_without_gpu(lib):
+    """The all-reduce entry point rejects bad arguments on the host; a world of one is a no-op."""
+    fake = ctypes.c_void_p(0x1000)
+    def reduce(ptr=fake, numel=64, dtype=2, rank=0, world=2, flags=fake, status=fake):
+        return lib.ab200_multimem_all_reduce(ptr, numel, dtype, rank, world, flags, 8, status, None)
+    assert reduce(world=1) == 0 and reduce(numel=0) == 0
+    assert reduce(numel=-1) == -2 and reduce(rank=2) == -2 and reduce(world=0) == -2
+    assert reduce(world=17, rank=3) == -9
+    assert reduce(dtype=5) == -3
+    assert reduce(ptr=None) == -1 and reduce(flags=None) == -1 and reduce(status=None) == -1
+    assert reduce(numel=63) == -5                            # 126 bytes: not whole 16-byte units
+    assert reduce(ptr=ctypes.c_void_p(0x1008)) == -5         # misaligned base
+    assert lib.ab200_collective_flag_bytes() == (32 * 16 + 32) * 4
+    # The reservation field of the GEMM flags: bits 16-23.
+    assert _lib.FLAG_RESERVE_SMS_SHIFT == 16
 
 
 def test_workspace_sizes(lib):
