@@ -1,0 +1,182 @@
+"""
+Full-size configurations in the mode the benchmark runs them, and gradients against expectations that
+never pass through a tensor the GPU stored.
+
+The oracle here is float64 (or fp32) arithmetic on the operands as the kernels see them - rounded to
+the autocast dtype - evaluated on sampled rows or columns where the whole product would take minutes
+on a CPU.  The activations used (gelu, silu) are smooth, so a pre-activation that the GPU and the CPU
+round to neighbouring bf16 values moves the derivative by far less than the tolerance, and the
+gradients can be checked without handing the oracle the GPU's saved tensor.
+Tolerance: rtol = atol = 1e-2 (bf16 / fp16 products with fp32 accumulation).
+"""
+
+import pytest
+import torch
+
+import attorch_b200
+from attorch_b200 import _lib
+from oracle import linear_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+DEV = 'cuda'
+TOL = 1e-2
+
+
+def close(got, want, what, tol=TOL, atol=None):
+    torch.testing.assert_close(got.float().cpu(), want.float().cpu(), rtol=tol, atol=atol or tol,
+                               msg=lambda m: f'{what}: {m}')
+
+
+def layer_from(w, b, act_func, dtype):
+    layer = attorch_b200.Linear(w.shape[0], w.shape[1], bias=b is not None, act_func=act_func, device=DEV, dtype=dtype)
+    with torch.no_grad():
+        layer.weight.copy_(w)
+        if b is not None:
+            layer.bias.copy_(b)
+    return layer
+
+
+def test_config2_in_the_benchmarks_mode():
+    """
+    fp32 parameters and fp32 input under bf16 autocast, M = 8192, 4096 -> 4096, gelu, bias, upstream
+    gradient N(0, 1) * 0.01: the cast kernels, the bf16 GEMMs and fp32 dX / dW / db at full size.
+    Expectation: operands rounded to bf16, products in float64 on 48 sampled rows (output, dX) and 48
+    sampled input features (dW, over all 8192 rows, with dZ from a full fp32 product on the CPU), db in
+    full.  Nothing the GPU stored enters the expectation.
+    """
+    torch.manual_seed(0)
+    M, K, N = 8192, 4096, 4096
+    x = torch.randn(M, K)
+    lin = torch.nn.Linear(K, N)
+    w = lin.weight.detach().T.contiguous()
+    b = lin.bias.detach().clone()
+    dy = (torch.randn(M, N) * 0.01).bfloat16()
+    layer = layer_from(w, b, 'gelu', torch.float32)
+    xg = x.to(DEV).requires_grad_(True)
+    with torch.autocast('cuda', dtype=torch.bfloat16):
+        y = layer(xg)
+    assert y.dtype is torch.bfloat16
+    y.backward(dy.to(DEV))
+    attorch_b200.check_status()
+    assert xg.grad.dtype is torch.float32 and layer.weight.grad.dtype is torch.float32 \
+        and layer.bias.grad.dtype is torch.float32
+    xb, wb, bb = x.bfloat16().float(), w.bfloat16().float(), b.bfloat16().float()
+    z = xb @ wb + bb                                   # fp32 on the CPU: 275 GFLOP
+    zr = z.bfloat16().float()                          # the pre-activation as the reference stores it
+    rows = torch.randperm(M)[:48]
+    z64 = xb[rows].double() @ wb.double() + bb.double()
+    close(y[rows.to(DEV)], oracle.act_forward('gelu', z64.float()), 'output rows')
+    dz = (dy.float() * oracle.act_grad('gelu', zr)).bfloat16().float()
+    close(xg.grad[rows.to(DEV)], dz[rows].double() @ wb.double().T, 'dX rows')
+    feats = torch.randperm(K)[:48]
+    close(layer.weight.grad[feats.to(DEV)], xb[:, feats].double().T @ dz.double(), 'dW rows')
+    close(layer.bias.grad, dz.sum(0), 'db')
+
+
+@pytest.mark.parametrize('m', [1, 8, 32, 128])
+def test_config4_full_size(m):
+    """Skinny forward at its full size: fp16, 8192 -> 28672, no bias, no activation, M rows."""
+    gen = torch.Generator().manual_seed(40 + m)
+    K, N = 8192, 28672
+    x = torch.randn(m, K, generator=gen).half()
+    w = (torch.randn(K, N, generator=gen) * 0.02).half()
+    layer = layer_from(w, None, None, torch.float16)
+    with torch.no_grad():
+        y = layer(x.to(DEV))
+    attorch_b200.check_status()
+    assert y.shape == (m, N) and y.dtype is torch.float16
+    if torch.cuda.get_device_properties(0).multi_processor_count <= 186:
+        assert _lib.load().ab200_last_path() == (_lib.PATH_TCGEN05 if m >= 8 else _lib.PATH_STREAMK)
+    close(y, x.float() @ w.float(), 'output')
+
+
+def test_config5_per_gpu_shape():
+    """
+    The data-parallel configuration's per-GPU step at 8 GPUs: 8192 tokens, two layers 8192 -> 8192
+    (gelu + bias, then bias), bf16.  Sampled rows for the output and dX, sampled columns for both
+    weight gradients (all rows of them), the bias gradients in full; float64 products of the bf16
+    operands, nothing from the GPU in the expectation.
+    """
+    torch.manual_seed(1)
+    M, D = 8192, 8192
+    x = torch.randn(M, D).bfloat16()
+    w1 = (torch.randn(D, D) / D ** 0.5).bfloat16()
+    b1 = torch.randn(D).bfloat16()
+    w2 = (torch.randn(D, D) / D ** 0.5).bfloat16()
+    b2 = torch.randn(D).bfloat16()
+    dy = (torch.randn(M, D) * 0.01).bfloat16()
+    l1, l2 = layer_from(w1, b1, 'gelu', torch.bfloat16), layer_from(w2, b2, None, torch.bfloat16)
+    xg = x.to(DEV).requires_grad_(True)
+    y = l2(l1(xg))
+    y.backward(dy.to(DEV))
+    attorch_b200.check_status()
+
+    rows = torch.randperm(M)[:32]
+    cols = torch.randperm(D)[:32]
+    f64 = lambda t: t.double()
+    # Rows of the forward pass and of dX.
+    z1 = (f64(x[rows]) @ f64(w1) + f64(b1)).float()
+    h = oracle.act_forward('gelu', z1).bfloat16()
+    close(y[rows.to(DEV)], f64(h) @ f64(w2) + f64(b2), 'output rows')
+    dh = (f64(dy[rows]) @ f64(w2).T).float().bfloat16()
+    dz1 = (dh.float() * oracle.act_grad('gelu', z1.bfloat16().float())).bfloat16()
+    close(xg.grad[rows.to(DEV)], f64(dz1) @ f64(w1).T, 'dX rows')
+    # Columns of the weight gradients: dW2[:, c] = H^T dY[:, c] needs all of H = gelu(X W1 + b1): fp32 on the CPU.
+    h_full = oracle.act_forward('gelu', x.float() @ w1.float() + b1.float()).bfloat16()
+    close(l2.weight.grad[:, cols.to(DEV)], h_full.float().T @ dy[:, cols].float(), 'dW2 columns')
+    close(l2.bias.grad, dy.float().sum(0), 'db2')
+    # dW1[:, c] = X^T dZ1[:, c], dZ1[:, c] = (dY W2^T)[:, c] * gelu'(Z1[:, c]).
+    z1c = (x.float() @ w1[:, cols].float() + b1[cols].float()).bfloat16().float()
+    dhc = (dy.float() @ w2[cols].float().T).bfloat16().float()
+    dz1c = (dhc * oracle.act_grad('gelu', z1c)).bfloat16()
+    # The first layer's dZ is rounded twice on the GPU (the saved act'(Z) to bf16, then the product),
+    # once in this expectation: a relative difference of about 0.3 % RMS per element of dZ, which over
+    # a reduction of 8192 rows of N(0, 1) inputs adds up to about 2e-3 RMS on weight-gradient values of
+    # 0.6 RMS (plus their own bf16 rounding, 1.4e-3 RMS).  Among 262144 sampled elements the largest
+    # deviation is therefore 4 to 5 of those standard deviations, about 1.1e-2: the absolute tolerance
+    # is 2e-2 here, the relative one stays 1e-2.
+    close(l1.weight.grad[:, cols.to(DEV)], x.float().T @ dz1c.float(), 'dW1 columns', atol=2e-2)
+    db1_c = dz1c.float().sum(0)
+    close(l1.bias.grad[cols.to(DEV)], db1_c, 'db1 columns')
+
+
+FAMILIES = [('tcgen05 pairs', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK),
+            ('tcgen05 single CTA', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK | _lib.FLAG_NO_PAIR),
+            ('tcgen05 register stores', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK | _lib.FLAG_NO_TMA_STORE),
+            ('stream-K', _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_FORCE_STREAMK),
+            ('generic', _lib.FLAG_FORCE_GENERIC)]
+
+
+@pytest.mark.parametrize('act_func', ['gelu', 'silu'])
+@pytest.mark.parametrize('save_derivative', [True, False])
+@pytest.mark.parametrize('family,flags', FAMILIES, ids=[f[0] for f in FAMILIES])
+def test_gradients_against_an_independent_expectation(family, flags, save_derivative, act_func):
+    """
+    One check per kernel family in which dX, dW and db are compared with the oracle's own forward and
+    backward (float64 products of the bf16 operands): neither the pre-activation nor the derivative
+    the GPU saved is handed to the oracle.
+    """
+    gen = torch.Generator().manual_seed(77)
+    M, K, N = 300, 264, 520
+    x = torch.randn(M, K, generator=gen).bfloat16()
+    w = (torch.randn(K, N, generator=gen) / K ** 0.5).bfloat16()
+    b = torch.randn(N, generator=gen).bfloat16()
+    dy = torch.randn(M, N, generator=gen).bfloat16()
+    layer = layer_from(w, b, act_func, torch.bfloat16)
+    previous_flags = attorch_b200.set_gemm_flags(flags)
+    previous_mode = attorch_b200.set_save_derivative(save_derivative)
+    try:
+        xg = x.to(DEV).requires_grad_(True)
+        y = layer(xg)
+        y.backward(dy.to(DEV))
+        attorch_b200.check_status()
+    finally:
+        attorch_b200.set_gemm_flags(previous_flags)
+        attorch_b200.set_save_derivative(previous_mode)
+    z = x.double() @ w.double() + b.double()
+    close(y, oracle.act_forward(act_func, z.float()), 'output')
+    zr = z.float().bfloat16().float()
+    dz = (dy.float() * oracle.act_grad(act_func, zr)).bfloat16()
+    close(xg.grad, dz.double() @ w.double().T, 'dX')
+    close(layer.weight.grad, x.double().T @ dz.double(), 'dW')
+    close(layer.bias.grad, dz.float().sum(0), 'db')
