@@ -178,6 +178,7 @@ const char* ab200_error_string(int code) {
     case ERR_LAUNCH: return "kernel launch failed";
     case ERR_TOO_LARGE: return "a dimension exceeds 2^31 - 1";
     case ERR_DRIVER: return "CUDA driver entry point or symbol address unavailable";
+    case ERR_BAD_PROBABILITY: return "dropout probability outside [0, 1]";
     case ERR_STATIC_SCRATCH_TOO_SMALL:
       return "shape needs more scratch than the built-in array of ab200_act_backward_static holds";
     case DEV_TIMEOUT_PRODUCER: return "device: TMA producer gave up waiting for a free stage";
@@ -591,9 +592,14 @@ int launch_act_elementwise(const void* x, const void* dy, void* out, int64_t n, 
   if (n < 0) return ERR_BAD_SHAPE;
   if (!valid_dtype(dtype)) return ERR_BAD_DTYPE;
   if (!valid_act(act)) return ERR_BAD_ACT;
-  if (!(drop_p >= 0.0f && drop_p < 1.0f)) return ERR_BAD_SHAPE;
+  if (!(drop_p >= 0.0f && drop_p <= 1.0f)) return ERR_BAD_PROBABILITY;
   if (n == 0) return OK;
   if (!x || !out || (kBackward && !dy)) return ERR_NULL_POINTER;
+  if (drop_p == 1.0f) {
+    // Every element is dropped (the uniform numbers lie in [0, 1)): the reference's
+    // tl.where(random < 1, 0, ...) gives zeros in both directions (attorch/dropout_kernels.py:12-46).
+    return cudaMemsetAsync(out, 0, static_cast<size_t>(n) * dtype_size(dtype), stream) == cudaSuccess ? OK : ERR_LAUNCH;
+  }
   const int dropout = drop_p > 0.0f ? ((flags & AB200_FLAG_DROPOUT_PACKED) ? DROPOUT_PACKED : DROPOUT_REFERENCE)
                                     : DROPOUT_OFF;
   const uint32_t threshold = dropout ? dropout_threshold(drop_p, dropout) : 0u;

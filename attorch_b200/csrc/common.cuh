@@ -27,6 +27,7 @@ enum Status : int {
   ERR_TOO_LARGE = -9,
   ERR_DRIVER = -10,
   ERR_STATIC_SCRATCH_TOO_SMALL = -11,
+  ERR_BAD_PROBABILITY = -12,
 };
 
 // Codes a kernel writes to the caller's device status word when a bounded wait runs out.

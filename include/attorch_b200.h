@@ -45,6 +45,7 @@ extern "C" {
 #define AB200_ERR_TOO_LARGE (-9)
 #define AB200_ERR_DRIVER (-10)
 #define AB200_ERR_STATIC_SCRATCH_TOO_SMALL (-11)
+#define AB200_ERR_BAD_PROBABILITY (-12)
 
 /* Device-side status codes (written to *status). */
 #define AB200_DEV_OK 0
@@ -261,7 +262,8 @@ int ab200_linear_backward_weight(const void* x, const void* dz, void* dw, int64_
  * Replaces act_func_forward_kernel (attorch/act_kernels.py:840-880, launched at
  * attorch/act_layers.py:66-73) with apply_dropout (attorch/dropout_kernels.py:12-28).  x, y: n
  * contiguous elements of `dtype`; act != AB200_ACT_NONE is not required (identity + dropout works).
- * drop_p = 0 switches dropout off; otherwise element i is dropped iff
+ * drop_p = 0 switches dropout off and drop_p = 1 drops every element (zeros, as the reference's
+ * tl.where(random < 1, 0, ...) gives); otherwise element i is dropped iff
  * ab200_dropout_uniform(seed, i, flags) < drop_p.  flags: 0 or AB200_FLAG_DROPOUT_PACKED.
  */
 int ab200_act_forward(const void* x, void* y, int64_t n, int dtype, int act, float act_param, float drop_p,

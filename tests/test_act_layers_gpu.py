@@ -140,3 +140,17 @@ def test_eval_mode_and_edge_shapes():
         attorch_b200.GELU(approximate='fast')
     with pytest.raises(RuntimeError, match='no CPU fallback'):
         attorch_b200.ReLU()(torch.randn(4))
+
+
+@pytest.mark.parametrize('stream', ['reference', 'packed'])
+def test_drop_everything(stream):
+    """drop_p = 1: every element is dropped in both directions, as the reference's tl.where(random < 1, 0, ...) gives."""
+    attorch_b200.set_dropout_stream(stream)
+    try:
+        layer = attorch_b200.GELU(drop_p=1.0)
+        layer.train()
+        y, dx = run(layer, torch.randn(5, 77).bfloat16(), torch.randn(5, 77))
+    finally:
+        attorch_b200.set_dropout_stream('reference')
+    assert torch.count_nonzero(y) == 0 and torch.count_nonzero(dx) == 0
+    assert not torch.isnan(y.float()).any() and not torch.isnan(dx.float()).any()

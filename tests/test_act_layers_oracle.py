@@ -99,3 +99,19 @@ def test_integer_threshold_equals_float_comparison(drop_p):
             m = np.where(signed < 0, -signed - 1, signed).astype(np.uint64)
             u = m.astype(np.float32) * np.float32(4.6566127342e-10)
         assert np.array_equal(u < p32, m < np.uint64(t))
+
+
+def test_drop_everything_in_the_oracle_and_on_the_host():
+    """drop_p = 1 drops every element; probabilities outside [0, 1] are rejected with their own code."""
+    import ctypes
+    from attorch_b200 import _lib
+    from attorch_b200 import build as builder
+    x = torch.randn(64)
+    assert torch.count_nonzero(oracle.act_layer_forward(x, 'relu', drop_p=1.0, seed=5)) == 0
+    if not builder.LIB_PATH.exists():
+        pytest.skip('library not built')
+    lib = _lib.load()
+    fake = ctypes.c_void_p(0x1000)
+    assert lib.ab200_act_forward(fake, fake, 8, 2, 4, 0.0, 1.5, 0, None, 0) == -12
+    assert lib.ab200_act_forward(fake, fake, 8, 2, 4, 0.0, -0.1, 0, None, 0) == -12
+    assert lib.ab200_act_input_grad(fake, fake, fake, 0, 2, 4, 0.0, 1.0, 0, None, 0) == 0     # empty: nothing to do

@@ -62,7 +62,7 @@ def test_header_constants_match_python():
 def test_version_and_error_strings(lib):
     assert lib.ab200_version() == 1000
     assert _lib.error_string(0) == 'ok'
-    for code in range(-11, 5):
+    for code in range(-12, 5):
         assert _lib.error_string(code) != 'unknown code'
     assert _lib.error_string(99) == 'unknown code'
 
