@@ -566,8 +566,9 @@ class StepRunner:
         transport = os.environ.get('AB200_TRANSPORT', 'auto') if self.distributed else 'nccl'
         self.buckets = None
         if self.distributed and transport != 'nccl' and schedule in (None, 'graph_overlap'):
-            # The library's own all-reduce: 8 CTAs, the whole bucket of a layer in one call.
-            ctas = int(os.environ.get('AB200_COMM_CTAS', '8'))
+            # The library's own all-reduce, the whole bucket of a layer in one call.  4 CTAs measured
+            # best for workload c2 at 2, 4 and 8 GPUs (8 GPUs: 0.735 / 0.740 / 0.754 ms with 4 / 8 / 16).
+            ctas = int(os.environ.get('AB200_COMM_CTAS', '4'))
             buckets = GradientBuckets(self.layers, overlap=True, dw_chunks=int(os.environ.get('AB200_DW_CHUNKS', '1')),
                                       grad_dtype=grad_dtype, transport=transport, comm_ctas=ctas)
             if buckets.transport == 'multimem':
@@ -1170,6 +1171,8 @@ def main():
         'clocks': clocks,
         'e2e': {'value': e2e_value, 'unit': 'TFLOP/s', 'ms_per_step': e2e_ms,
                 'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': d2h_bytes,
+                'host_link_gbs_per_gpu': (h2d_bytes + d2h_bytes) / (e2e_ms * 1e-3) / 1e9,
+                'bound': 'host-device copies (PCIe and host memory, shared by the ranks of a box)',
                 'read_back': 'the step\'s output and the last layer\'s bias gradient'},
         'gpu_launches': int(launches),
         'roofline': roofline,
