@@ -9,6 +9,8 @@ Public surface (mirrors the reference's for this path, attorch/__init__.py:7-22)
     Sigmoid ... Softshrink, ActFuncAutoGrad
                       the standalone activation layers with fused dropout (attorch/act_layers.py)
     GLU, GLUAutoGrad  the gated linear unit with an arbitrary activation (attorch/glu_layer.py)
+    CrossEntropyLoss, CrossEntropyLossAutoGrad
+                      mean cross-entropy over class indices (attorch/cross_entropy_loss_layer.py)
     set_dropout_stream
                       the reference's dropout mask (default) or a cheaper generator
     nn                torch.nn with this package's modules in place of PyTorch's (attorch/nn.py)
@@ -19,11 +21,12 @@ from . import convert, nn
 from .act_layers import (CELU, ELU, GELU, SELU, ActFuncAutoGrad, Hardshrink, Hardsigmoid, Hardswish,
                          Hardtanh, LeakyReLU, LogSigmoid, Mish, ReLU, ReLU6, Sigmoid, SiLU, Softplus,
                          Softshrink, Softsign, Tanh, Tanhshrink, set_dropout_stream)
+from .cross_entropy_loss_layer import CrossEntropyLoss, CrossEntropyLossAutoGrad
 from .glu_layer import GLU, GLUAutoGrad
 from .linear_layer import (Linear, LinearAutoGrad, check_status, get_output_dtype, set_gemm_flags,
                            set_reserved_sms, set_save_derivative)
 
-__all__ = ['convert', 'nn', 'GLU', 'GLUAutoGrad', 'Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags',
+__all__ = ['convert', 'nn', 'CrossEntropyLoss', 'CrossEntropyLossAutoGrad', 'GLU', 'GLUAutoGrad', 'Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags',
            'set_save_derivative', 'set_reserved_sms', 'set_dropout_stream', 'ActFuncAutoGrad', 'CELU', 'ELU', 'GELU', 'SELU', 'Hardshrink',
            'Hardsigmoid', 'Hardswish', 'Hardtanh', 'LeakyReLU', 'LogSigmoid', 'Mish', 'ReLU', 'ReLU6',
            'Sigmoid', 'SiLU', 'Softplus', 'Softshrink', 'Softsign', 'Tanh', 'Tanhshrink']

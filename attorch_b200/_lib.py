@@ -73,6 +73,11 @@ SIGNATURES = {
     'ab200_dropout_uniform': (_f32, [ctypes.c_uint32, ctypes.c_uint64, _int]),
     'ab200_dropout_threshold': (ctypes.c_uint32, [_f32, _int]),
     'ab200_cast_2d': (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _int, _int, _ptr]),
+    'ab200_cross_entropy_workspace_bytes': (_i64, [_i64]),
+    'ab200_cross_entropy_forward': (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _int, _int,
+                                           _ptr, _i64, _ptr]),
+    'ab200_cross_entropy_backward': (_int, [_ptr, _int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64,
+                                            _i64, _int, _int, _int, _ptr]),
     'ab200_multimem_all_reduce': (_int, [_ptr, _i64, _int, _int, _int, _ptr, _int, _ptr, _ptr]),
     'ab200_collective_flag_bytes': (_i64, []),
 }

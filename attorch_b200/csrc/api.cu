@@ -14,6 +14,7 @@
 #include "kernels_misc.cuh"
 #include "act_elementwise.cuh"
 #include "glu.cuh"
+#include "cross_entropy.cuh"
 
 namespace ab200 {
 
@@ -673,6 +674,74 @@ int ab200_glu_forward(const void* x, void* y, int64_t outer, int64_t inner, int 
 int ab200_glu_backward(const void* dy, const void* x, void* dx, int64_t outer, int64_t inner, int dtype, int act,
                        float act_param, void* stream) {
   return launch_glu<true>(x, dy, dx, outer, inner, dtype, act, act_param, static_cast<cudaStream_t>(stream));
+}
+
+int64_t ab200_cross_entropy_workspace_bytes(int64_t M) { return M > 0 ? (2 * M + 1) * 4 : 4; }
+
+int ab200_cross_entropy_forward(const void* logits, const int64_t* target, const void* weight, void* loss,
+                                float* lse, int64_t M, int64_t V, int64_t stride_m, int64_t stride_v, int dtype,
+                                int weight_dtype, int loss_dtype, void* workspace, int64_t workspace_bytes,
+                                void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || V <= 0) return ERR_BAD_SHAPE;
+  if (!fits_int(M) || !fits_int(V)) return ERR_TOO_LARGE;
+  if (!valid_dtype(dtype) || !valid_dtype(loss_dtype) || (weight && !valid_dtype(weight_dtype))) return ERR_BAD_DTYPE;
+  if (!loss || !workspace || (M > 0 && (!logits || !target || !lse))) return ERR_NULL_POINTER;
+  if (workspace_bytes < ab200_cross_entropy_workspace_bytes(M)) return ERR_WORKSPACE_TOO_SMALL;
+  float* row_loss = static_cast<float*>(workspace);
+  float* row_weight = row_loss + M;
+  float* denominator = row_weight + M;
+  if (M > 0) {
+    const unsigned grid = static_cast<unsigned>(M);
+    const long long* t = reinterpret_cast<const long long*>(target);
+    if (dtype == DT_F32)
+      ce_forward_kernel<float><<<grid, kCeThreads, 0, stream>>>(static_cast<const float*>(logits), stride_m, stride_v, t,
+                                                             weight, weight_dtype, row_loss, row_weight, lse, static_cast<int>(V));
+    else if (dtype == DT_F16)
+      ce_forward_kernel<__half><<<grid, kCeThreads, 0, stream>>>(static_cast<const __half*>(logits), stride_m, stride_v, t,
+                                                              weight, weight_dtype, row_loss, row_weight, lse, static_cast<int>(V));
+    else
+      ce_forward_kernel<__nv_bfloat16><<<grid, kCeThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), stride_m,
+                                                                     stride_v, t, weight, weight_dtype, row_loss,
+                                                                     row_weight, lse, static_cast<int>(V));
+    ++g_launches;
+    if (cudaGetLastError() != cudaSuccess) return ERR_LAUNCH;
+  }
+  ce_finish_kernel<<<1, 1024, 0, stream>>>(row_loss, row_weight, M, weight != nullptr ? 1 : 0, loss, loss_dtype, denominator);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
+}
+
+int ab200_cross_entropy_backward(const void* loss_grad, int loss_grad_dtype, const void* logits, const int64_t* target,
+                                 const void* weight, const float* lse, const void* workspace, void* logits_grad,
+                                 int64_t M, int64_t V, int64_t stride_m, int64_t stride_v, int64_t ld_grad, int dtype,
+                                 int weight_dtype, int grad_dtype, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || V <= 0) return ERR_BAD_SHAPE;
+  if (!fits_int(M) || !fits_int(V)) return ERR_TOO_LARGE;
+  if (!valid_dtype(dtype) || !valid_dtype(grad_dtype) || !valid_dtype(loss_grad_dtype) ||
+      (weight && !valid_dtype(weight_dtype)))
+    return ERR_BAD_DTYPE;
+  // The gradient has the input's type, or fp32 for 16-bit logits (the loss's type under autocast).
+  if (grad_dtype != dtype && grad_dtype != DT_F32) return ERR_BAD_DTYPE;
+  if (M == 0) return OK;
+  if (!loss_grad || !logits || !target || !lse || !workspace || !logits_grad) return ERR_NULL_POINTER;
+  if (ld_grad < V) return ERR_BAD_STRIDE;
+  const float* denominator = static_cast<const float*>(workspace) + 2 * M;
+  const unsigned grid = static_cast<unsigned>(M);
+  const long long* t = reinterpret_cast<const long long*>(target);
+#define AB200_CE_BWD(T, G)                                                                                          \
+  ce_backward_kernel<T, G><<<grid, kCeThreads, 0, stream>>>(static_cast<const T*>(logits), stride_m, stride_v, t, weight, \
+                                                          weight_dtype, lse, denominator, loss_grad, loss_grad_dtype, \
+                                                          static_cast<G*>(logits_grad), ld_grad, static_cast<int>(V))
+  if (dtype == DT_F32) AB200_CE_BWD(float, float);
+  else if (dtype == DT_F16 && grad_dtype == DT_F16) AB200_CE_BWD(__half, __half);
+  else if (dtype == DT_F16) AB200_CE_BWD(__half, float);
+  else if (grad_dtype == DT_BF16) AB200_CE_BWD(__nv_bfloat16, __nv_bfloat16);
+  else AB200_CE_BWD(__nv_bfloat16, float);
+#undef AB200_CE_BWD
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
 }
 
 uint32_t ab200_dropout_threshold(float drop_p, int flags) {

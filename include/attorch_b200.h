@@ -326,6 +326,40 @@ int ab200_cast_2d(const void* src, void* dst, int64_t rows, int64_t cols, int64_
                   int64_t src_stride_c, int src_dtype, int dst_dtype, void* stream);
 
 /*
+ * Cross-entropy loss of a logits matrix against class indices, the loss the final projection of a
+ * language model feeds.  Forward replaces cross_entropy_loss_forward_kernel
+ * (attorch/cross_entropy_loss_kernels.py:13-88, launched at attorch/cross_entropy_loss_layer.py:67-80)
+ * together with the sums and the division that follow it there (lines 75-79):
+ *     L = sum_i w[t_i] * (log sum_j exp(x_ij) - x_{i,t_i}) / (weight ? sum_i w[t_i] : M)
+ *   logits  [M, V] of `dtype`, element strides (stride_m, stride_v); evaluated in fp32
+ *   target  [M] int64 class indices in [0, V)
+ *   weight  [V] class weights of weight_dtype, or NULL
+ *   loss    one element of loss_dtype (the reference: fp32 under autocast, else the logits' type)
+ *   lse     [M] fp32, receives log-sum-exp of every row: backward then needs one exponential per
+ *           element instead of a second maximum / sum pass (the reference recomputes both)
+ *   workspace  ab200_cross_entropy_workspace_bytes(M) bytes; it must reach the backward call intact
+ *           (it holds the denominator of the mean)
+ * M = 0 gives a loss of 0.  Row sums are added in a fixed order.
+ */
+int ab200_cross_entropy_forward(const void* logits, const int64_t* target, const void* weight, void* loss,
+                                float* lse, int64_t M, int64_t V, int64_t stride_m, int64_t stride_v, int dtype,
+                                int weight_dtype, int loss_dtype, void* workspace, int64_t workspace_bytes,
+                                void* stream);
+
+int64_t ab200_cross_entropy_workspace_bytes(int64_t M);
+
+/*
+ * Its backward:  dx_ij = dL * s_i * (exp(x_ij - lse_i) - [j == t_i]),  s_i = w[t_i] / sum_i w[t_i]  or
+ * 1 / M.  Replaces cross_entropy_loss_backward_kernel (attorch/cross_entropy_loss_kernels.py:91-173,
+ * launched at attorch/cross_entropy_loss_layer.py:107-114).  loss_grad: one element of loss_grad_dtype
+ * (device memory); logits_grad: [M, V] of grad_dtype (the logits' type, or fp32), row pitch ld_grad.
+ */
+int ab200_cross_entropy_backward(const void* loss_grad, int loss_grad_dtype, const void* logits, const int64_t* target,
+                                 const void* weight, const float* lse, const void* workspace, void* logits_grad,
+                                 int64_t M, int64_t V, int64_t stride_m, int64_t stride_v, int64_t ld_grad, int dtype,
+                                 int weight_dtype, int grad_dtype, void* stream);
+
+/*
  * In-place SUM all-reduce of a gradient bucket over the GPUs of one NVSwitch domain (one process per
  * GPU), through NVLink multicast: the switch adds the ranks' copies (multimem.ld_reduce) and writes the
  * sums back to all of them (multimem.st); see csrc/allreduce_multimem.cu.  No counterpart in the

@@ -409,3 +409,44 @@ def glu_backward(dy: Tensor, x: Tensor, dim: int, act_func: str) -> Tensor:
     g1 = (dy * act_forward(name, z, param)).to(x.dtype)
     g2 = (dy * x1 * act_grad(name, z, param)).to(x.dtype)
     return torch.cat([g1, g2], dim=dim)
+
+
+def cross_entropy_forward(x: Tensor, target: Tensor, weight: Optional[Tensor] = None,
+                          autocast: bool = False) -> Tensor:
+    """
+    cross_entropy_loss_forward_kernel (attorch/cross_entropy_loss_kernels.py:56-88) and the host code
+    after it (attorch/cross_entropy_loss_layer.py:75-79): logits widened to fp32 (line 74), per row
+    log(sum(exp(x - max))) - x[target] + max, times the target's class weight if weights are given;
+    summed and divided by the batch size, or by the sum of the targets' weights.  Stored in fp32 under
+    autocast, else in the logits' dtype (get_output_dtype(..., autocast='fp32'), line 58).
+    """
+    xf = x.float()
+    mx = xf.max(dim=1).values
+    rows = torch.arange(len(x))
+    loss = torch.log(torch.exp(xf - mx[:, None]).sum(dim=1)) - xf[rows, target] + mx
+    if weight is not None:
+        w = weight.float()[target]
+        total = (loss * w).sum() / w.sum()
+    else:
+        total = (loss / len(x)).sum() if len(x) else loss.sum()
+    return total.to(torch.float32 if autocast else x.dtype)
+
+
+def cross_entropy_backward(output_grad: Tensor, x: Tensor, target: Tensor, weight: Optional[Tensor] = None,
+                           autocast: bool = False) -> Tensor:
+    """
+    cross_entropy_loss_backward_kernel (attorch/cross_entropy_loss_kernels.py:145-173):
+    dL * (softmax(x) - onehot(target)), times weight[target] / sum of the targets' weights, or divided
+    by the batch size; fp32 arithmetic, stored in the loss's dtype.
+    """
+    xf = x.float()
+    softmax = torch.softmax(xf, dim=1)
+    onehot = torch.zeros_like(xf)
+    onehot[torch.arange(len(x)), target] = 1.0
+    grad = output_grad.float() * (softmax - onehot)
+    if weight is not None:
+        w = weight.float()[target]
+        grad = grad * (w / w.sum())[:, None]
+    else:
+        grad = grad / len(x)
+    return grad.to(torch.float32 if autocast else x.dtype)

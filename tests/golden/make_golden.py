@@ -167,6 +167,7 @@ def main():
     act_layer_goldens(attorch)
     glu_goldens(attorch)
     elementwise_bf16_goldens(attorch)
+    cross_entropy_goldens(attorch)
 
 
 ACT_LAYERS = [('Sigmoid', {}), ('LogSigmoid', {}), ('Tanh', {}), ('ReLU', {}), ('GELU', {}),
@@ -291,6 +292,39 @@ def elementwise_bf16_goldens(attorch):
     data['skipped'] = np.array(','.join(skipped))
     np.savez_compressed(OUT_DIR / 'elementwise_bf16.npz', **data)
     print('wrote elementwise_bf16.npz; the interpreter could not run:', skipped)
+
+
+CROSS_ENTROPY_CASES = [(1, 8, False), (16, 10, False), (16, 10, True), (37, 50, True), (5, 1000, False),
+                       (64, 257, True)]
+
+
+def cross_entropy_goldens(attorch):
+    """
+    The reference's cross-entropy loss (attorch/cross_entropy_loss_layer.py) in fp32: logits scaled so
+    that rows have a wide range, targets drawn uniformly, with and without class weights; the loss and
+    the gradient of the logits for an upstream gradient of 1 (loss.backward()) and of 0.5.
+    """
+    from attorch.cross_entropy_loss_kernels import cross_entropy_loss_backward_kernel, \
+        cross_entropy_loss_forward_kernel
+    cross_entropy_loss_forward_kernel.configs = cross_entropy_loss_forward_kernel.configs[:1]
+    cross_entropy_loss_backward_kernel.configs = cross_entropy_loss_backward_kernel.configs[:1]
+    gen = torch.Generator().manual_seed(8)
+    data = {}
+    for case, (batch, classes, weighted) in enumerate(CROSS_ENTROPY_CASES):
+        x = torch.randn(batch, classes, generator=gen) * 3
+        target = torch.randint(0, classes, (batch,), generator=gen)
+        weight = torch.rand(classes, generator=gen) + 0.1 if weighted else None
+        data[f'x_{case}'], data[f'target_{case}'] = x.numpy(), target.numpy()
+        if weighted:
+            data[f'weight_{case}'] = weight.numpy()
+        for scale, label in ((1.0, 'unit'), (0.5, 'half')):
+            xin = x.clone().requires_grad_(True)
+            loss = attorch.CrossEntropyLoss(weight=weight)(xin, target)
+            (loss * scale).backward()
+            data[f'loss_{case}'] = loss.detach().numpy()
+            data[f'dx_{case}_{label}'] = xin.grad.numpy()
+    np.savez_compressed(OUT_DIR / 'cross_entropy_fp32.npz', **data)
+    print('wrote cross_entropy_fp32.npz')
 
 
 if __name__ == '__main__':

@@ -18,7 +18,7 @@ TOLERANCE = {torch.float32: 1e-2, torch.float16: 1e-2, torch.bfloat16: 1e-2}
 def golden_names(prefix: str = ''):
     """Names of the linear-layer golden cases (the activation-layer and GLU files have their own loaders)."""
     return sorted(p.stem for p in GOLDEN_DIR.glob(f'{prefix}*.npz')
-                  if not p.stem.startswith(('act_layers', 'glu_', 'elementwise_')))
+                  if not p.stem.startswith(('act_layers', 'glu_', 'elementwise_', 'cross_entropy_')))
 
 
 # (module name, constructor arguments, act_func string) in the order of tests/golden/make_golden.py.
