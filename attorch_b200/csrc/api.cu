@@ -676,7 +676,7 @@ int ab200_glu_backward(const void* dy, const void* x, void* dx, int64_t outer, i
   return launch_glu<true>(x, dy, dx, outer, inner, dtype, act, act_param, static_cast<cudaStream_t>(stream));
 }
 
-int64_t ab200_cross_entropy_workspace_bytes(int64_t M) { return M > 0 ? (2 * M + 1) * 4 : 4; }
+int64_t ab200_cross_entropy_workspace_bytes(int64_t M) { return M > 0 ? (4 * M + 1) * 4 : 4; }
 
 int ab200_cross_entropy_forward(const void* logits, const int64_t* target, const void* weight, void* loss,
                                 float* lse, int64_t M, int64_t V, int64_t stride_m, int64_t stride_v, int dtype,
@@ -688,22 +688,27 @@ int ab200_cross_entropy_forward(const void* logits, const int64_t* target, const
   if (!valid_dtype(dtype) || !valid_dtype(loss_dtype) || (weight && !valid_dtype(weight_dtype))) return ERR_BAD_DTYPE;
   if (!loss || !workspace || (M > 0 && (!logits || !target || !lse))) return ERR_NULL_POINTER;
   if (workspace_bytes < ab200_cross_entropy_workspace_bytes(M)) return ERR_WORKSPACE_TOO_SMALL;
+  // Workspace: per row the weighted loss, the weight, the maximum and log(sum exp(x - maximum)); then
+  // the denominator of the mean.
   float* row_loss = static_cast<float*>(workspace);
   float* row_weight = row_loss + M;
-  float* denominator = row_weight + M;
+  float* row_max = row_weight + M;
+  float* row_logsum = row_max + M;
+  float* denominator = row_logsum + M;
   if (M > 0) {
     const unsigned grid = static_cast<unsigned>(M);
     const long long* t = reinterpret_cast<const long long*>(target);
     if (dtype == DT_F32)
       ce_forward_kernel<float><<<grid, kCeThreads, 0, stream>>>(static_cast<const float*>(logits), stride_m, stride_v, t,
-                                                             weight, weight_dtype, row_loss, row_weight, lse, static_cast<int>(V));
+                                                             weight, weight_dtype, row_loss, row_weight, row_max, row_logsum, lse, static_cast<int>(V));
     else if (dtype == DT_F16)
       ce_forward_kernel<__half><<<grid, kCeThreads, 0, stream>>>(static_cast<const __half*>(logits), stride_m, stride_v, t,
-                                                              weight, weight_dtype, row_loss, row_weight, lse, static_cast<int>(V));
+                                                              weight, weight_dtype, row_loss, row_weight, row_max, row_logsum, lse, static_cast<int>(V));
     else
       ce_forward_kernel<__nv_bfloat16><<<grid, kCeThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), stride_m,
                                                                      stride_v, t, weight, weight_dtype, row_loss,
-                                                                     row_weight, lse, static_cast<int>(V));
+                                                                     row_weight, row_max, row_logsum, lse,
+                                                                     static_cast<int>(V));
     ++g_launches;
     if (cudaGetLastError() != cudaSuccess) return ERR_LAUNCH;
   }
@@ -727,12 +732,15 @@ int ab200_cross_entropy_backward(const void* loss_grad, int loss_grad_dtype, con
   if (M == 0) return OK;
   if (!loss_grad || !logits || !target || !lse || !workspace || !logits_grad) return ERR_NULL_POINTER;
   if (ld_grad < V) return ERR_BAD_STRIDE;
-  const float* denominator = static_cast<const float*>(workspace) + 2 * M;
+  const float* row_max = static_cast<const float*>(workspace) + 2 * M;
+  const float* row_logsum = row_max + M;
+  const float* denominator = row_logsum + M;
   const unsigned grid = static_cast<unsigned>(M);
   const long long* t = reinterpret_cast<const long long*>(target);
 #define AB200_CE_BWD(T, G)                                                                                          \
   ce_backward_kernel<T, G><<<grid, kCeThreads, 0, stream>>>(static_cast<const T*>(logits), stride_m, stride_v, t, weight, \
-                                                          weight_dtype, lse, denominator, loss_grad, loss_grad_dtype, \
+                                                          weight_dtype, row_max, row_logsum, denominator, loss_grad,  \
+                                                          loss_grad_dtype,                                           \
                                                           static_cast<G*>(logits_grad), ld_grad, static_cast<int>(V))
   if (dtype == DT_F32) AB200_CE_BWD(float, float);
   else if (dtype == DT_F16 && grad_dtype == DT_F16) AB200_CE_BWD(__half, __half);

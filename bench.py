@@ -1,7 +1,7 @@
 """
 Benchmark of the fused linear layer (forward + backward) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|act] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|act|ce] [--impl reference]
 
 For N > 1 launch one rank per GPU with torchrun (RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the
 environment).  Rank 0 prints one JSON line, last.
@@ -16,6 +16,7 @@ Workloads (synthetic, seeded; shapes of the reference configurations this path i
   c4  skinny forward only, fp16, 8192 -> 28672, M in {1, 8, 32, 128}: prints weight-read GB/s.
   act standalone activation layer (GELU, drop_p = 0.1, bf16, 32768 x 4096 elements) and gated linear
       unit (silu, bf16, 16384 x 2*14336): GB/s.
+  ce  cross-entropy loss of bf16 logits [8192, 50304], forward and backward: GB/s.
 
 One "step" is one forward + backward of the workload on one batch.  ``value`` is the whole-job
 TFLOP/s at 6 * M * K * N floating-point operations per layer and step with the inputs resident in
@@ -505,6 +506,60 @@ def activation_layer(args, device):
           flush=True)
 
 
+def cross_entropy_loss(args, device):
+    """
+    The loss after the final projection: mean cross-entropy of bf16 logits [8192 tokens, 50304 classes]
+    (824 MB, larger than L2) against int64 targets, forward and backward, through the C ABI and through
+    attorch_b200.CrossEntropyLoss.  HBM-bound: forward reads the logits once (n e bytes), backward reads
+    them and writes the gradient (2 n e).
+    """
+    import attorch_b200
+    from attorch_b200 import _lib
+    lib = _lib.load()
+    peaks, peak_source = measured_peaks()
+    rows, classes = 8192, 50304
+    n = rows * classes
+    x = (torch.randn(rows, classes, device=device) * 2).bfloat16()
+    target = torch.randint(0, classes, (rows,), device=device)
+    dx = torch.empty_like(x)
+    loss = torch.empty((), dtype=torch.bfloat16, device=device)
+    dloss = torch.ones((), dtype=torch.bfloat16, device=device)
+    lse = torch.empty(rows, dtype=torch.float32, device=device)
+    ws = torch.empty(lib.ab200_cross_entropy_workspace_bytes(rows), dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def forward():
+        _lib.check(lib.ab200_cross_entropy_forward(x.data_ptr(), target.data_ptr(), None, loss.data_ptr(), lse.data_ptr(),
+                                                   rows, classes, classes, 1, _lib.BF16, 0, _lib.BF16, ws.data_ptr(),
+                                                   ws.numel(), stream), 'ab200_cross_entropy_forward')
+
+    def backward():
+        _lib.check(lib.ab200_cross_entropy_backward(dloss.data_ptr(), _lib.BF16, x.data_ptr(), target.data_ptr(), None,
+                                                    lse.data_ptr(), ws.data_ptr(), dx.data_ptr(), rows, classes, classes,
+                                                    1, classes, _lib.BF16, 0, _lib.BF16, stream),
+                   'ab200_cross_entropy_backward')
+
+    layer = attorch_b200.CrossEntropyLoss()
+    xg = x.clone().requires_grad_(True)
+
+    def module_step():
+        layer(xg, target).backward()
+        xg.grad = None
+
+    results = {}
+    for name, fn, nbytes in (('kernel_forward', forward, n * 2.0), ('kernel_backward', backward, 2 * n * 2.0),
+                             ('module_forward_backward', module_step, 3 * n * 2.0)):
+        ms = event_time(fn, args.steps, max(args.warmup, 3))
+        results[name] = {'us': round(ms * 1e3, 2), 'gbs': round(nbytes / (ms * 1e-3) / 1e9, 1)}
+    best = results['kernel_forward']['gbs']
+    print(json.dumps({'metric': 'cross_entropy_gbs', 'value': best, 'unit': 'GB/s', 'n_gpus': 1, 'steps': args.steps,
+                      'warmup': args.warmup, 'higher_is_better': True, 'dtype': 'bf16', 'data': 'synthetic',
+                      'config': {'workload': 'ce', 'shape': [rows, classes], 'l2': 'inputs larger than L2', **results},
+                      'roofline': {'bound': 'hbm', 'achieved': best, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
+                                   'frac': best / peaks['hbm_gbs'], 'traffic': None, 'peak_source': peak_source}}),
+          flush=True)
+
+
 class Comm:
     """Rank, world size and the two collectives the timing protocol needs."""
     def __init__(self, device, world_size, rank):
@@ -925,7 +980,7 @@ def main():
     parser.add_argument('--gpus', type=int, default=1)
     parser.add_argument('--steps', type=int, default=200)
     parser.add_argument('--warmup', type=int, default=10)
-    parser.add_argument('--workload', choices=sorted(WORKLOADS) + ['c4', 'act'], default='c2')
+    parser.add_argument('--workload', choices=sorted(WORKLOADS) + ['c4', 'act', 'ce'], default='c2')
     parser.add_argument('--only', default=None,
                         help='workload act: time just this entry (e.g. kernel_forward, glu_backward)')
     parser.add_argument('--impl', choices=['b200', 'reference'], default='b200')
@@ -940,7 +995,7 @@ def main():
                         help='override the tokens per GPU (profiling of reduced cases)')
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.workload in ('c4', 'act'):
+    if args.workload in ('c4', 'act', 'ce'):
         if args.impl == 'reference':
             print(json.dumps({'impl': 'reference', 'unavailable': f'{args.workload} has no CPU arm; use c2'}))
             return
@@ -948,6 +1003,8 @@ def main():
         torch.cuda.set_device(0)
         if args.workload == 'c4':
             print(json.dumps(skinny_forward(args.steps, args.warmup, torch.device('cuda', 0), _lib.load())), flush=True)
+        elif args.workload == 'ce':
+            cross_entropy_loss(args, torch.device('cuda', 0))
         else:
             activation_layer(args, torch.device('cuda', 0))
         return

@@ -335,10 +335,11 @@ int ab200_cast_2d(const void* src, void* dst, int64_t rows, int64_t cols, int64_
  *   target  [M] int64 class indices in [0, V)
  *   weight  [V] class weights of weight_dtype, or NULL
  *   loss    one element of loss_dtype (the reference: fp32 under autocast, else the logits' type)
- *   lse     [M] fp32, receives log-sum-exp of every row: backward then needs one exponential per
- *           element instead of a second maximum / sum pass (the reference recomputes both)
- *   workspace  ab200_cross_entropy_workspace_bytes(M) bytes; it must reach the backward call intact
- *           (it holds the denominator of the mean)
+ *   lse     [M] fp32, receives log-sum-exp of every row (for callers that want it)
+ *   workspace  ab200_cross_entropy_workspace_bytes(M) bytes; it must reach the backward call intact:
+ *           it holds every row's maximum and log(sum exp(x - maximum)), with which backward needs
+ *           one exponential per element instead of a second maximum / sum pass (the reference
+ *           recomputes both), and the denominator of the mean
  * M = 0 gives a loss of 0.  Row sums are added in a fixed order.
  */
 int ab200_cross_entropy_forward(const void* logits, const int64_t* target, const void* weight, void* loss,
@@ -349,7 +350,7 @@ int ab200_cross_entropy_forward(const void* logits, const int64_t* target, const
 int64_t ab200_cross_entropy_workspace_bytes(int64_t M);
 
 /*
- * Its backward:  dx_ij = dL * s_i * (exp(x_ij - lse_i) - [j == t_i]),  s_i = w[t_i] / sum_i w[t_i]  or
+ * Its backward:  dx_ij = dL * s_i * (softmax(x_i)_j - [j == t_i]),  s_i = w[t_i] / sum_i w[t_i]  or
  * 1 / M.  Replaces cross_entropy_loss_backward_kernel (attorch/cross_entropy_loss_kernels.py:91-173,
  * launched at attorch/cross_entropy_loss_layer.py:107-114).  loss_grad: one element of loss_grad_dtype
  * (device memory); logits_grad: [M, V] of grad_dtype (the logits' type, or fp32), row pitch ld_grad.

@@ -161,7 +161,7 @@ def test_gradients_against_an_independent_expectation(family, flags, save_deriva
     x = torch.randn(M, K, generator=gen).bfloat16()
     w = (torch.randn(K, N, generator=gen) / K ** 0.5).bfloat16()
     b = torch.randn(N, generator=gen).bfloat16()
-    dy = torch.randn(M, N, generator=gen).bfloat16()
+    dy = (torch.randn(M, N, generator=gen) * 0.25).bfloat16()
     layer = layer_from(w, b, act_func, torch.bfloat16)
     previous_flags = attorch_b200.set_gemm_flags(flags)
     previous_mode = attorch_b200.set_save_derivative(save_derivative)
