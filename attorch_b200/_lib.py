@@ -25,8 +25,10 @@ FLAG_NO_TMA_STORE = 32
 FLAG_SAVE_DERIVATIVE = 64
 FLAG_WHOLE_TILES = 128
 FLAG_DROPOUT_PACKED = 256
+FLAG_DERIVATIVE_FP16 = 512
 FLAG_RESERVE_SMS_SHIFT = 16   # bits 16-23: SMs a GEMM call leaves free
 ACT_SAVED_DERIVATIVE = 22
+ACT_SAVED_DERIVATIVE_F16 = 23
 
 PATH_TCGEN05, PATH_STREAMK, PATH_GENERIC = 1, 2, 3
 

@@ -37,7 +37,9 @@ enum Act : int {
   ACT_COUNT = 22,
   // Backward only: the saved tensor already holds act'(Z) (written by a forward pass that was asked
   // to save the derivative), so dZ = dY * saved.
-  ACT_SAVED_DERIVATIVE = 22
+  ACT_SAVED_DERIVATIVE = 22,
+  // Same, with the saved act'(Z) stored as fp16 whatever the type of dY and dZ (2-byte types only).
+  ACT_SAVED_DERIVATIVE_F16 = 23
 };
 
 namespace actm {
@@ -263,7 +265,7 @@ __device__ __forceinline__ void act_fwd_grad(float (&v)[N], const float (&zr)[N]
 template <int N>
 __device__ __forceinline__ void act_grad_mul(float (&g)[N], const float (&z)[N], int act, float p) {
   if (act == ACT_NONE) return;
-  if (act == ACT_SAVED_DERIVATIVE) {
+  if (act == ACT_SAVED_DERIVATIVE || act == ACT_SAVED_DERIVATIVE_F16) {
 #pragma unroll
     for (int i = 0; i < N; ++i) g[i] *= z[i];
     return;

@@ -29,7 +29,7 @@ int launch_hybrid_finish(const GemmArgs& g, int first_tile, int count, int worke
   a.bias = g.bias; a.bias_dtype = g.bias_dtype;
   a.aux = g.aux; a.ld_aux = g.ld_aux;
   a.out = g.out; a.ld_out = g.ld_out; a.out_dtype = g.out_dtype;
-  a.act = g.act; a.act_param = g.act_param; a.save_grad = g.save_grad;
+  a.act = g.act; a.act_param = g.act_param; a.save_grad = g.save_grad; a.grad_dtype = g.grad_dtype;
   a.residual = g.residual; a.ld_res = g.ld_res;
   // 16 blocks per tile: enough parallelism for a handful of tiles.
   hybrid_finish_kernel<<<dim3(count, 16), 256, 0, stream>>>(a);
@@ -43,7 +43,7 @@ std::atomic<int64_t> g_launches{0};   // all host threads: backward runs on auto
 
 bool valid_dtype(int dt) { return dt == DT_F32 || dt == DT_F16 || dt == DT_BF16; }
 bool valid_act(int act) { return act >= 0 && act < ACT_COUNT; }
-bool valid_backward_act(int act) { return valid_act(act) || act == ACT_SAVED_DERIVATIVE; }
+bool valid_backward_act(int act) { return valid_act(act) || act == ACT_SAVED_DERIVATIVE || act == ACT_SAVED_DERIVATIVE_F16; }
 
 // Can TMA address this matrix: unit inner stride, 16-byte aligned base and row pitch?
 bool tma_ok(const void* p, long long pitch_elems, long long unit_stride, int elt) {
@@ -108,7 +108,7 @@ int launch_finish(float* partial, const GemmArgs& e, long long M, long long N, c
   if (blocks > cap) blocks = cap;
   streamk_finish_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
       partial, N, static_cast<int>(M), static_cast<int>(N), e.bias, e.bias_dtype, e.aux, e.ld_aux, e.out,
-      e.ld_out, e.out_dtype, e.act, e.act_param, e.save_grad, e.residual, e.ld_res);
+      e.ld_out, e.out_dtype, e.act, e.act_param, e.save_grad, e.grad_dtype, e.residual, e.ld_res);
   ++g_launches;
   return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
 }
@@ -249,6 +249,10 @@ int ab200_linear_forward_residual(const void* x, const void* w, const void* bias
   if (!out || (K > 0 && (!x || !w))) return ERR_NULL_POINTER;
   if (ld_out < N || (pre_act && ld_pre < N)) return ERR_BAD_STRIDE;
   const int save_grad = (flags & AB200_FLAG_SAVE_DERIVATIVE) && act != ACT_NONE ? 1 : 0;
+  // The saved derivative of a bf16 layer may be stored as fp16 (same size, three more mantissa bits;
+  // activation derivatives are of order one, far inside fp16's range): the product dY * act'(Z) then
+  // differs from one formed with the unrounded derivative by 1 part in 4000 instead of 1 in 500.
+  const int grad_dtype = (save_grad && out_dtype == DT_BF16 && (flags & AB200_FLAG_DERIVATIVE_FP16)) ? DT_F16 : out_dtype;
 
   const int elt = dtype_size(op_dtype);
   const bool tc_ok = K > 0 && tma_ok(x, x_stride_m, x_stride_k, elt) && tma_ok(w, w_stride_k, w_stride_n, elt) &&
@@ -266,6 +270,7 @@ int ab200_linear_forward_residual(const void* x, const void* w, const void* bias
     a.bias = bias; a.bias_dtype = bias_dtype;
     a.act = act; a.act_param = act_param;
     a.save_grad = save_grad;
+    a.grad_dtype = grad_dtype;
     a.residual = residual; a.ld_res = ld_res;
     g_last_path = AB200_PATH_GENERIC;
     return launch_any(a, stream);
@@ -299,6 +304,7 @@ int ab200_linear_forward_residual(const void* x, const void* w, const void* bias
     e.bias = bias; e.bias_dtype = bias_dtype; e.aux = pre_act; e.ld_aux = ld_pre;
     e.out = out; e.ld_out = ld_out; e.out_dtype = out_dtype; e.act = act; e.act_param = act_param;
     e.save_grad = save_grad;
+    e.grad_dtype = grad_dtype;
     e.residual = residual; e.ld_res = ld_res;
     return launch_finish(static_cast<float*>(workspace), e, M, N, stream);
   }
@@ -311,6 +317,7 @@ int ab200_linear_forward_residual(const void* x, const void* w, const void* bias
   g.bias = bias; g.bias_dtype = bias_dtype;
   g.act = act; g.act_param = act_param;
   g.save_grad = save_grad;
+  g.grad_dtype = grad_dtype;
   g.residual = residual; g.ld_res = ld_res;
   return run_tiles_or_split(p, workspace, workspace_bytes, stream, flags);
 }

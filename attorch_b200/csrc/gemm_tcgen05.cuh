@@ -71,6 +71,7 @@ struct GemmArgs {
   int partial_transposed;
   int* status;            // device word; a bounded wait that runs out stores a DeviceStatus here
   int save_grad;          // aux receives act'(Z) instead of Z (see actm::fwd_grad)
+  int grad_dtype;         // element type act'(Z) is stored in (2 bytes if out_dtype is; see api.cu)
   int tma_store;          // bit 0: `out` goes through shared memory and a TMA store; bit 1: `aux` too
 };
 
@@ -611,12 +612,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int row0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32;   // chunk's first row
           // Writes one 32 x 32 chunk of an output: through the warp's staging buffer and a TMA
           // store, or straight from registers where TMA cannot address the output.
-          auto emit = [&](const CUtensorMap* map, void* base, long long ld, bool by_tma, const float (&w)[32]) {
+          auto emit = [&](const CUtensorMap* map, void* base, long long ld, bool by_tma, const float (&w)[32], int dt) {
             if (by_tma) {
               // One staging buffer per warp: the previous store must have read it out first.
               if (lane == 0) ptx::tma_store_wait_read();
               __syncwarp();
-              stage_row_chunk(stage_buf, lane, args.out_dtype, w);
+              stage_row_chunk(stage_buf, lane, dt, w);
               ptx::fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0 && row0 < args.M) {
@@ -624,7 +625,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 ptx::tma_store_commit();
               }
             } else if (row_ok) {
-              store_row_chunk(base, args.out_dtype, static_cast<long long>(row) * ld + col0, w, valid);
+              store_row_chunk(base, dt, static_cast<long long>(row) * ld + col0, w, valid);
             }
           };
           if (args.aux != nullptr && args.save_grad) {
@@ -633,14 +634,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
             for (int i = 0; i < 32; ++i) zr[i] = round_through(v[i], args.out_dtype);
             act_fwd_grad(v, zr, g, args.act, args.act_param);
-            emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, g);
+            emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, g, args.grad_dtype);
           } else {
-            if (args.aux != nullptr) emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, v);
+            if (args.aux != nullptr) emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, v, args.out_dtype);
             act_fwd_inplace(v, args.act, args.act_param);
           }
           if (args.residual != nullptr && row_ok)
             add_residual_chunk(v, args.residual, args.out_dtype, static_cast<long long>(row) * args.ld_res + col0, valid);
-          emit(&tmap_out, args.out, args.ld_out, (args.tma_store & 1) != 0, v);
+          emit(&tmap_out, args.out, args.ld_out, (args.tma_store & 1) != 0, v, args.out_dtype);
         }
       }
       // This warp has read its share of the accumulator: tell the (leader's) MMA issuer.

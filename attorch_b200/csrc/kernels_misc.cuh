@@ -45,6 +45,8 @@ act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restri
   float sum[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
+  // The saved derivative of a bf16 layer may have been stored as fp16 (same size): see api.cu.
+  const bool z_is_half = sizeof(T) == 2 && act == ACT_SAVED_DERIVATIVE_F16;
 
   if (col0 < N) {
     for (int r0 = row_begin + rl; r0 < row_end; r0 += kRowLanes * kUnroll) {
@@ -68,7 +70,10 @@ act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restri
           for (int i = 0; i < 8; ++i) {
             const bool in = col0 + i < N;
             g[u][i] = in ? to_f32<T>(dy[r * ld_dy + col0 + i]) : 0.0f;
-            zz[u][i] = (in && z != nullptr) ? to_f32<T>(z[r * ld_z + col0 + i]) : 0.0f;
+            if (z_is_half)
+              zz[u][i] = in ? __half2float(reinterpret_cast<const __half*>(z)[r * ld_z + col0 + i]) : 0.0f;
+            else
+              zz[u][i] = (in && z != nullptr) ? to_f32<T>(z[r * ld_z + col0 + i]) : 0.0f;
           }
         }
       }
@@ -82,7 +87,8 @@ act_backward_kernel(const T* __restrict__ dy, long long ld_dy, const T* __restri
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             g[u][i] = to_f32<T>(ge[i]);
-            zz[u][i] = (z != nullptr) ? to_f32<T>(ze[i]) : 0.0f;
+            if (z_is_half) zz[u][i] = __half2float(reinterpret_cast<const __half*>(zq[u])[i]);
+            else zz[u][i] = (z != nullptr) ? to_f32<T>(ze[i]) : 0.0f;
           }
         }
         alignas(16) T o[8];
@@ -177,7 +183,7 @@ colsum_finish_kernel(const float* __restrict__ partial, int chunks, int N, void*
 __global__ void streamk_finish_kernel(float* __restrict__ partial, long long ld_partial, int M, int N,
                                       const void* bias, int bias_dtype, void* aux, long long ld_aux,
                                       void* out, long long ld_out, int out_dtype, int act,
-                                      float act_param, int save_grad, const void* residual,
+                                      float act_param, int save_grad, int grad_dtype, const void* residual,
                                       long long ld_res) {
   // Four consecutive columns per thread where the row pitch allows 16-byte accesses.
   const bool vec = (N % 4 == 0) && (ld_partial % 4 == 0);
@@ -205,7 +211,7 @@ __global__ void streamk_finish_kernel(float* __restrict__ partial, long long ld_
       if (aux != nullptr && save_grad) {
         float zr[1] = {round_through(v[0], out_dtype)}, g[1];
         act_fwd_grad(v, zr, g, act, act_param);
-        store_from_f32(aux, out_dtype, m * ld_aux + n, g[0]);
+        store_from_f32(aux, grad_dtype, m * ld_aux + n, g[0]);
       } else {
         if (aux != nullptr) store_from_f32(aux, out_dtype, m * ld_aux + n, v[0]);
         act_fwd_inplace(v, act, act_param);
@@ -230,7 +236,7 @@ struct HybridFinishArgs {
   const void* bias; int bias_dtype;
   void* aux; long long ld_aux;
   void* out; long long ld_out; int out_dtype;
-  int act; float act_param; int save_grad;
+  int act; float act_param; int save_grad; int grad_dtype;
   const void* residual; long long ld_res;
 };
 
@@ -281,7 +287,7 @@ __global__ void __launch_bounds__(256) hybrid_finish_kernel(const HybridFinishAr
       if (a.aux != nullptr && a.save_grad) {
         float zr[1] = {round_through(v[0], a.out_dtype)}, g[1];
         act_fwd_grad(v, zr, g, a.act, a.act_param);
-        store_from_f32(a.aux, a.out_dtype, m * a.ld_aux + n, g[0]);
+        store_from_f32(a.aux, a.grad_dtype, m * a.ld_aux + n, g[0]);
       } else {
         if (a.aux != nullptr) store_from_f32(a.aux, a.out_dtype, m * a.ld_aux + n, v[0]);
         act_fwd_inplace(v, a.act, a.act_param);
@@ -369,6 +375,7 @@ struct AnyGemmArgs {
   const void* bias; int bias_dtype;
   int act; float act_param;
   int save_grad;          // aux receives act'(Z) instead of Z
+  int grad_dtype;         // ... stored in this element type
   const void* residual; long long ld_res;   // optional [M, N] in the output dtype, added after the activation
 };
 
@@ -437,7 +444,7 @@ __global__ void __launch_bounds__(256) gemm_any_kernel(const AnyGemmArgs g) {
       if (g.aux != nullptr && g.save_grad) {
         float zr[1] = {round_through(v[0], g.out_dtype)}, d[1];
         act_fwd_grad(v, zr, d, g.act, g.act_param);
-        store_from_f32(g.aux, g.out_dtype, m * g.ld_aux + n, d[0]);
+        store_from_f32(g.aux, g.grad_dtype, m * g.ld_aux + n, d[0]);
       } else {
         if (g.aux != nullptr) store_from_f32(g.aux, g.out_dtype, m * g.ld_aux + n, v[0]);
         act_fwd_inplace(v, g.act, g.act_param);

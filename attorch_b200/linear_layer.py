@@ -235,7 +235,12 @@ class LinearAutoGrad(torch.autograd.Function):
 
             saves_derivative = save_pre_act and _save_derivative
             output = torch.empty((batch_dim, out_feat_dim), device=input.device, dtype=output_dtype)
-            pre_act = torch.empty_like(output) if save_pre_act else None
+            # A bf16 layer keeps act'(Z) as fp16: same size, three more mantissa bits, so that
+            # dZ = dY * act'(Z) is in effect rounded once, as the reference's dZ is.
+            derivative_fp16 = saves_derivative and output_dtype is torch.bfloat16
+            pre_act = (torch.empty((batch_dim, out_feat_dim), device=input.device,
+                                   dtype=torch.float16 if derivative_fp16 else output_dtype)
+                       if save_pre_act else None)
 
             ws_bytes = _cached_size('ab200_forward_workspace_bytes', batch_dim, in_feat_dim, out_feat_dim, _gemm_flags)
             workspace = _workspace(input.device, ws_bytes) if ws_bytes else None
@@ -265,7 +270,8 @@ class LinearAutoGrad(torch.autograd.Function):
                 _dtype_id(bias_op.dtype) if bias_op is not None else 0,
                 act_id(name), 0.0 if param is None else param,
                 _ptr(workspace), ws_bytes, _ptr(scratch['status']), stream,
-                _flags_for(input.device) | (_lib.FLAG_SAVE_DERIVATIVE if saves_derivative else 0)),
+                _flags_for(input.device) | (_lib.FLAG_SAVE_DERIVATIVE if saves_derivative else 0) |
+                (_lib.FLAG_DERIVATIVE_FP16 if derivative_fp16 else 0)),
                 'ab200_linear_forward_residual')
 
         ctx.residual_requires_grad = residual is not None and residual.requires_grad
@@ -341,7 +347,8 @@ class LinearAutoGrad(torch.autograd.Function):
                     pre_act.stride(0) if pre_act is not None else out_feat_dim,
                     pre_act_grad.stride(0), _dtype_id(op_dtype),
                     _dtype_id(bias_grad.dtype) if need_db else 0,
-                    _lib.ACT_SAVED_DERIVATIVE if ctx.saved_derivative else act_id(ctx.act_func),
+                    (_lib.ACT_SAVED_DERIVATIVE_F16 if pre_act.dtype is not op_dtype else _lib.ACT_SAVED_DERIVATIVE)
+                    if ctx.saved_derivative else act_id(ctx.act_func),
                     0.0 if ctx.param is None else ctx.param,
                     _ptr(workspace), ws_bytes, stream), 'ab200_act_backward')
 

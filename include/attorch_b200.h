@@ -82,6 +82,9 @@ extern "C" {
 /* ab200_act_backward only: `z` already holds act'(Z), written by a forward call that had
  * AB200_FLAG_SAVE_DERIVATIVE set; dZ = dY * z. */
 #define AB200_ACT_SAVED_DERIVATIVE 22
+/* Same, for a forward call that also had AB200_FLAG_DERIVATIVE_FP16 set: `z` holds act'(Z) as fp16
+ * whatever `dtype` is (2-byte types only). */
+#define AB200_ACT_SAVED_DERIVATIVE_F16 23
 
 /* Flags (bit set) accepted by the GEMM entry points. */
 #define AB200_FLAG_FORCE_GENERIC 1  /* use the any-shape CUDA-core kernel                      */
@@ -93,6 +96,9 @@ extern "C" {
 #define AB200_FLAG_SAVE_DERIVATIVE 64 /* forward: pre_act receives act'(Z) instead of Z            */
 #define AB200_FLAG_WHOLE_TILES 128  /* never share out or halve a partial last round of tiles   */
 #define AB200_FLAG_DROPOUT_PACKED 256 /* activation layers: the cheaper dropout stream (see below) */
+#define AB200_FLAG_DERIVATIVE_FP16 512 /* forward with SAVE_DERIVATIVE and a bf16 output: act'(Z) is stored
+                                        * as fp16 (same size, 3 more mantissa bits; derivatives are O(1)), so
+                                        * that dZ = dY * act'(Z) is in effect rounded once, as the reference's */
 /* Bits 16-23 of the flags of a GEMM entry point: the number of SMs (0-255) the persistent kernel of
  * that call leaves free, for a collective that runs beside it (same purpose as
  * ab200_set_gemm_cta_limit, but per call instead of process-wide). */

@@ -264,7 +264,9 @@ def linear_backward(output_grad: Tensor, x: Tensor, pre_act: Optional[Tensor], w
     if name is None:
         dz = dy
     elif stored_derivative is not None:
-        dz = (dy.float() * stored_derivative.flatten(0, -2).float()).to(stored_derivative.dtype)
+        # Stored in dY's dtype: the saved derivative itself may be kept in another 2-byte type (fp16 for
+        # a bf16 layer), the product is rounded to the layer's own.
+        dz = (dy.float() * stored_derivative.flatten(0, -2).float()).to(dy.dtype)
     else:
         z = pre_act.float() if (name in FP32_ACTS or derivative_in_fp32) else pre_act
         grad = act_grad(name, z, param)

@@ -56,6 +56,8 @@ def test_header_constants_match_python():
     assert int(defines['AB200_FLAG_SAVE_DERIVATIVE']) == _lib.FLAG_SAVE_DERIVATIVE
     assert int(defines['AB200_FLAG_WHOLE_TILES']) == _lib.FLAG_WHOLE_TILES
     assert int(defines['AB200_FLAG_DROPOUT_PACKED']) == _lib.FLAG_DROPOUT_PACKED
+    assert int(defines['AB200_FLAG_DERIVATIVE_FP16']) == _lib.FLAG_DERIVATIVE_FP16
+    assert int(defines['AB200_ACT_SAVED_DERIVATIVE_F16']) == _lib.ACT_SAVED_DERIVATIVE_F16
     assert int(defines['AB200_ACT_SAVED_DERIVATIVE']) == _lib.ACT_SAVED_DERIVATIVE
 
 
