@@ -119,6 +119,36 @@ def _step_worker(rank, world_size, port, transport, exchange_dtype):
         dist.destroy_process_group()
 
 
+def test_collective_wait_runs_out_and_reports():
+    """
+    The bounded wait of the all-reduce kernel, on one GPU: launched as rank 0 of 2 with a flag block for
+    "rank 1" that nothing ever signals, its first cross-rank barrier gives up after the 2 s limit, the
+    kernel skips the data phase (no multicast address is ever touched) and returns; the status word then
+    holds AB200_DEV_TIMEOUT_COLLECTIVE and the device keeps working.
+    """
+    import time
+    from attorch_b200 import _lib
+    lib = _lib.load()
+    device = torch.device('cuda', 0)
+    words = lib.ab200_collective_flag_bytes() // 4
+    flags = [torch.zeros(words, dtype=torch.int32, device=device) for _ in range(2)]
+    blocks = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=device)
+    data = torch.ones(4096, dtype=torch.bfloat16, device=device)     # stands in for the bucket; never accessed
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    rc = lib.ab200_multimem_all_reduce(data.data_ptr(), data.numel(), _lib.BF16, 0, 2, blocks.data_ptr(), 2,
+                                       status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    assert int(status.item()) == 4                                   # AB200_DEV_TIMEOUT_COLLECTIVE
+    assert _lib.error_string(4).startswith('device: all-reduce gave up')
+    assert 1.5 < elapsed < 10.0
+    assert torch.all(data == 1)                                      # the data phase was skipped
+    assert float((torch.ones(8, device=device) * 2).sum()) == 16.0   # the context is still usable
+
+
 def _spawn(fn, *args):
     if torch.cuda.device_count() < 2:
         pytest.skip('needs two GPUs')
