@@ -17,7 +17,7 @@ A plain torch-on-CPU restatement of what the reference's ``attorch.Linear`` comp
 Parity pinned: tests/test_oracle.py checks this file against golden vectors produced by the
 reference itself (its Triton kernels run by the Triton CPU interpreter; generator
 tests/golden/make_golden.py) for fp32 and fp16, all 22 activation settings, the piecewise
-switch points, strided 3-D inputs, and BASELINE.json config 1.  bf16 has no reference-made vectors
+switch points, strided 3-D inputs, and the smallest configuration (fp32, 64 x 128 -> 256, bias, relu).  bf16 has no reference-made vectors
 (the interpreter's bf16 dot product is broken); the bf16 rules are the fp16 rules with the
 other 16-bit type, and on GPU boxes that have the reference the GPU tests compare against it.
 """

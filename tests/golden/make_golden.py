@@ -94,7 +94,7 @@ def save(name, store_inputs, x, w, b, dy, outs, **meta):
 
 
 def config1_inputs():
-    """BASELINE.json config 1: fp32, X [64, 128], 128 -> 256, bias, relu, every draw under seed 0."""
+    """The smallest configuration: fp32, X [64, 128], 128 -> 256, bias, relu, every draw under seed 0."""
     torch.manual_seed(0)
     x = torch.randn(64, 128)
     torch.manual_seed(0)

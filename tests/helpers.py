@@ -39,7 +39,7 @@ def load_act_layer_golden():
 
 
 def config1_inputs():
-    """BASELINE.json config 1 inputs, regenerated as tests/golden/make_golden.py makes them."""
+    """The smallest configuration (fp32, 64 x 128 -> 256, bias, relu) inputs, regenerated as tests/golden/make_golden.py makes them."""
     torch.manual_seed(0)
     x = torch.randn(64, 128)
     torch.manual_seed(0)

@@ -352,11 +352,11 @@ def test_bitwise_repeatable():
 
 
 # ------------------------------------------------------------------------------------------------
-# 4. Full-size BASELINE.json configurations, checked through sub-sampled oracle products
+# 4. Full-size benchmark configurations, checked through sub-sampled oracle products
 # ------------------------------------------------------------------------------------------------
 def test_config2_full_size_bf16():
     """
-    BASELINE.json config 2 (bf16, M = 8192, 4096 -> 4096, gelu, bias).  The oracle is evaluated on 48
+    The headline configuration (bf16, M = 8192, 4096 -> 4096, gelu, bias).  The oracle is evaluated on 48
     sampled rows (output, dX) and 48 sampled input features (dW); db in full.
     """
     torch.manual_seed(0)
@@ -392,7 +392,7 @@ def test_config2_full_size_bf16():
 
 @pytest.mark.parametrize('m', [1, 8, 32, 128])
 def test_config4_skinny_fp16(m):
-    """BASELINE.json config 4 at reduced N (fp16, forward only, K = 8192): the swap-AB stream-K kernel."""
+    """The skinny forward-only configuration at reduced N (fp16, forward only, K = 8192): the swap-AB stream-K kernel."""
     gen = torch.Generator().manual_seed(m)
     K, N = 8192, 4096
     x = torch.randn(m, K, generator=gen).half()
@@ -410,7 +410,7 @@ def test_config4_skinny_fp16(m):
 @pytest.mark.parametrize('m', [1, 8, 32, 100, 128])
 def test_config4_full_width_fp16(m, act_func):
     """
-    BASELINE.json config 4 at its full output width (N = 28672) and reduced K: from 8 rows on, the 112
+    The skinny forward-only configuration at its full output width (N = 28672) and reduced K: from 8 rows on, the 112
     column blocks of 256 run as one wave of whole tiles with the fused epilogue; fewer rows keep the
     swap-AB stream-K kernel.  Both against the oracle.
     """
@@ -479,7 +479,7 @@ def test_gemms_under_a_cta_limit():
 
 
 def test_mlp_pair_shapes_of_config3():
-    """BASELINE.json config 3 at reduced token count: 4096 -> 14336 (silu, no bias) -> 4096 (no bias)."""
+    """The transformer MLP pair at reduced token count: 4096 -> 14336 (silu, no bias) -> 4096 (no bias)."""
     gen = torch.Generator().manual_seed(23)
     x = torch.randn(384, 4096, generator=gen).bfloat16()
     w_up = (torch.randn(4096, 14336, generator=gen) * 0.02).bfloat16()

@@ -58,7 +58,7 @@ def test_switch_points_exact(name):
 
 
 def test_oracle_matches_torch_on_config1():
-    """BASELINE.json config 1 against torch.nn.Linear + ReLU, the comparator of the reference's test."""
+    """The smallest configuration (fp32, 64 x 128 -> 256, bias, relu) against torch.nn.Linear + ReLU, the comparator of the reference's test."""
     case = load_golden('config1_fp32_relu')
     x = case['x'].clone().requires_grad_(True)
     lin = torch.nn.Linear(128, 256)
