@@ -147,13 +147,21 @@ class GradientBuckets:
         if transport not in ('nccl', 'multimem', 'auto'):
             raise ValueError(f"transport must be 'nccl', 'multimem' or 'auto', not {transport!r}")
         if transport != 'nccl' and self.world_size > 1 and self.device.type == 'cuda':
+            failure = None
             try:
                 self._multimem = _MultimemBucket(total, self.grad_dtype, self.device, process_group, comm_ctas)
+            except Exception as error:
+                failure = error
+            # All ranks use the same transport: one that could not set the mapping up sends everybody to NCCL.
+            agreed = torch.tensor([0 if failure is None else 1], dtype=torch.int32, device=self.device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MAX, group=process_group)
+            if int(agreed.item()) == 0:
                 self.transport = 'multimem'
                 comm_sms = comm_ctas
-            except Exception:
+            else:
+                self._multimem = None
                 if transport == 'multimem':
-                    raise
+                    raise RuntimeError('NVLink multicast transport unavailable on at least one rank') from failure
         self.flat = (self._multimem.flat if self._multimem is not None else
                      torch.zeros(total, dtype=self.grad_dtype, device=self.device))
         # What .grad aliases: the same buffer, or a second one in the parameters' dtype.
