@@ -9,6 +9,7 @@ Public surface (mirrors the reference's for this path, attorch/__init__.py:7-22)
     Sigmoid ... Softshrink, ActFuncAutoGrad
                       the standalone activation layers with fused dropout (attorch/act_layers.py)
     GLU, GLUAutoGrad  the gated linear unit with an arbitrary activation (attorch/glu_layer.py)
+    GatedLinear       a projection with the gated linear unit fused into its epilogue
     CrossEntropyLoss, CrossEntropyLossAutoGrad
                       mean cross-entropy over class indices (attorch/cross_entropy_loss_layer.py)
     set_dropout_stream
@@ -22,11 +23,12 @@ from .act_layers import (CELU, ELU, GELU, SELU, ActFuncAutoGrad, Hardshrink, Har
                          Hardtanh, LeakyReLU, LogSigmoid, Mish, ReLU, ReLU6, Sigmoid, SiLU, Softplus,
                          Softshrink, Softsign, Tanh, Tanhshrink, set_dropout_stream)
 from .cross_entropy_loss_layer import CrossEntropyLoss, CrossEntropyLossAutoGrad
+from .gated_linear import GatedLinear, GatedLinearAutoGrad
 from .glu_layer import GLU, GLUAutoGrad
 from .linear_layer import (Linear, LinearAutoGrad, check_status, get_output_dtype, set_gemm_flags,
                            set_reserved_sms, set_save_derivative)
 
-__all__ = ['convert', 'nn', 'CrossEntropyLoss', 'CrossEntropyLossAutoGrad', 'GLU', 'GLUAutoGrad', 'Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags',
+__all__ = ['convert', 'nn', 'CrossEntropyLoss', 'CrossEntropyLossAutoGrad', 'GatedLinear', 'GatedLinearAutoGrad', 'GLU', 'GLUAutoGrad', 'Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags',
            'set_save_derivative', 'set_reserved_sms', 'set_dropout_stream', 'ActFuncAutoGrad', 'CELU', 'ELU', 'GELU', 'SELU', 'Hardshrink',
            'Hardsigmoid', 'Hardswish', 'Hardtanh', 'LeakyReLU', 'LogSigmoid', 'Mish', 'ReLU', 'ReLU6',
            'Sigmoid', 'SiLU', 'Softplus', 'Softshrink', 'Softsign', 'Tanh', 'Tanhshrink']

@@ -55,6 +55,8 @@ SIGNATURES = {
                                              _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
                                              _int, _int, _int, _int, _f32,
                                              _ptr, _i64, _ptr, _ptr, _int]),
+    'ab200_gated_linear_forward': (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                                          _i64, _int, _int, _int, _int, _f32, _ptr, _ptr, _int]),
     'ab200_act_backward_workspace_bytes': (_i64, [_i64, _i64]),
     'ab200_act_backward': (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64,
                                   _int, _int, _int, _f32, _ptr, _i64, _ptr]),

@@ -322,6 +322,44 @@ int ab200_linear_forward_residual(const void* x, const void* w, const void* bias
   return run_tiles_or_split(p, workspace, workspace_bytes, stream, flags);
 }
 
+int ab200_gated_linear_forward(const void* x, const void* w, const void* bias, void* pre_act, void* out, int64_t M,
+                               int64_t K, int64_t H, int64_t x_stride_m, int64_t x_stride_k, int64_t w_stride_k,
+                               int64_t w_stride_n, int64_t ld_pre, int64_t ld_out, int op_dtype, int out_dtype,
+                               int bias_dtype, int act, float act_param, int* status, void* stream_, int flags) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || K < 0 || H < 0) return ERR_BAD_SHAPE;
+  if (!fits_int(M) || !fits_int(K) || !fits_int(2 * H)) return ERR_TOO_LARGE;
+  if (!valid_dtype(op_dtype) || !valid_dtype(out_dtype) || (bias && !valid_dtype(bias_dtype))) return ERR_BAD_DTYPE;
+  if (!valid_act(act)) return ERR_BAD_ACT;
+  if (M == 0 || H == 0) return OK;
+  if (!out || !x || !w || !status) return ERR_NULL_POINTER;
+  if (ld_out < H || (pre_act && ld_pre < 2 * H)) return ERR_BAD_STRIDE;
+  const int elt = dtype_size(op_dtype);
+  // Tensor-core path only: operands TMA can address, a reduction, and a second half that starts on a
+  // 16-byte boundary in W, in the saved pre-activation and in the bias.
+  if (K <= 0 || !tma_ok(x, x_stride_m, x_stride_k, elt) || !tma_ok(w, w_stride_k, w_stride_n, elt) ||
+      x_stride_m < K || w_stride_k < 2 * H || (H * elt) % 16 != 0 || (H * dtype_size(out_dtype)) % 16 != 0)
+    return ERR_BAD_STRIDE;
+  TcProblem p{};
+  p.op_dtype = op_dtype;
+  p.a = x; p.a_mn = false; p.a_pitch = x_stride_m;
+  p.b = w; p.b_mn = true; p.b_pitch = w_stride_k;
+  p.allow_pair = pair_allowed(flags);
+  p.allow_tma_store = !(flags & AB200_FLAG_NO_TMA_STORE);
+  p.reserve_sms = (flags >> AB200_FLAG_RESERVE_SMS_SHIFT) & 0xFF;
+  GemmArgs& g = p.g;
+  g.status = status;
+  g.M = static_cast<int>(M); g.N = static_cast<int>(H); g.K = static_cast<int>(K);
+  g.gate_cols = static_cast<int>(H);
+  g.out = out; g.ld_out = ld_out; g.out_dtype = out_dtype; g.grad_dtype = out_dtype;
+  g.aux = pre_act; g.ld_aux = ld_pre;
+  g.bias = bias; g.bias_dtype = bias_dtype;
+  g.act = act; g.act_param = act_param;
+  g.stream_k = 0;
+  g_last_path = AB200_PATH_TCGEN05;
+  return launch_tc_counted(p, 256, stream);
+}
+
 extern "C++" {
 namespace {
 // Rows per block of act_backward_kernel for an M x N problem whose blocks are cols_per_block wide:

@@ -96,7 +96,8 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
     rc = encode_2d(&ta, p.op_dtype, p.a, p.g.K, p.g.M, p.a_pitch * elt, Cfg::BKE, Cfg::BM);
   if (rc != OK) return rc;
   if (Cfg::B_MN)
-    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.N, p.g.K, p.b_pitch * elt, Cfg::MN_ATOM, Cfg::BKE, Cfg::MN_BASE32);
+    rc = encode_2d(&tb, p.op_dtype, p.b, p.g.gate_cols ? 2ull * p.g.gate_cols : p.g.N, p.g.K, p.b_pitch * elt,
+                   Cfg::MN_ATOM, Cfg::BKE, Cfg::MN_BASE32);
   else
     rc = encode_2d(&tb, p.op_dtype, p.b, p.g.K, p.g.N, p.b_pitch * elt, Cfg::BKE, Cfg::B_BOX_ROWS);
   if (rc != OK) return rc;
@@ -108,10 +109,12 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   g.tma_store = 0;
   if (!g.stream_k && p.allow_tma_store) {
     if (g.out != nullptr && encode_store_map(&tout, g.out_dtype, g.out, g.M, g.N, g.ld_out)) g.tma_store |= 1;
-    if (g.aux != nullptr && encode_store_map(&taux, g.out_dtype, g.aux, g.M, g.N, g.ld_aux)) g.tma_store |= 2;
+    if (g.aux != nullptr &&
+        encode_store_map(&taux, g.out_dtype, g.aux, g.M, g.gate_cols ? 2ull * g.gate_cols : g.N, g.ld_aux))
+      g.tma_store |= 2;
   }
   g.tiles_m = (g.M + Cfg::TILE_M - 1) / Cfg::TILE_M;
-  g.tiles_n = (g.N + Cfg::BN - 1) / Cfg::BN;
+  g.tiles_n = g.gate_cols ? (g.gate_cols + Cfg::BN / 2 - 1) / (Cfg::BN / 2) : (g.N + Cfg::BN - 1) / Cfg::BN;
   g.k_blocks = (g.K + Cfg::BKE - 1) / Cfg::BKE;
   g.group_m = raster_group_m() / Cfg::CTAS > 0 ? raster_group_m() / Cfg::CTAS : 1;
   const uint32_t fmt = p.op_dtype == DT_F32 ? 2u : (p.op_dtype == DT_BF16 ? 1u : 0u);
@@ -163,6 +166,13 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   // workers busy), its tiles' reductions are shared out over all workers instead.
   int tail_tiles = 0;
   CUtensorMap tpartial = ta;
+  if (g.gate_cols) {
+    // Gated epilogue: whole tiles only, B MN-major; the first half of the saved pre-activation gets a map
+    // of its own (see the kernel).
+    if (!Cfg::B_MN || g.stream_k) return ERR_BAD_STRIDE;
+    if ((g.tma_store & 2) && !encode_store_map(&tpartial, g.out_dtype, g.aux, g.M, g.gate_cols, g.ld_aux))
+      g.tma_store &= ~2;
+  }
   // Half-width last round: where the last round of whole tiles would fill at most half of the workers,
   // its tiles run as twice as many units of BN / 2 columns, handed out like tiles: that round then
   // takes about half as long (weight-gradient product of 8192 tokens, 4096 -> 4096: 256 pair tiles on
@@ -178,7 +188,7 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
   const long long rounds = (tiles + cap - 1) / cap;
   const int last_round = static_cast<int>(tiles - (rounds - 1) * cap);   // tiles in the last round
   const int tail_mode = tail_mode_override();
-  if (!g.stream_k && p.allow_split_tail && Cfg::kHalfUnits && tail_mode != 1 && tail_mode != 2 && cap > 1 &&
+  if (!g.stream_k && !g.gate_cols && p.allow_split_tail && Cfg::kHalfUnits && tail_mode != 1 && tail_mode != 2 && cap > 1 &&
       (last_round * 2 <= cap || tail_mode == 3)) {
     g.stream_k = 3;
     g.dp_tiles = static_cast<int>(tiles) - last_round;
@@ -186,7 +196,7 @@ int launch_cfg(const TcProblem& p, cudaStream_t stream) {
     if (rounds == 1) workers = 2 * last_round < cap ? 2 * last_round : cap;
   }
   // Shared-out last round (AB200_TAIL_MODE=2, or where half-width units are not possible).
-  if (!g.stream_k && tail_mode != 1 && p.tail_workspace != nullptr && tiles > workers && g.k_blocks >= 16 &&
+  if (!g.stream_k && !g.gate_cols && tail_mode != 1 && p.tail_workspace != nullptr && tiles > workers && g.k_blocks >= 16 &&
       workers <= kMaxTailPieces) {
     const int rem = static_cast<int>(tiles % workers);
     // Two slots per worker (its share of the tail touches at most two tiles).

@@ -73,6 +73,11 @@ struct GemmArgs {
   int save_grad;          // aux receives act'(Z) instead of Z (see actm::fwd_grad)
   int grad_dtype;         // element type act'(Z) is stored in (2 bytes if out_dtype is; see api.cu)
   int tma_store;          // bit 0: `out` goes through shared memory and a TMA store; bit 1: `aux` too
+  // Gated linear unit in the epilogue (forward only, B MN-major, whole tiles): B is [K, 2 * gate_cols],
+  // a tile multiplies BN / 2 columns of the first half and the matching BN / 2 columns of the second,
+  // aux receives both pre-activation halves ([M, 2 * gate_cols]) and out = x1 * act(x2) ([M, gate_cols]).
+  // N is then gate_cols; 0 switches it off.
+  int gate_cols;
 };
 
 template <int BN_, int ELT_, bool A_MN_, bool B_MN_, int CTAS_ = 1>
@@ -490,8 +495,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if constexpr (Cfg::B_MN) {
 #pragma unroll
             for (int j = 0; j < Cfg::BN_CTA / Cfg::MN_ATOM; ++j)
-              if (j * Cfg::MN_ATOM < b_cols)
-                ptx::tma_load_2d<kPair>(b_dst + j * Cfg::MN_BOX_BYTES, &tmap_b, full, n0 + j * Cfg::MN_ATOM, k0);
+              if (j * Cfg::MN_ATOM < b_cols) {
+                int col = n0 + j * Cfg::MN_ATOM;
+                if (args.gate_cols) {
+                  // Column t of the tile: first half of the gated pair for t < BN / 2, else second half.
+                  const int t = static_cast<int>(cta) * b_cols + j * Cfg::MN_ATOM;
+                  col = seg.n_blk * (BN / 2) + (t < BN / 2 ? t : args.gate_cols + t - BN / 2);
+                }
+                ptx::tma_load_2d<kPair>(b_dst + j * Cfg::MN_BOX_BYTES, &tmap_b, full, col, k0);
+              }
           } else {
 #pragma unroll
             for (int j = 0; j < Cfg::BN_CTA / Cfg::B_BOX_ROWS; ++j)
@@ -565,6 +577,66 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::tc_fence_after_sync();
       const int row = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32 + lane;
       const bool row_ok = row < args.M;
+      if (args.gate_cols) {
+        // Gated linear unit: chunk c of the first half pairs with chunk c of the second half.
+        constexpr int HB = BN / 2;
+        const int row0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32;
+        const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * BN;
+        auto emit_at = [&](const CUtensorMap* map, void* base, long long ld, bool by_tma, const float (&w)[32],
+                           int col, int valid) {
+          if (by_tma) {
+            if (lane == 0) ptx::tma_store_wait_read();
+            __syncwarp();
+            stage_row_chunk(stage_buf, lane, args.out_dtype, w);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && row0 < args.M) {
+              ptx::tma_store_2d(map, stage_buf, col, row0);
+              ptx::tma_store_commit();
+            }
+          } else if (row_ok) {
+            store_row_chunk(base, args.out_dtype, static_cast<long long>(row) * ld + col, w, valid);
+          }
+        };
+#pragma unroll 1
+        for (int c = half; c < HB / 32; c += Cfg::kEpilogueWarps / 4) {
+          const int col0 = seg.n_blk * HB + c * 32;           // column within each half
+          if (col0 >= args.gate_cols) break;                  // warp-uniform
+          const int valid = (args.gate_cols - col0 < 32) ? args.gate_cols - col0 : 32;
+          uint32_t r1[32], r2[32];
+          ptx::tmem_ld_32x32(t_acc + c * 32, r1);
+          ptx::tmem_ld_32x32(t_acc + HB + c * 32, r2);
+          ptx::tmem_ld_wait();
+          float x1[32], x2[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            x1[i] = __uint_as_float(r1[i]);
+            x2[i] = __uint_as_float(r2[i]);
+          }
+          if (args.bias != nullptr) {
+            add_bias_chunk(x1, args.bias, args.bias_dtype, col0, valid, args.out_dtype);
+            add_bias_chunk(x2, args.bias, args.bias_dtype, args.gate_cols + col0, valid, args.out_dtype);
+          }
+          if (args.aux != nullptr) {
+            // tmap_partial covers the first half only ([M, gate_cols]), so that a ragged last chunk of
+            // it is clipped instead of spilling into the second half's columns.
+            emit_at(&tmap_partial, args.aux, args.ld_aux, (args.tma_store & 2) != 0, x1, col0, valid);
+            emit_at(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, x2, args.gate_cols + col0, valid);
+          }
+          // The unit multiplies the halves as they are stored (rounded to the output type), which is
+          // what a separate gated-linear-unit pass over the stored pre-activation reads
+          // (attorch/glu_kernels.py:45-52).
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            x1[i] = round_through(x1[i], args.out_dtype);
+            x2[i] = round_through(x2[i], args.out_dtype);
+          }
+          act_fwd_inplace(x2, args.act, args.act_param);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) x1[i] *= x2[i];
+          emit_at(&tmap_out, args.out, args.ld_out, (args.tma_store & 1) != 0, x1, col0, valid);
+        }
+      } else {
 #pragma unroll 1
       for (int c = half; c < seg.n_cols / 32; c += Cfg::kEpilogueWarps / 4) {
         const int col0 = seg.n_blk * BN + seg.n_off + c * 32;
@@ -643,6 +715,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             add_residual_chunk(v, args.residual, args.out_dtype, static_cast<long long>(row) * args.ld_res + col0, valid);
           emit(&tmap_out, args.out, args.ld_out, (args.tma_store & 1) != 0, v, args.out_dtype);
         }
+      }
       }
       // This warp has read its share of the accumulator: tell the (leader's) MMA issuer.
       ptx::tc_fence_before_sync();

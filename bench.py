@@ -495,7 +495,25 @@ def activation_layer(args, device):
             continue
         ms = event_time(fn, args.steps, max(args.warmup, 3))
         results[name] = {'us': round(ms * 1e3, 2), 'gbs': round(nbytes / (ms * 1e-3) / 1e9, 1)}
-    best = results[args.only or 'kernel_forward']['gbs']
+    # The same gate fused into the projection that feeds it (4096 -> 2 * 14336 on 16384 tokens, the gated
+    # up-projection of the MLP pair): one kernel against projection + gated-unit kernel; TFLOP/s of the product.
+    del gx, gdy, gy, gdx
+    torch.cuda.empty_cache()
+    if not args.only or args.only.startswith('gated'):
+        tokens, k_in = 16384, 4096
+        xg = torch.randn(tokens, k_in, device=device).bfloat16()
+        fused = attorch_b200.GatedLinear(k_in, half, bias=False, act_func='silu', device=device, dtype=torch.bfloat16)
+        plain = attorch_b200.Linear(k_in, 2 * half, bias=False, device=device, dtype=torch.bfloat16)
+        gate = attorch_b200.GLU(dim=-1, act_func='silu')
+        flops = 2.0 * tokens * k_in * 2 * half
+        with torch.no_grad():
+            for name, fn in (('gated_linear_forward_fused', lambda: fused(xg)),
+                             ('gated_linear_forward_two_kernels', lambda: gate(plain(xg)))):
+                if args.only and name != args.only:
+                    continue
+                ms = event_time(fn, args.steps, max(args.warmup, 3))
+                results[name] = {'us': round(ms * 1e3, 2), 'tflops': round(flops / (ms * 1e-3) / 1e12, 1)}
+    best = results.get(args.only or 'kernel_forward', {}).get('gbs', 0.0)
     print(json.dumps({'metric': 'activation_layer_gbs', 'value': best, 'unit': 'GB/s', 'n_gpus': 1,
                       'steps': args.steps, 'warmup': args.warmup, 'higher_is_better': True, 'dtype': 'bf16',
                       'data': 'synthetic',

@@ -183,6 +183,25 @@ int ab200_linear_forward_residual(const void* x, const void* w, const void* bias
                                   int act, float act_param, void* workspace, int64_t workspace_bytes,
                                   int* status, void* stream, int flags);
 
+/*
+ * Projection followed by a gated linear unit, in one kernel:
+ *     [X1 | X2] = X * W (+ bias),   pre_act <- [X1 | X2] (if not NULL),   out <- X1 * act(X2)
+ * with W [K, 2H], bias [2H], pre_act [M, 2H] (row pitch ld_pre >= 2H), out [M, H].  It replaces
+ * linear_forward_kernel without activation (attorch/linear_kernels.py:59-188) followed by
+ * glu_forward_kernel over its output (attorch/glu_kernels.py:13-53, with the two copies of the halves
+ * attorch/glu_layer.py:58-60 makes), i.e. attorch.GLU(act_func)(attorch.Linear(K, 2H)(x)), and saves
+ * the read of [M, 2H] between the two.  The halves are multiplied as they are stored (rounded to
+ * out_dtype), so the result equals the two-kernel sequence bit for bit.  Backward is the existing
+ * sequence: ab200_glu_backward on pre_act, then the bias sum and the two products.
+ * Tensor-core path only: returns AB200_ERR_BAD_STRIDE where x or w are not TMA-addressable or H is not a
+ * multiple of 16 bytes' worth of elements (callers then run the two kernels).  flags: AB200_FLAG_NO_PAIR,
+ * AB200_FLAG_NO_TMA_STORE, AB200_FLAG_RESERVE_SMS(n).
+ */
+int ab200_gated_linear_forward(const void* x, const void* w, const void* bias, void* pre_act, void* out, int64_t M,
+                               int64_t K, int64_t H, int64_t x_stride_m, int64_t x_stride_k, int64_t w_stride_k,
+                               int64_t w_stride_n, int64_t ld_pre, int64_t ld_out, int op_dtype, int out_dtype,
+                               int bias_dtype, int act, float act_param, int* status, void* stream, int flags);
+
 /* Workspace the forward call may use for this shape and these flags (0 when it needs none). */
 int64_t ab200_forward_workspace_bytes(int64_t M, int64_t K, int64_t N, int flags);
 
