@@ -680,40 +680,51 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
         } else {
-          if (args.bias != nullptr) add_bias_chunk(v, args.bias, args.bias_dtype, col0, valid, args.out_dtype);
           const int row0 = seg.m_blk * Cfg::TILE_M + static_cast<int>(cta) * BM + q * 32;   // chunk's first row
-          // Writes one 32 x 32 chunk of an output: through the warp's staging buffer and a TMA
-          // store, or straight from registers where TMA cannot address the output.
-          auto emit = [&](const CUtensorMap* map, void* base, long long ld, bool by_tma, const float (&w)[32], int dt) {
-            if (by_tma) {
-              // One staging buffer per warp: the previous store must have read it out first.
-              if (lane == 0) ptx::tma_store_wait_read();
-              __syncwarp();
-              stage_row_chunk(stage_buf, lane, dt, w);
-              ptx::fence_proxy_async_smem();
-              __syncwarp();
-              if (lane == 0 && row0 < args.M) {
-                ptx::tma_store_2d(map, stage_buf, col0, row0);
-                ptx::tma_store_commit();
+          // The fused epilogue of one chunk.  kOdt / kGdt fix the output type and the type the saved
+          // derivative is stored in at compile time (-1: read them from the arguments): with the types
+          // known the conversions and packings are single instructions instead of selections between
+          // the variants, which on the forward pass with bias, gelu and a saved derivative is 5 us of 217.
+          auto fused = [&]<int kOdt, int kGdt>() {
+            const int odt = kOdt >= 0 ? kOdt : args.out_dtype;
+            const int gdt = kGdt >= 0 ? kGdt : args.grad_dtype;
+            if (args.bias != nullptr) add_bias_chunk(v, args.bias, args.bias_dtype, col0, valid, odt);
+            // Writes one 32 x 32 chunk of an output: through the warp's staging buffer and a TMA
+            // store, or straight from registers where TMA cannot address the output.
+            auto emit = [&](const CUtensorMap* map, void* base, long long ld, bool by_tma, const float (&w)[32], int dt) {
+              if (by_tma) {
+                // One staging buffer per warp: the previous store must have read it out first.
+                if (lane == 0) ptx::tma_store_wait_read();
+                __syncwarp();
+                stage_row_chunk(stage_buf, lane, dt, w);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && row0 < args.M) {
+                  ptx::tma_store_2d(map, stage_buf, col0, row0);
+                  ptx::tma_store_commit();
+                }
+              } else if (row_ok) {
+                store_row_chunk(base, dt, static_cast<long long>(row) * ld + col0, w, valid);
               }
-            } else if (row_ok) {
-              store_row_chunk(base, dt, static_cast<long long>(row) * ld + col0, w, valid);
-            }
-          };
-          if (args.aux != nullptr && args.save_grad) {
-            // Save act'(Z) instead of Z: backward then needs one multiply per element.
-            float zr[32], g[32];
+            };
+            if (args.aux != nullptr && args.save_grad) {
+              // Save act'(Z) instead of Z: backward then needs one multiply per element.
+              float zr[32], g[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) zr[i] = round_through(v[i], args.out_dtype);
-            act_fwd_grad(v, zr, g, args.act, args.act_param);
-            emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, g, args.grad_dtype);
-          } else {
-            if (args.aux != nullptr) emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, v, args.out_dtype);
-            act_fwd_inplace(v, args.act, args.act_param);
-          }
-          if (args.residual != nullptr && row_ok)
-            add_residual_chunk(v, args.residual, args.out_dtype, static_cast<long long>(row) * args.ld_res + col0, valid);
-          emit(&tmap_out, args.out, args.ld_out, (args.tma_store & 1) != 0, v, args.out_dtype);
+              for (int i = 0; i < 32; ++i) zr[i] = round_through(v[i], odt);
+              act_fwd_grad(v, zr, g, args.act, args.act_param);
+              emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, g, gdt);
+            } else {
+              if (args.aux != nullptr) emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, v, odt);
+              act_fwd_inplace(v, args.act, args.act_param);
+            }
+            if (args.residual != nullptr && row_ok)
+              add_residual_chunk(v, args.residual, odt, static_cast<long long>(row) * args.ld_res + col0, valid);
+            emit(&tmap_out, args.out, args.ld_out, (args.tma_store & 1) != 0, v, odt);
+          };
+          if (args.out_dtype == DT_BF16 && args.grad_dtype == DT_F16) fused.template operator()<DT_BF16, DT_F16>();
+          else if (args.out_dtype == DT_BF16 && args.grad_dtype == DT_BF16) fused.template operator()<DT_BF16, DT_BF16>();
+          else fused.template operator()<-1, -1>();
         }
       }
       }

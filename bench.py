@@ -1210,6 +1210,11 @@ def main():
                             'tokens': c3.tokens, 'layers': ['4096->14336 silu', '14336->4096']}
             del c3
             torch.cuda.empty_cache()
+            # A pause first: c4 is a burst of 80 us kernels bound by HBM, and measured right after the
+            # seconds of sustained GEMMs above it runs at the clocks the power limiter left behind
+            # (5.3 TB/s instead of the 6.3 TB/s it reaches from idle).
+            torch.cuda.synchronize()
+            time.sleep(1.5)
             c4 = skinny_forward(30, 5, device, lib)
             extras['c4'] = {'unit': 'GB/s of weight read, against 8000 nominal and the measured copy bandwidth',
                             'rows': c4['config']['rows']}
