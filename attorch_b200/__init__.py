@@ -12,6 +12,9 @@ Public surface (mirrors the reference's for this path, attorch/__init__.py:7-22)
     GatedLinear       a projection with the gated linear unit fused into its epilogue
     CrossEntropyLoss, CrossEntropyLossAutoGrad
                       mean cross-entropy over class indices (attorch/cross_entropy_loss_layer.py)
+    LayerNorm, LayerNormAutoGrad
+                      layer normalisation (attorch/layer_norm_layer.py)
+    LayerNormLinear   a LayerNorm and the Linear after it with no cast pass between them
     set_dropout_stream
                       the reference's dropout mask (default) or a cheaper generator
     nn                torch.nn with this package's modules in place of PyTorch's (attorch/nn.py)
@@ -25,10 +28,11 @@ from .act_layers import (CELU, ELU, GELU, SELU, ActFuncAutoGrad, Hardshrink, Har
 from .cross_entropy_loss_layer import CrossEntropyLoss, CrossEntropyLossAutoGrad
 from .gated_linear import GatedLinear, GatedLinearAutoGrad
 from .glu_layer import GLU, GLUAutoGrad
+from .layer_norm_layer import LayerNorm, LayerNormAutoGrad, LayerNormLinear
 from .linear_layer import (Linear, LinearAutoGrad, check_status, get_output_dtype, set_gemm_flags,
                            set_reserved_sms, set_save_derivative)
 
-__all__ = ['convert', 'nn', 'CrossEntropyLoss', 'CrossEntropyLossAutoGrad', 'GatedLinear', 'GatedLinearAutoGrad', 'GLU', 'GLUAutoGrad', 'Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags',
+__all__ = ['convert', 'nn', 'CrossEntropyLoss', 'CrossEntropyLossAutoGrad', 'GatedLinear', 'GatedLinearAutoGrad', 'GLU', 'GLUAutoGrad', 'LayerNorm', 'LayerNormAutoGrad', 'LayerNormLinear', 'Linear', 'LinearAutoGrad', 'check_status', 'get_output_dtype', 'set_gemm_flags',
            'set_save_derivative', 'set_reserved_sms', 'set_dropout_stream', 'ActFuncAutoGrad', 'CELU', 'ELU', 'GELU', 'SELU', 'Hardshrink',
            'Hardsigmoid', 'Hardswish', 'Hardtanh', 'LeakyReLU', 'LogSigmoid', 'Mish', 'ReLU', 'ReLU6',
            'Sigmoid', 'SiLU', 'Softplus', 'Softshrink', 'Softsign', 'Tanh', 'Tanhshrink']

@@ -82,6 +82,11 @@ SIGNATURES = {
                                            _ptr, _i64, _ptr]),
     'ab200_cross_entropy_backward': (_int, [_ptr, _int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64,
                                             _i64, _int, _int, _int, _ptr]),
+    'ab200_layer_norm_forward': (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _int, _int,
+                                        _f32, _ptr]),
+    'ab200_layer_norm_workspace_bytes': (_i64, [_i64, _i64]),
+    'ab200_layer_norm_backward': (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64,
+                                         _int, _int, _int, _int, _ptr, _i64, _ptr]),
     'ab200_multimem_all_reduce': (_int, [_ptr, _i64, _int, _int, _int, _ptr, _int, _ptr, _ptr]),
     'ab200_collective_flag_bytes': (_i64, []),
 }

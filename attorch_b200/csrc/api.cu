@@ -15,6 +15,7 @@
 #include "act_elementwise.cuh"
 #include "glu.cuh"
 #include "cross_entropy.cuh"
+#include "layer_norm_launch.cuh"
 
 namespace ab200 {
 
@@ -795,6 +796,66 @@ int ab200_cross_entropy_backward(const void* loss_grad, int loss_grad_dtype, con
 #undef AB200_CE_BWD
   ++g_launches;
   return cudaGetLastError() == cudaSuccess ? OK : ERR_LAUNCH;
+}
+
+int ab200_layer_norm_forward(const void* x, const void* weight, const void* bias, float* mean, float* inv_std, void* y,
+                             int64_t rows, int64_t feat, int64_t ldx, int64_t ldy, int x_dtype, int param_dtype,
+                             int y_dtype, float eps, void* stream_) {
+  if (rows < 0 || feat <= 0) return ERR_BAD_SHAPE;
+  if (!fits_int(rows) || !fits_int(feat)) return ERR_TOO_LARGE;
+  if (!valid_dtype(x_dtype) || !valid_dtype(y_dtype) || (weight && !valid_dtype(param_dtype))) return ERR_BAD_DTYPE;
+  // y has x's type, or fp32 for a 16-bit x, or a 16-bit type for an fp32 x.
+  if (x_dtype != y_dtype && x_dtype != DT_F32 && y_dtype != DT_F32) return ERR_BAD_DTYPE;
+  if (rows == 0) return OK;
+  if (!x || !y || (bias && !weight) || ((mean == nullptr) != (inv_std == nullptr))) return ERR_NULL_POINTER;
+  if (ldx < feat || ldy < feat) return ERR_BAD_STRIDE;
+  const int rc = launch_layer_norm_forward(x, ldx, weight, weight ? bias : nullptr, param_dtype, mean, inv_std, y, ldy,
+                                           rows, static_cast<int>(feat), x_dtype, y_dtype, eps,
+                                           static_cast<cudaStream_t>(stream_));
+  if (rc < 0) return rc;
+  g_launches += rc;
+  return OK;
+}
+
+int64_t ab200_layer_norm_workspace_bytes(int64_t rows, int64_t feat) {
+  const long long parts = layer_norm_parts(rows, feat);
+  return parts > 0 ? 2 * parts * feat * 4 : 4;
+}
+
+int ab200_layer_norm_backward(const void* dy, const void* x, const float* mean, const float* inv_std,
+                              const void* weight, void* dx, float* weight_grad, float* bias_grad, int64_t rows,
+                              int64_t feat, int64_t lddy, int64_t ldx, int64_t lddx, int dy_dtype, int x_dtype,
+                              int param_dtype, int dx_dtype, void* workspace, int64_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows < 0 || feat <= 0) return ERR_BAD_SHAPE;
+  if (!fits_int(rows) || !fits_int(feat)) return ERR_TOO_LARGE;
+  if (!valid_dtype(x_dtype) || !valid_dtype(dy_dtype) || !valid_dtype(dx_dtype) || (weight && !valid_dtype(param_dtype)))
+    return ERR_BAD_DTYPE;
+  // dy has the forward output's type; dx the wider of that and x's.
+  const bool same = x_dtype == dy_dtype && x_dtype == dx_dtype;
+  const bool widened = x_dtype != DT_F32 && dy_dtype == DT_F32 && dx_dtype == DT_F32;
+  const bool narrowed = x_dtype == DT_F32 && dy_dtype != DT_F32 && dx_dtype == DT_F32;
+  if (!same && !widened && !narrowed) return ERR_BAD_DTYPE;
+  if ((weight_grad && !weight) || (bias_grad && !weight_grad)) return ERR_NULL_POINTER;
+  if (rows == 0) {
+    // No rows: the parameter gradients are sums over nothing.
+    if (weight_grad && cudaMemsetAsync(weight_grad, 0, feat * 4, stream) != cudaSuccess) return ERR_LAUNCH;
+    if (bias_grad && cudaMemsetAsync(bias_grad, 0, feat * 4, stream) != cudaSuccess) return ERR_LAUNCH;
+    return OK;
+  }
+  if (!dy || !x || !mean || !inv_std || !dx) return ERR_NULL_POINTER;
+  if (lddy < feat || ldx < feat || lddx < feat) return ERR_BAD_STRIDE;
+  if (weight_grad) {
+    if (!workspace) return ERR_NULL_POINTER;
+    if (workspace_bytes < ab200_layer_norm_workspace_bytes(rows, feat)) return ERR_WORKSPACE_TOO_SMALL;
+    if (reinterpret_cast<uintptr_t>(workspace) & 3) return ERR_BAD_STRIDE;
+  }
+  const int rc = launch_layer_norm_backward(dy, lddy, x, ldx, mean, inv_std, weight, param_dtype, dx, lddx, weight_grad,
+                                            bias_grad, static_cast<float*>(workspace), rows, static_cast<int>(feat),
+                                            dy_dtype, x_dtype, dx_dtype, stream);
+  if (rc < 0) return rc;
+  g_launches += rc;
+  return OK;
 }
 
 uint32_t ab200_dropout_threshold(float drop_p, int flags) {

@@ -1,0 +1,383 @@
+// Layer normalisation over the rows of a matrix, forward and backward: the step in front of the first
+// projection of a transformer block (reference: attorch/layer_norm_kernels.py:14-221, launched from
+// attorch/layer_norm_layer.py:19-157; the caller is examples/wikitext-2/gpt.py:82).
+//
+//   forward   mean_i = sum_j x_ij / F,  d_ij = x_ij - mean_i,  inv_std_i = rsqrt(sum_j d_ij^2 / F + eps)
+//             y_ij = d_ij * inv_std_i [* w_j [+ b_j]]
+//   backward  p_ij = (x_ij - mean_i) * inv_std_i,  g_ij = w_j * dy_ij
+//             dx_ij = inv_std_i * (g_ij - (p_ij * sum_j(p_ij g_ij) / F + sum_j g_ij / F))
+//             dw_j = sum_i dy_ij p_ij,  db_j = sum_i dy_ij
+//
+// Both kernels are bound by HBM and touch every element once: a row is loaded into registers (16 elements
+// per thread, 16-byte loads), both row sums are taken from the registers, and the result is written from
+// them.  A row belongs to a group of R threads: one warp for rows of up to 512 elements (eight rows per
+// block), 256 threads up to 4096, 512 threads beyond; elements past 16 * R are read again (from L2) in
+// the second and third pass.  Blocks loop over rows, so weight and bias are loaded once per block, and
+// in backward each thread keeps the weight- and bias-gradient sums of its own columns in registers over
+// all rows of its block; one partial row per row group goes to the workspace, and ln_param_finish_kernel
+// adds the partials in a fixed order.  (The reference re-reads x and dy in a second pass over the same
+// data for these sums only when its programs hold several rows; it writes one partial per program.)
+//
+// The stored type of y may differ from x's: fp32 for a 16-bit x (the reference's autocast_to_fp32), or
+// a 16-bit y for an fp32 x - the operand type of the projection that follows, which saves that layer's
+// cast pass over the activations.  Every value is computed in fp32 and rounded once by the store, as in
+// the reference (it widens the loaded row, line 84, and the store narrows, line 102).  All sums have a
+// fixed order: results do not depend on scheduling.
+#pragma once
+#include "common.cuh"
+
+namespace ab200 {
+
+constexpr int kLnCache = 16;   // elements of a row that one thread keeps in registers
+
+// V elements of T starting at p, which is aligned to V * sizeof(T) bytes (4, 8 or 16), as one access.
+template <class T, int V>
+__device__ __forceinline__ void ln_load(const T* p, float* v) {
+  constexpr int kBytes = V * static_cast<int>(sizeof(T));
+  static_assert(V == 1 || kBytes == 8 || kBytes == 16, "one scalar, or an 8- or 16-byte access");
+  if constexpr (V == 1) {
+    v[0] = to_f32<T>(*p);
+  } else if constexpr (kBytes == 16) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+    for (int i = 0; i < V; ++i) v[i] = to_f32<T>(e[i]);
+  } else {
+    const uint2 q = *reinterpret_cast<const uint2*>(p);
+    const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+    for (int i = 0; i < V; ++i) v[i] = to_f32<T>(e[i]);
+  }
+}
+
+template <class T, int V>
+__device__ __forceinline__ void ln_store(T* p, const float* v) {
+  constexpr int kBytes = V * static_cast<int>(sizeof(T));
+  if constexpr (V == 1) {
+    *p = from_f32<T>(v[0]);
+  } else if constexpr (kBytes == 16) {
+    uint4 q;
+    T* e = reinterpret_cast<T*>(&q);
+#pragma unroll
+    for (int i = 0; i < V; ++i) e[i] = from_f32<T>(v[i]);
+    *reinterpret_cast<uint4*>(p) = q;
+  } else {
+    uint2 q;
+    T* e = reinterpret_cast<T*>(&q);
+#pragma unroll
+    for (int i = 0; i < V; ++i) e[i] = from_f32<T>(v[i]);
+    *reinterpret_cast<uint2*>(p) = q;
+  }
+}
+
+// Sums a and b over the R threads of a row group; every thread of the block must call it.  Groups of
+// more than one warp go through shared memory (two buffers, used in turn, so one barrier per call).
+template <int R, int kThreads>
+__device__ __forceinline__ float2 ln_group_sum(float a, float b, float2 (*scratch)[kThreads / 32], int& phase) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    a += __shfl_xor_sync(0xFFFFFFFFu, a, off);
+    b += __shfl_xor_sync(0xFFFFFFFFu, b, off);
+  }
+  if constexpr (R > 32) {
+    static_assert(R == kThreads, "a row group larger than a warp is the whole block");
+    if ((threadIdx.x & 31) == 0) scratch[phase][threadIdx.x >> 5] = make_float2(a, b);
+    __syncthreads();
+    a = 0.0f;
+    b = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) {
+      a += scratch[phase][w].x;
+      b += scratch[phase][w].y;
+    }
+    phase ^= 1;
+  }
+  return make_float2(a, b);
+}
+
+template <int A, int B>
+struct LnMax {
+  static constexpr int value = A > B ? A : B;
+};
+
+template <class TIn, class TOut, int R, bool kVec>
+__global__ void __launch_bounds__(R < 256 ? 256 : R)
+ln_forward_kernel(const TIn* __restrict__ x, long long ldx, const void* __restrict__ w, const void* __restrict__ b,
+                  int param_dtype, float* __restrict__ mean, float* __restrict__ inv_std, TOut* __restrict__ y,
+                  long long ldy, long long rows, int F, float eps) {
+  constexpr int kThreads = R < 256 ? 256 : R;
+  constexpr int kRowsPerBlock = kThreads / R;
+  constexpr int V = kVec ? 16 / LnMax<sizeof(TIn), sizeof(TOut)>::value : 1;
+  constexpr int kG = kLnCache / V;          // groups of V elements each thread keeps
+  __shared__ float2 scratch[2][kThreads / 32];
+  int phase = 0;
+  const int t = threadIdx.x % R, slot = threadIdx.x / R;
+  const int groups = F / V;
+  const float feat = static_cast<float>(F);
+
+  float wc[kLnCache], bc[kLnCache];
+#pragma unroll
+  for (int i = 0; i < kG; ++i) {
+    const int g = t + i * R;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const bool in = g < groups;
+      wc[i * V + j] = (w != nullptr && in) ? load_as_f32(w, param_dtype, g * V + j) : 1.0f;
+      bc[i * V + j] = (b != nullptr && in) ? load_as_f32(b, param_dtype, g * V + j) : 0.0f;
+    }
+  }
+
+  const long long row_blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  for (long long rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {
+    const long long row = rb * kRowsPerBlock + slot;
+    const bool live = row < rows;
+    const TIn* xr = x + (live ? row : 0) * ldx;
+    TOut* yr = y + (live ? row : 0) * ldy;
+
+    float xc[kLnCache];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kG; ++i) {
+      const int g = t + i * R;
+      if (live && g < groups) {
+        ln_load<TIn, V>(xr + g * V, &xc[i * V]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) xc[i * V + j] = 0.0f;
+      }
+#pragma unroll
+      for (int j = 0; j < V; ++j) s += xc[i * V + j];
+    }
+    if (live) {
+      for (int g = t + kG * R; g < groups; g += R) {
+        float v[V];
+        ln_load<TIn, V>(xr + g * V, v);
+#pragma unroll
+        for (int j = 0; j < V; ++j) s += v[j];
+      }
+    }
+    const float mu = ln_group_sum<R, kThreads>(s, 0.0f, scratch, phase).x / feat;
+
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kG; ++i) {
+      const bool in = t + i * R < groups;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float d = in ? xc[i * V + j] - mu : 0.0f;
+        xc[i * V + j] = d;
+        q += d * d;
+      }
+    }
+    if (live) {
+      for (int g = t + kG * R; g < groups; g += R) {
+        float v[V];
+        ln_load<TIn, V>(xr + g * V, v);
+#pragma unroll
+        for (int j = 0; j < V; ++j) q += (v[j] - mu) * (v[j] - mu);
+      }
+    }
+    const float rs = rsqrtf(ln_group_sum<R, kThreads>(q, 0.0f, scratch, phase).x / feat + eps);
+    if (live && t == 0 && mean != nullptr) {
+      mean[row] = mu;
+      inv_std[row] = rs;
+    }
+    if (!live) continue;      // only in the one-warp-per-row variant, which has no block barrier
+
+#pragma unroll
+    for (int i = 0; i < kG; ++i) {
+      const int g = t + i * R;
+      if (g < groups) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) o[j] = xc[i * V + j] * rs * wc[i * V + j] + bc[i * V + j];
+        ln_store<TOut, V>(yr + g * V, o);
+      }
+    }
+    for (int g = t + kG * R; g < groups; g += R) {
+      float v[V], o[V];
+      ln_load<TIn, V>(xr + g * V, v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float wj = w != nullptr ? load_as_f32(w, param_dtype, g * V + j) : 1.0f;
+        const float bj = b != nullptr ? load_as_f32(b, param_dtype, g * V + j) : 0.0f;
+        o[j] = (v[j] - mu) * rs * wj + bj;
+      }
+      ln_store<TOut, V>(yr + g * V, o);
+    }
+  }
+}
+
+// kParams: also accumulate the weight- and bias-gradient sums of this thread's columns (requires
+// F <= kLnCache * R, so that every column is one that a thread keeps).  wpart / bpart: one row of F
+// floats per row group of the grid, [gridDim.x * rows per block, F].
+template <class TIn, class TDy, class TDx, int R, bool kVec, bool kParams>
+__global__ void __launch_bounds__(R < 256 ? 256 : R)
+ln_backward_kernel(const TDy* __restrict__ dy, long long lddy, const TIn* __restrict__ x, long long ldx,
+                   const float* __restrict__ mean, const float* __restrict__ inv_std, const void* __restrict__ w,
+                   int param_dtype, TDx* __restrict__ dx, long long lddx, float* __restrict__ wpart,
+                   float* __restrict__ bpart, long long rows, int F) {
+  constexpr int kThreads = R < 256 ? 256 : R;
+  constexpr int kRowsPerBlock = kThreads / R;
+  constexpr int V =
+      kVec ? 16 / LnMax<LnMax<sizeof(TIn), sizeof(TDy)>::value, sizeof(TDx)>::value : 1;
+  constexpr int kG = kLnCache / V;
+  __shared__ float2 scratch[2][kThreads / 32];
+  int phase = 0;
+  const int t = threadIdx.x % R, slot = threadIdx.x / R;
+  const int groups = F / V;
+  const float feat = static_cast<float>(F);
+
+  float wc[kLnCache];
+#pragma unroll
+  for (int i = 0; i < kG; ++i) {
+    const int g = t + i * R;
+#pragma unroll
+    for (int j = 0; j < V; ++j)
+      wc[i * V + j] = (w != nullptr && g < groups) ? load_as_f32(w, param_dtype, g * V + j) : 1.0f;
+  }
+  float wacc[kParams ? kLnCache : 1], bacc[kParams ? kLnCache : 1];
+  if constexpr (kParams) {
+#pragma unroll
+    for (int i = 0; i < kLnCache; ++i) wacc[i] = bacc[i] = 0.0f;
+  }
+
+  const long long row_blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  for (long long rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {
+    const long long row = rb * kRowsPerBlock + slot;
+    const bool live = row < rows;
+    const TIn* xr = x + (live ? row : 0) * ldx;
+    const TDy* gr = dy + (live ? row : 0) * lddy;
+    TDx* dr = dx + (live ? row : 0) * lddx;
+    const float mu = live ? mean[row] : 0.0f;
+    const float rs = live ? inv_std[row] : 0.0f;
+
+    float pc[kLnCache], gc[kLnCache];
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kG; ++i) {
+      const int g = t + i * R;
+      if (live && g < groups) {
+        ln_load<TIn, V>(xr + g * V, &pc[i * V]);
+        ln_load<TDy, V>(gr + g * V, &gc[i * V]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const int e = i * V + j;
+          const float p = (pc[e] - mu) * rs;
+          pc[e] = p;
+          if constexpr (kParams) {
+            wacc[e] += gc[e] * p;
+            bacc[e] += gc[e];
+          }
+          gc[e] *= wc[e];
+          s1 += p * gc[e];
+          s2 += gc[e];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) pc[i * V + j] = gc[i * V + j] = 0.0f;
+      }
+    }
+    if (live) {
+      for (int g = t + kG * R; g < groups; g += R) {
+        float xv[V], gv[V];
+        ln_load<TIn, V>(xr + g * V, xv);
+        ln_load<TDy, V>(gr + g * V, gv);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float wj = w != nullptr ? load_as_f32(w, param_dtype, g * V + j) : 1.0f;
+          const float p = (xv[j] - mu) * rs;
+          s1 += p * (wj * gv[j]);
+          s2 += wj * gv[j];
+        }
+      }
+    }
+    const float2 sums = ln_group_sum<R, kThreads>(s1, s2, scratch, phase);
+    const float c1 = sums.x / feat, c2 = sums.y / feat;
+    if (!live) continue;
+
+#pragma unroll
+    for (int i = 0; i < kG; ++i) {
+      const int g = t + i * R;
+      if (g < groups) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) o[j] = rs * (gc[i * V + j] - (pc[i * V + j] * c1 + c2));
+        ln_store<TDx, V>(dr + g * V, o);
+      }
+    }
+    for (int g = t + kG * R; g < groups; g += R) {
+      float xv[V], gv[V], o[V];
+      ln_load<TIn, V>(xr + g * V, xv);
+      ln_load<TDy, V>(gr + g * V, gv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float wj = w != nullptr ? load_as_f32(w, param_dtype, g * V + j) : 1.0f;
+        const float p = (xv[j] - mu) * rs;
+        o[j] = rs * (wj * gv[j] - (p * c1 + c2));
+      }
+      ln_store<TDx, V>(dr + g * V, o);
+    }
+  }
+
+  if constexpr (kParams) {
+    const long long part = static_cast<long long>(blockIdx.x) * kRowsPerBlock + slot;
+#pragma unroll
+    for (int i = 0; i < kG; ++i) {
+      const int g = t + i * R;
+      if (g < groups) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          wpart[part * F + g * V + j] = wacc[i * V + j];
+          if (bpart != nullptr) bpart[part * F + g * V + j] = bacc[i * V + j];
+        }
+      }
+    }
+  }
+}
+
+// Weight- and bias-gradient partial sums for rows wider than the register variant holds: one thread per
+// column, gridDim.y chunks of rows; partial row blockIdx.y of wpart / bpart.
+template <class TIn, class TDy>
+__global__ void __launch_bounds__(256)
+ln_param_grad_kernel(const TDy* __restrict__ dy, long long lddy, const TIn* __restrict__ x, long long ldx,
+                     const float* __restrict__ mean, const float* __restrict__ inv_std, float* __restrict__ wpart,
+                     float* __restrict__ bpart, long long rows, int F, long long rows_per_chunk) {
+  const int col = blockIdx.x * 256 + threadIdx.x;
+  if (col >= F) return;
+  const long long begin = blockIdx.y * rows_per_chunk;
+  const long long end = begin + rows_per_chunk < rows ? begin + rows_per_chunk : rows;
+  float wa = 0.0f, ba = 0.0f;
+  for (long long r = begin; r < end; ++r) {
+    const float g = to_f32<TDy>(dy[r * lddy + col]);
+    const float p = (to_f32<TIn>(x[r * ldx + col]) - mean[r]) * inv_std[r];
+    wa += g * p;
+    ba += g;
+  }
+  wpart[static_cast<long long>(blockIdx.y) * F + col] = wa;
+  if (bpart != nullptr) bpart[static_cast<long long>(blockIdx.y) * F + col] = ba;
+}
+
+// weight_grad[j] = sum over the partial rows of wpart[., j], in order; the same for the bias.
+__global__ void __launch_bounds__(256)
+ln_param_finish_kernel(const float* __restrict__ wpart, const float* __restrict__ bpart, int parts, int F,
+                       float* __restrict__ weight_grad, float* __restrict__ bias_grad) {
+  const int col = blockIdx.x * 256 + threadIdx.x;
+  if (col >= F) return;
+  const float* src = blockIdx.y == 0 ? wpart : bpart;
+  float* dst = blockIdx.y == 0 ? weight_grad : bias_grad;
+  if (dst == nullptr) return;
+  // Four interleaved sums keep four loads in flight; the order is still fixed.
+  float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+  int p = 0;
+  for (; p + 4 <= parts; p += 4) {
+    a0 += src[static_cast<long long>(p) * F + col];
+    a1 += src[static_cast<long long>(p + 1) * F + col];
+    a2 += src[static_cast<long long>(p + 2) * F + col];
+    a3 += src[static_cast<long long>(p + 3) * F + col];
+  }
+  for (; p < parts; ++p) a0 += src[static_cast<long long>(p) * F + col];
+  dst[col] = (a0 + a1) + (a2 + a3);
+}
+
+}  // namespace ab200

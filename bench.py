@@ -578,6 +578,98 @@ def cross_entropy_loss(args, device):
           flush=True)
 
 
+def layer_norm(args, device):
+    """
+    Layer normalisation in front of the first projection, on the C2 shape (8192 tokens, 4096 features):
+    the kernels through the C ABI (fp32 in / fp32 out as PyTorch's autocast would run it, fp32 in / bf16
+    out as the fused operand store, bf16 throughout), then under bf16 autocast one forward + backward of
+    LayerNorm -> Linear(4096 -> 4096, gelu) as attorch_b200.LayerNormLinear, as the two layers one after
+    the other, and as torch.nn.LayerNorm -> torch.nn.Linear -> gelu.  HBM-bound: forward moves
+    rows * feat * (input + output element) bytes, backward rows * feat * (x + dy + dx elements).
+    """
+    import attorch_b200
+    from attorch_b200 import _lib
+    lib = _lib.load()
+    peaks, peak_source = measured_peaks()
+    rows, feat = 8192, 4096
+    n = rows * feat
+    stream = torch.cuda.current_stream().cuda_stream
+    ids = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+    w = torch.randn(feat, device=device)
+    b = torch.randn(feat, device=device)
+    stats = torch.empty(2, rows, device=device)
+    pgrad = torch.empty(2, feat, device=device)
+    ws = torch.empty(lib.ab200_layer_norm_workspace_bytes(rows, feat), dtype=torch.uint8, device=device)
+    results = {}
+    # Three sets of buffers per case, used in turn: 3 * (64 ... 128 MiB) per tensor is larger than L2.
+    for name, xdt, ydt in (('fp32_fp32', torch.float32, torch.float32), ('fp32_bf16', torch.float32, torch.bfloat16),
+                           ('bf16_bf16', torch.bfloat16, torch.bfloat16)):
+        xs = [(torch.randn(rows, feat, device=device) * 2 + 0.5).to(xdt) for _ in range(3)]
+        ys = [torch.empty(rows, feat, dtype=ydt, device=device) for _ in range(3)]
+        dys = [torch.randn(rows, feat, device=device).to(ydt) for _ in range(3)]
+        dxs = [torch.empty(rows, feat, dtype=xdt, device=device) for _ in range(3)]
+        turn = [0]
+
+        def forward():
+            i = turn[0] = (turn[0] + 1) % 3
+            _lib.check(lib.ab200_layer_norm_forward(xs[i].data_ptr(), w.data_ptr(), b.data_ptr(), stats[0].data_ptr(),
+                                                    stats[1].data_ptr(), ys[i].data_ptr(), rows, feat, feat, feat,
+                                                    ids[xdt], _lib.F32, ids[ydt], 1e-5, stream),
+                       'ab200_layer_norm_forward')
+
+        def backward():
+            i = turn[0] = (turn[0] + 1) % 3
+            _lib.check(lib.ab200_layer_norm_backward(dys[i].data_ptr(), xs[i].data_ptr(), stats[0].data_ptr(),
+                                                     stats[1].data_ptr(), w.data_ptr(), dxs[i].data_ptr(),
+                                                     pgrad[0].data_ptr(), pgrad[1].data_ptr(), rows, feat, feat, feat,
+                                                     feat, ids[ydt], ids[xdt], _lib.F32, ids[xdt], ws.data_ptr(),
+                                                     ws.numel(), stream), 'ab200_layer_norm_backward')
+
+        xe, ye = xs[0].element_size(), ys[0].element_size()
+        for kind, fn, nbytes in (('forward', forward, n * (xe + ye)), ('backward', backward, n * (2 * xe + ye))):
+            ms = event_time(fn, args.steps, max(args.warmup, 3))
+            results[f'{name}_{kind}'] = {'us': round(ms * 1e3, 2), 'gbs': round(nbytes / (ms * 1e-3) / 1e9, 1)}
+        del xs, ys, dys, dxs
+    attorch_b200.check_status()
+
+    # The block: LayerNorm -> Linear(gelu) under bf16 autocast, forward + backward, fp32 parameters and input.
+    torch.manual_seed(0)
+    norm = attorch_b200.LayerNorm(feat)
+    linear = attorch_b200.Linear(feat, feat, act_func='gelu')
+    fused = attorch_b200.LayerNormLinear(norm, linear)
+    t_norm = torch.nn.LayerNorm(feat, device=device)
+    t_linear = torch.nn.Linear(feat, feat, device=device)
+    xg = (torch.randn(rows, feat, device=device) * 2 + 0.5).requires_grad_(True)
+    dy = (torch.randn(rows, feat, device=device) * 0.01).bfloat16()
+
+    def block(call, params):
+        def step():
+            with torch.autocast('cuda', dtype=torch.bfloat16):
+                y = call(xg)
+            y.backward(dy)
+            xg.grad = None
+            for p in params:
+                p.grad = None
+        return step
+
+    ours = list(fused.parameters())
+    theirs = list(t_norm.parameters()) + list(t_linear.parameters())
+    for name, step in (('block_fused', block(fused, ours)),
+                       ('block_two_layers', block(lambda t: linear(norm(t)), ours)),
+                       ('block_torch', block(lambda t: torch.nn.functional.gelu(t_linear(t_norm(t))), theirs))):
+        ms = event_time(step, args.steps, max(args.warmup, 3))
+        results[name] = {'us': round(ms * 1e3, 2)}
+    attorch_b200.check_status()
+    best = results['fp32_bf16_forward']['gbs']
+    print(json.dumps({'metric': 'layer_norm_gbs', 'value': best, 'unit': 'GB/s', 'n_gpus': 1, 'steps': args.steps,
+                      'warmup': args.warmup, 'higher_is_better': True, 'dtype': 'f32', 'data': 'synthetic',
+                      'config': {'workload': 'ln', 'shape': [rows, feat], 'l2': 'buffers used in turn, larger than L2',
+                                 **results},
+                      'roofline': {'bound': 'hbm', 'achieved': best, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s',
+                                   'frac': best / peaks['hbm_gbs'], 'traffic': None, 'peak_source': peak_source}}),
+          flush=True)
+
+
 class Comm:
     """Rank, world size and the two collectives the timing protocol needs."""
     def __init__(self, device, world_size, rank):
@@ -998,7 +1090,7 @@ def main():
     parser.add_argument('--gpus', type=int, default=1)
     parser.add_argument('--steps', type=int, default=200)
     parser.add_argument('--warmup', type=int, default=10)
-    parser.add_argument('--workload', choices=sorted(WORKLOADS) + ['c4', 'act', 'ce'], default='c2')
+    parser.add_argument('--workload', choices=sorted(WORKLOADS) + ['c4', 'act', 'ce', 'ln'], default='c2')
     parser.add_argument('--only', default=None,
                         help='workload act: time just this entry (e.g. kernel_forward, glu_backward)')
     parser.add_argument('--impl', choices=['b200', 'reference'], default='b200')
@@ -1013,7 +1105,7 @@ def main():
                         help='override the tokens per GPU (profiling of reduced cases)')
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.workload in ('c4', 'act', 'ce'):
+    if args.workload in ('c4', 'act', 'ce', 'ln'):
         if args.impl == 'reference':
             print(json.dumps({'impl': 'reference', 'unavailable': f'{args.workload} has no CPU arm; use c2'}))
             return
@@ -1023,6 +1115,8 @@ def main():
             print(json.dumps(skinny_forward(args.steps, args.warmup, torch.device('cuda', 0), _lib.load())), flush=True)
         elif args.workload == 'ce':
             cross_entropy_loss(args, torch.device('cuda', 0))
+        elif args.workload == 'ln':
+            layer_norm(args, torch.device('cuda', 0))
         else:
             activation_layer(args, torch.device('cuda', 0))
         return

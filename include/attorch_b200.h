@@ -386,6 +386,46 @@ int ab200_cross_entropy_backward(const void* loss_grad, int loss_grad_dtype, con
                                  int weight_dtype, int grad_dtype, void* stream);
 
 /*
+ * Layer normalisation over the rows of [rows, feat], the step in front of a transformer block's first
+ * projection (the caller: examples/wikitext-2/gpt.py:82).  Replaces layer_norm_forward_kernel
+ * (attorch/layer_norm_kernels.py:14-103, launched at attorch/layer_norm_layer.py:74-82):
+ *     y_ij = (x_ij - mean_i) * rsqrt(var_i + eps) [* weight_j [+ bias_j]],  var_i the biased variance
+ *   x       [rows, feat] of x_dtype, unit inner stride, row pitch ldx (elements)
+ *   weight, bias  [feat] of param_dtype, or NULL (bias only together with weight)
+ *   mean, inv_std  [rows] fp32, receive the row statistics for backward; both NULL when not wanted
+ *   y       [rows, feat] of y_dtype, row pitch ldy.  y_dtype is x_dtype, or fp32 for a 16-bit x (the
+ *           reference's autocast_to_fp32, attorch/layer_norm_layer.py:55-57), or a 16-bit type for an
+ *           fp32 x: the operand type of the projection that follows under autocast, which then needs no
+ *           cast pass of its own.  Values are computed in fp32 and rounded once by the store.
+ * One pass over x: each row is held in registers between the sums and the store.
+ */
+int ab200_layer_norm_forward(const void* x, const void* weight, const void* bias, float* mean, float* inv_std, void* y,
+                             int64_t rows, int64_t feat, int64_t ldx, int64_t ldy, int x_dtype, int param_dtype,
+                             int y_dtype, float eps, void* stream);
+
+/* Bytes of workspace ab200_layer_norm_backward needs when it is asked for parameter gradients. */
+int64_t ab200_layer_norm_workspace_bytes(int64_t rows, int64_t feat);
+
+/*
+ * Its backward.  Replaces layer_norm_backward_kernel (attorch/layer_norm_kernels.py:106-221, launched at
+ * attorch/layer_norm_layer.py:134-144) and the sums over its per-program partial rows (lines 146-149):
+ *     p_ij = (x_ij - mean_i) * inv_std_i,  g_ij = weight_j * dy_ij (dy_ij without weight)
+ *     dx_ij = inv_std_i * (g_ij - (p_ij * sum_j(p_ij g_ij) / feat + sum_j g_ij / feat))
+ *     weight_grad_j = sum_i dy_ij p_ij,  bias_grad_j = sum_i dy_ij      (fp32, fixed order of addition)
+ *   dy      [rows, feat] of dy_dtype (the forward's y_dtype), row pitch lddy
+ *   dx      [rows, feat] of dx_dtype, row pitch lddx: the wider of x_dtype and dy_dtype (the reference
+ *           stores it in the forward's output type and the autograd engine casts, layer_norm_layer.py:117)
+ *   weight_grad, bias_grad  [feat] fp32 or NULL (bias_grad only together with weight_grad; weight_grad
+ *           needs weight); with them, workspace of ab200_layer_norm_workspace_bytes(rows, feat) bytes
+ * One pass over x and dy for rows of up to 8192 elements: the parameter-gradient sums of a thread's
+ * columns stay in its registers over all rows of its block.
+ */
+int ab200_layer_norm_backward(const void* dy, const void* x, const float* mean, const float* inv_std,
+                              const void* weight, void* dx, float* weight_grad, float* bias_grad, int64_t rows,
+                              int64_t feat, int64_t lddy, int64_t ldx, int64_t lddx, int dy_dtype, int x_dtype,
+                              int param_dtype, int dx_dtype, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * In-place SUM all-reduce of a gradient bucket over the GPUs of one NVSwitch domain (one process per
  * GPU), through NVLink multicast: the switch adds the ranks' copies (multimem.ld_reduce) and writes the
  * sums back to all of them (multimem.st); see csrc/allreduce_multimem.cu.  No counterpart in the

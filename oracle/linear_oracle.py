@@ -452,3 +452,52 @@ def cross_entropy_backward(output_grad: Tensor, x: Tensor, target: Tensor, weigh
     else:
         grad = grad / len(x)
     return grad.to(torch.float32 if autocast else x.dtype)
+
+
+def layer_norm_forward(x: Tensor, weight: Optional[Tensor] = None, bias: Optional[Tensor] = None,
+                       eps: float = 1e-5, output_dtype: Optional[torch.dtype] = None
+                       ) -> Tuple[Tensor, Tensor, Tensor]:
+    """
+    layer_norm_forward_kernel (attorch/layer_norm_kernels.py:82-103): the row widened to fp32 (line 84),
+    mean = sum / feat_dim, diff = x - mean, inv_std = rsqrt(sum(diff^2) / feat_dim + eps), output =
+    diff * inv_std, then * weight, then + bias (bias only together with weight, attorch/
+    layer_norm_layer.py:59-60), rounded once by the store.  A 1-D input is one row (attorch/
+    layer_norm_layer.py:51).  Returns (output in output_dtype - the input's dtype unless given -,
+    mean fp32, inv_std fp32).
+    """
+    rows = x.unsqueeze(0) if x.ndim == 1 else x
+    rows = rows.flatten(0, -2).float()
+    feat_dim = rows.shape[1]
+    mean = rows.sum(dim=1) / feat_dim
+    diff = rows - mean[:, None]
+    inv_std = torch.rsqrt((diff * diff).sum(dim=1) / feat_dim + eps)
+    out = diff * inv_std[:, None]
+    if weight is not None:
+        out = out * weight.float()
+        if bias is not None:
+            out = out + bias.float()
+    return out.to(output_dtype or x.dtype).view(x.shape), mean, inv_std
+
+
+def layer_norm_backward(output_grad: Tensor, x: Tensor, mean: Tensor, inv_std: Tensor,
+                        weight: Optional[Tensor] = None, has_bias: bool = False,
+                        grad_dtype: Optional[torch.dtype] = None
+                        ) -> Tuple[Tensor, Optional[Tensor], Optional[Tensor]]:
+    """
+    layer_norm_backward_kernel (attorch/layer_norm_kernels.py:183-221) and the sums after it (attorch/
+    layer_norm_layer.py:146-149): with pre_lin = (x - mean) * inv_std and g = weight * dy (dy without
+    weights), dx = inv_std * (g - (pre_lin * sum(pre_lin * g) / feat_dim + sum(g) / feat_dim));
+    weight_grad = sum over rows of dy * pre_lin, bias_grad = sum over rows of dy, both fp32.  dx is
+    stored in the forward's output dtype (attorch/layer_norm_layer.py:117-118).
+    """
+    rows = (x.unsqueeze(0) if x.ndim == 1 else x).flatten(0, -2).float()
+    dy = output_grad.reshape(rows.shape).float()
+    feat_dim = rows.shape[1]
+    pre_lin = (rows - mean[:, None]) * inv_std[:, None]
+    g = weight.float() * dy if weight is not None else dy
+    term1 = pre_lin * ((pre_lin * g).sum(dim=1) / feat_dim)[:, None]
+    term2 = (g.sum(dim=1) / feat_dim)[:, None]
+    dx = inv_std[:, None] * (g - (term1 + term2))
+    weight_grad = (dy * pre_lin).sum(dim=0) if weight is not None else None
+    bias_grad = dy.sum(dim=0) if (weight is not None and has_bias) else None
+    return dx.to(grad_dtype or output_grad.dtype).view(x.shape), weight_grad, bias_grad

@@ -15,7 +15,8 @@ attorch/glu_kernels.py:13-16 and 56-59).
 Each case is stored as one .npz with the inputs (or the seed that regenerates them plus a
 checksum) and the reference's output, dX, dW and db; the standalone activation layers go into
 act_layers_fp32.npz, the gated linear unit into glu_fp32.npz, bf16 runs of both (element-wise
-kernels only) into elementwise_bf16.npz.  The linear layer itself is not generated in bf16: the
+kernels only) into elementwise_bf16.npz, the cross-entropy loss into cross_entropy_fp32.npz, layer
+normalisation into layer_norm.npz.  The linear layer itself is not generated in bf16: the
 interpreter's bf16 dot product returns garbage.
 """
 
@@ -168,6 +169,7 @@ def main():
     glu_goldens(attorch)
     elementwise_bf16_goldens(attorch)
     cross_entropy_goldens(attorch)
+    layer_norm_goldens(attorch)
 
 
 ACT_LAYERS = [('Sigmoid', {}), ('LogSigmoid', {}), ('Tanh', {}), ('ReLU', {}), ('GELU', {}),
@@ -325,6 +327,65 @@ def cross_entropy_goldens(attorch):
             data[f'dx_{case}_{label}'] = xin.grad.numpy()
     np.savez_compressed(OUT_DIR / 'cross_entropy_fp32.npz', **data)
     print('wrote cross_entropy_fp32.npz')
+
+
+LAYER_NORM_CASES = [
+    # shape, dtype, elementwise_affine, bias, eps
+    ((16,), 'float32', True, True, 1e-5),
+    ((5, 40), 'float32', True, True, 1e-5),
+    ((5, 40), 'float32', True, False, 1e-6),
+    ((5, 40), 'float32', False, False, 1e-5),
+    ((3, 7, 96), 'float32', True, True, 1e-5),
+    ((2049, 2), 'float32', True, True, 1e-5),        # several rows per program in the reference, ragged
+    ((257, 33), 'float32', True, True, 1e-5),
+    ((6, 1100), 'float32', True, True, 1e-5),
+    ((4, 6, 64), 'float16', True, True, 1e-5),
+    ((9, 200), 'float16', True, False, 1e-5),
+    ((9, 200), 'float16', False, False, 1e-6),
+]
+
+
+def layer_norm_goldens(attorch):
+    """
+    The reference's layer normalisation (attorch/layer_norm_layer.py) on fp32 and fp16 inputs: output,
+    input gradient and, with an affine transform, the gradients of weight and bias, for a normal upstream
+    gradient.  Weights and biases are drawn from N(0, 1) as the reference's own test does
+    (tests/test_layer_norm_layer.py:40-49); inputs get an offset and a scale per row so that mean and
+    variance differ between rows.
+    """
+    from attorch.layer_norm_kernels import layer_norm_backward_kernel, layer_norm_forward_kernel
+    layer_norm_forward_kernel.configs = layer_norm_forward_kernel.configs[:1]
+    layer_norm_backward_kernel.configs = layer_norm_backward_kernel.configs[:1]
+    gen = torch.Generator().manual_seed(9)
+    data = {}
+    for case, (shape, dtype_name, affine, bias, eps) in enumerate(LAYER_NORM_CASES):
+        dtype = getattr(torch, dtype_name)
+        rows = int(np.prod(shape[:-1])) if len(shape) > 1 else 1
+        x = torch.randn(shape, generator=gen)
+        if len(shape) > 1:
+            scale = (torch.rand(rows, generator=gen) * 3 + 0.2).view(*shape[:-1], 1)
+            shift = (torch.randn(rows, generator=gen) * 2).view(*shape[:-1], 1)
+            x = x * scale + shift
+        x = x.to(dtype)
+        dy = torch.randn(shape, generator=gen).to(dtype)
+        layer = attorch.LayerNorm(shape[-1], eps, affine, bias, device='cpu', dtype=dtype)
+        if affine:
+            with torch.no_grad():
+                layer.weight.copy_(torch.randn(shape[-1], generator=gen))
+                if bias:
+                    layer.bias.copy_(torch.randn(shape[-1], generator=gen))
+        xin = x.clone().requires_grad_(True)
+        y = layer(xin)
+        y.backward(dy)
+        assert y.dtype is dtype and xin.grad.dtype is dtype
+        data[f'x_{case}'], data[f'dy_{case}'] = to_np(x), to_np(dy)
+        data[f'y_{case}'], data[f'dx_{case}'] = to_np(y), to_np(xin.grad)
+        if affine:
+            data[f'w_{case}'], data[f'dw_{case}'] = to_np(layer.weight), to_np(layer.weight.grad)
+            if bias:
+                data[f'b_{case}'], data[f'db_{case}'] = to_np(layer.bias), to_np(layer.bias.grad)
+    np.savez_compressed(OUT_DIR / 'layer_norm.npz', **data)
+    print('wrote layer_norm.npz')
 
 
 if __name__ == '__main__':

@@ -18,7 +18,7 @@ TOLERANCE = {torch.float32: 1e-2, torch.float16: 1e-2, torch.bfloat16: 1e-2}
 def golden_names(prefix: str = ''):
     """Names of the linear-layer golden cases (the activation-layer and GLU files have their own loaders)."""
     return sorted(p.stem for p in GOLDEN_DIR.glob(f'{prefix}*.npz')
-                  if not p.stem.startswith(('act_layers', 'glu_', 'elementwise_', 'cross_entropy_')))
+                  if not p.stem.startswith(('act_layers', 'glu_', 'elementwise_', 'cross_entropy_', 'layer_norm')))
 
 
 # (module name, constructor arguments, act_func string) in the order of tests/golden/make_golden.py.
@@ -96,3 +96,19 @@ def glu_golden_cases():
 def load_glu_golden():
     raw = np.load(GOLDEN_DIR / 'glu_fp32.npz')
     return {key: torch.from_numpy(raw[key]) for key in raw.files}
+
+
+# (shape, dtype, elementwise_affine, bias, eps) in the order of tests/golden/make_golden.py.
+LAYER_NORM_CASES = [
+    ((16,), 'float32', True, True, 1e-5),
+    ((5, 40), 'float32', True, True, 1e-5),
+    ((5, 40), 'float32', True, False, 1e-6),
+    ((5, 40), 'float32', False, False, 1e-5),
+    ((3, 7, 96), 'float32', True, True, 1e-5),
+    ((2049, 2), 'float32', True, True, 1e-5),
+    ((257, 33), 'float32', True, True, 1e-5),
+    ((6, 1100), 'float32', True, True, 1e-5),
+    ((4, 6, 64), 'float16', True, True, 1e-5),
+    ((9, 200), 'float16', True, False, 1e-5),
+    ((9, 200), 'float16', False, False, 1e-6),
+]

@@ -12,7 +12,8 @@ from attorch_b200 import convert, nn
 def test_namespace_prefers_this_package_and_falls_back_to_torch():
     assert nn.Linear is attorch_b200.Linear
     assert nn.GELU is attorch_b200.GELU and nn.Softshrink is attorch_b200.Softshrink
-    assert nn.Conv2d is torch.nn.Conv2d and nn.LayerNorm is torch.nn.LayerNorm
+    assert nn.LayerNorm is attorch_b200.LayerNorm and nn.CrossEntropyLoss is attorch_b200.CrossEntropyLoss
+    assert nn.Conv2d is torch.nn.Conv2d and nn.BatchNorm2d is torch.nn.BatchNorm2d
     assert nn.Module is torch.nn.Module and nn.Parameter is torch.nn.Parameter
 
 
