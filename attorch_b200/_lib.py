@@ -86,7 +86,7 @@ SIGNATURES = {
                                         _f32, _ptr]),
     'ab200_layer_norm_workspace_bytes': (_i64, [_i64, _i64]),
     'ab200_layer_norm_backward': (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64,
-                                         _int, _int, _int, _int, _ptr, _i64, _ptr]),
+                                         _int, _int, _int, _int, _ptr, _i64, _ptr, _ptr]),
     'ab200_multimem_all_reduce': (_int, [_ptr, _i64, _int, _int, _int, _ptr, _int, _ptr, _ptr]),
     'ab200_collective_flag_bytes': (_i64, []),
 }

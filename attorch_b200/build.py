@@ -10,6 +10,7 @@ import argparse
 import concurrent.futures
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -62,8 +63,40 @@ def is_current() -> bool:
             and STAMP_PATH.read_text().strip() == source_digest())
 
 
-def _compile(nvcc: str, src: Path, verbose: bool) -> Path:
+_INCLUDE_RE = re.compile(r'^\s*#\s*include\s*"([^"]+)"', re.MULTILINE)
+
+
+def _dependencies(src: Path, seen=None) -> set:
+    """The source file and every file of this repository it includes, directly or not."""
+    seen = set() if seen is None else seen
+    if src in seen or not src.exists():
+        return seen
+    seen.add(src)
+    for name in _INCLUDE_RE.findall(src.read_text()):
+        for base in (src.parent, CSRC, INCLUDE):
+            cand = (base / name).resolve()
+            if cand.exists():
+                _dependencies(cand, seen)
+                break
+    return seen
+
+
+def _unit_digest(src: Path) -> str:
+    h = hashlib.sha256()
+    for path in sorted(_dependencies(src.resolve())):
+        h.update(path.name.encode())
+        h.update(path.read_bytes())
+    h.update(' '.join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _compile(nvcc: str, src: Path, verbose: bool, force: bool = False) -> Path:
+    """Compiles one translation unit unless its object is newer than everything it includes."""
     obj = OBJ_DIR / (src.stem + '.o')
+    stamp = OBJ_DIR / (src.stem + '.stamp')
+    digest = _unit_digest(src)
+    if not force and not verbose and obj.exists() and stamp.exists() and stamp.read_text().strip() == digest:
+        return obj
     cmd = [nvcc, *NVCC_FLAGS, f'-I{INCLUDE}', f'-I{CSRC}']
     if verbose:
         cmd += ['-Xptxas', '-v']
@@ -74,6 +107,7 @@ def _compile(nvcc: str, src: Path, verbose: bool) -> Path:
         sys.stderr.write(proc.stderr)
     if proc.returncode != 0:
         raise RuntimeError(f'nvcc failed on {src.name} with exit code {proc.returncode}')
+    stamp.write_text(digest + '\n')
     return obj
 
 
@@ -86,7 +120,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     sources = sorted(CSRC.glob('*.cu'))
     workers = min(len(sources), os.cpu_count() or 1)
     with concurrent.futures.ThreadPoolExecutor(max_workers=workers) as pool:
-        objects = list(pool.map(lambda src: _compile(nvcc, src, verbose), sources))
+        objects = list(pool.map(lambda src: _compile(nvcc, src, verbose, force), sources))
     cmd = [nvcc, *LINK_FLAGS, *[str(o) for o in objects], '-o', str(LIB_PATH)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:

@@ -187,6 +187,7 @@ const char* ab200_error_string(int code) {
     case DEV_TIMEOUT_MMA: return "device: MMA issuer gave up waiting for operands or an accumulator";
     case DEV_TIMEOUT_EPILOGUE: return "device: epilogue gave up waiting for an accumulator";
     case DEV_TIMEOUT_COLLECTIVE: return "device: all-reduce gave up waiting for another rank";
+    case DEV_TIMEOUT_ROW_COPY: return "device: layer normalisation gave up waiting for a row copy into shared memory";
     default: return "unknown code";
   }
 }
@@ -825,7 +826,8 @@ int64_t ab200_layer_norm_workspace_bytes(int64_t rows, int64_t feat) {
 int ab200_layer_norm_backward(const void* dy, const void* x, const float* mean, const float* inv_std,
                               const void* weight, void* dx, float* weight_grad, float* bias_grad, int64_t rows,
                               int64_t feat, int64_t lddy, int64_t ldx, int64_t lddx, int dy_dtype, int x_dtype,
-                              int param_dtype, int dx_dtype, void* workspace, int64_t workspace_bytes, void* stream_) {
+                              int param_dtype, int dx_dtype, void* workspace, int64_t workspace_bytes, int* status,
+                              void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (rows < 0 || feat <= 0) return ERR_BAD_SHAPE;
   if (!fits_int(rows) || !fits_int(feat)) return ERR_TOO_LARGE;
@@ -852,7 +854,7 @@ int ab200_layer_norm_backward(const void* dy, const void* x, const float* mean, 
   }
   const int rc = launch_layer_norm_backward(dy, lddy, x, ldx, mean, inv_std, weight, param_dtype, dx, lddx, weight_grad,
                                             bias_grad, static_cast<float*>(workspace), rows, static_cast<int>(feat),
-                                            dy_dtype, x_dtype, dx_dtype, stream);
+                                            dy_dtype, x_dtype, dx_dtype, status, stream);
   if (rc < 0) return rc;
   g_launches += rc;
   return OK;

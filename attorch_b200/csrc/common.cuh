@@ -37,6 +37,7 @@ enum DeviceStatus : int {
   DEV_TIMEOUT_MMA = 2,
   DEV_TIMEOUT_EPILOGUE = 3,
   DEV_TIMEOUT_COLLECTIVE = 4,
+  DEV_TIMEOUT_ROW_COPY = 5,
 };
 
 template <class T>

@@ -24,30 +24,52 @@
 // the reference (it widens the loaded row, line 84, and the store narrows, line 102).  All sums have a
 // fixed order: results do not depend on scheduling.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace ab200 {
 
 constexpr int kLnCache = 16;   // elements of a row that one thread keeps in registers
 
-// V elements of T starting at p, which is aligned to V * sizeof(T) bytes (4, 8 or 16), as one access.
+// V elements of T as loaded: one scalar, or an 8- or 16-byte word.
+template <class T, int V>
+struct LnRawType {
+  static_assert(V * sizeof(T) == 8 || V * sizeof(T) == 16, "an 8- or 16-byte access");
+  using type = std::conditional_t<V * sizeof(T) == 16, uint4, uint2>;
+};
+template <class T>
+struct LnRawType<T, 1> {
+  using type = T;
+};
+template <class T, int V>
+using LnRaw = typename LnRawType<T, V>::type;
+
+// V elements of T starting at p, which is aligned to V * sizeof(T) bytes, as one access.
+template <class T, int V>
+__device__ __forceinline__ LnRaw<T, V> ln_load_raw(const T* p) {
+  return *reinterpret_cast<const LnRaw<T, V>*>(p);
+}
+
+template <class T, int V>
+__device__ __forceinline__ LnRaw<T, V> ln_zero_raw() {
+  if constexpr (V == 1) return from_f32<T>(0.0f);
+  else if constexpr (V * sizeof(T) == 16) return make_uint4(0u, 0u, 0u, 0u);
+  else return make_uint2(0u, 0u);
+}
+
+template <class T, int V>
+__device__ __forceinline__ void ln_unpack(const LnRaw<T, V>& q, float* v) {
+  const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+  for (int i = 0; i < V; ++i) v[i] = to_f32<T>(e[i]);
+}
+
 template <class T, int V>
 __device__ __forceinline__ void ln_load(const T* p, float* v) {
-  constexpr int kBytes = V * static_cast<int>(sizeof(T));
-  static_assert(V == 1 || kBytes == 8 || kBytes == 16, "one scalar, or an 8- or 16-byte access");
-  if constexpr (V == 1) {
-    v[0] = to_f32<T>(*p);
-  } else if constexpr (kBytes == 16) {
-    const uint4 q = *reinterpret_cast<const uint4*>(p);
-    const T* e = reinterpret_cast<const T*>(&q);
-#pragma unroll
-    for (int i = 0; i < V; ++i) v[i] = to_f32<T>(e[i]);
-  } else {
-    const uint2 q = *reinterpret_cast<const uint2*>(p);
-    const T* e = reinterpret_cast<const T*>(&q);
-#pragma unroll
-    for (int i = 0; i < V; ++i) v[i] = to_f32<T>(e[i]);
-  }
+  const LnRaw<T, V> q = ln_load_raw<T, V>(p);
+  ln_unpack<T, V>(q, v);
 }
 
 template <class T, int V>
@@ -128,7 +150,22 @@ ln_forward_kernel(const TIn* __restrict__ x, long long ldx, const void* __restri
   }
 
   const long long row_blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  // The part of row block rb that this thread keeps, as loaded; zeros past the end of the problem.
+  auto fetch = [&](long long rb, LnRaw<TIn, V> (&dst)[kG]) {
+    const long long r = rb * kRowsPerBlock + slot;
+    const bool ok = rb < row_blocks && r < rows;
+    const TIn* p = x + (ok ? r : 0) * ldx;
+#pragma unroll
+    for (int i = 0; i < kG; ++i) {
+      const int g = t + i * R;
+      dst[i] = (ok && g < groups) ? ln_load_raw<TIn, V>(p + g * V) : ln_zero_raw<TIn, V>();
+    }
+  };
+  LnRaw<TIn, V> cur[kG], nxt[kG];
+  fetch(blockIdx.x, cur);
   for (long long rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {
+    // The next row's loads are in flight while this row is summed, normalised and stored.
+    fetch(rb + gridDim.x, nxt);
     const long long row = rb * kRowsPerBlock + slot;
     const bool live = row < rows;
     const TIn* xr = x + (live ? row : 0) * ldx;
@@ -138,13 +175,7 @@ ln_forward_kernel(const TIn* __restrict__ x, long long ldx, const void* __restri
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < kG; ++i) {
-      const int g = t + i * R;
-      if (live && g < groups) {
-        ln_load<TIn, V>(xr + g * V, &xc[i * V]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < V; ++j) xc[i * V + j] = 0.0f;
-      }
+      ln_unpack<TIn, V>(cur[i], &xc[i * V]);
 #pragma unroll
       for (int j = 0; j < V; ++j) s += xc[i * V + j];
     }
@@ -182,29 +213,31 @@ ln_forward_kernel(const TIn* __restrict__ x, long long ldx, const void* __restri
       mean[row] = mu;
       inv_std[row] = rs;
     }
-    if (!live) continue;      // only in the one-warp-per-row variant, which has no block barrier
-
+    if (live) {
 #pragma unroll
-    for (int i = 0; i < kG; ++i) {
-      const int g = t + i * R;
-      if (g < groups) {
-        float o[V];
+      for (int i = 0; i < kG; ++i) {
+        const int g = t + i * R;
+        if (g < groups) {
+          float o[V];
 #pragma unroll
-        for (int j = 0; j < V; ++j) o[j] = xc[i * V + j] * rs * wc[i * V + j] + bc[i * V + j];
+          for (int j = 0; j < V; ++j) o[j] = xc[i * V + j] * rs * wc[i * V + j] + bc[i * V + j];
+          ln_store<TOut, V>(yr + g * V, o);
+        }
+      }
+      for (int g = t + kG * R; g < groups; g += R) {
+        float v[V], o[V];
+        ln_load<TIn, V>(xr + g * V, v);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float wj = w != nullptr ? load_as_f32(w, param_dtype, g * V + j) : 1.0f;
+          const float bj = b != nullptr ? load_as_f32(b, param_dtype, g * V + j) : 0.0f;
+          o[j] = (v[j] - mu) * rs * wj + bj;
+        }
         ln_store<TOut, V>(yr + g * V, o);
       }
     }
-    for (int g = t + kG * R; g < groups; g += R) {
-      float v[V], o[V];
-      ln_load<TIn, V>(xr + g * V, v);
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const float wj = w != nullptr ? load_as_f32(w, param_dtype, g * V + j) : 1.0f;
-        const float bj = b != nullptr ? load_as_f32(b, param_dtype, g * V + j) : 0.0f;
-        o[j] = (v[j] - mu) * rs * wj + bj;
-      }
-      ln_store<TOut, V>(yr + g * V, o);
-    }
+    for (int i = 0; i < kG; ++i) cur[i] = nxt[i];
   }
 }
 
@@ -243,7 +276,29 @@ ln_backward_kernel(const TDy* __restrict__ dy, long long lddy, const TIn* __rest
   }
 
   const long long row_blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  // The parts of x and dy of row block rb that this thread keeps, as loaded; zeros past the end.
+  auto fetch = [&](long long rb, LnRaw<TIn, V> (&xdst)[kG], LnRaw<TDy, V> (&gdst)[kG]) {
+    const long long r = rb * kRowsPerBlock + slot;
+    const bool ok = rb < row_blocks && r < rows;
+    const TIn* px = x + (ok ? r : 0) * ldx;
+    const TDy* pg = dy + (ok ? r : 0) * lddy;
+#pragma unroll
+    for (int i = 0; i < kG; ++i) {
+      const int g = t + i * R;
+      const bool in = ok && g < groups;
+      xdst[i] = in ? ln_load_raw<TIn, V>(px + g * V) : ln_zero_raw<TIn, V>();
+      gdst[i] = in ? ln_load_raw<TDy, V>(pg + g * V) : ln_zero_raw<TDy, V>();
+    }
+  };
+  // With 512 threads (at most 128 registers each) the sums of the parameter gradients leave no room for
+  // a second row.
+  constexpr bool kPrefetch = !(R == 512 && kParams);
+  LnRaw<TIn, V> xcur[kG], xnxt[kPrefetch ? kG : 1];
+  LnRaw<TDy, V> gcur[kG], gnxt[kPrefetch ? kG : 1];
+  fetch(blockIdx.x, xcur, gcur);
   for (long long rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {
+    // The next row's loads are in flight while this row is reduced and its gradient stored.
+    if constexpr (kPrefetch) fetch(rb + gridDim.x, xnxt, gnxt);
     const long long row = rb * kRowsPerBlock + slot;
     const bool live = row < rows;
     const TIn* xr = x + (live ? row : 0) * ldx;
@@ -257,9 +312,9 @@ ln_backward_kernel(const TDy* __restrict__ dy, long long lddy, const TIn* __rest
 #pragma unroll
     for (int i = 0; i < kG; ++i) {
       const int g = t + i * R;
+      ln_unpack<TIn, V>(xcur[i], &pc[i * V]);
+      ln_unpack<TDy, V>(gcur[i], &gc[i * V]);
       if (live && g < groups) {
-        ln_load<TIn, V>(xr + g * V, &pc[i * V]);
-        ln_load<TDy, V>(gr + g * V, &gc[i * V]);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           const int e = i * V + j;
@@ -273,9 +328,6 @@ ln_backward_kernel(const TDy* __restrict__ dy, long long lddy, const TIn* __rest
           s1 += p * gc[e];
           s2 += gc[e];
         }
-      } else {
-#pragma unroll
-        for (int j = 0; j < V; ++j) pc[i * V + j] = gc[i * V + j] = 0.0f;
       }
     }
     if (live) {
@@ -294,29 +346,38 @@ ln_backward_kernel(const TDy* __restrict__ dy, long long lddy, const TIn* __rest
     }
     const float2 sums = ln_group_sum<R, kThreads>(s1, s2, scratch, phase);
     const float c1 = sums.x / feat, c2 = sums.y / feat;
-    if (!live) continue;
-
+    if (live) {
 #pragma unroll
-    for (int i = 0; i < kG; ++i) {
-      const int g = t + i * R;
-      if (g < groups) {
-        float o[V];
+      for (int i = 0; i < kG; ++i) {
+        const int g = t + i * R;
+        if (g < groups) {
+          float o[V];
 #pragma unroll
-        for (int j = 0; j < V; ++j) o[j] = rs * (gc[i * V + j] - (pc[i * V + j] * c1 + c2));
+          for (int j = 0; j < V; ++j) o[j] = rs * (gc[i * V + j] - (pc[i * V + j] * c1 + c2));
+          ln_store<TDx, V>(dr + g * V, o);
+        }
+      }
+      for (int g = t + kG * R; g < groups; g += R) {
+        float xv[V], gv[V], o[V];
+        ln_load<TIn, V>(xr + g * V, xv);
+        ln_load<TDy, V>(gr + g * V, gv);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float wj = w != nullptr ? load_as_f32(w, param_dtype, g * V + j) : 1.0f;
+          const float p = (xv[j] - mu) * rs;
+          o[j] = rs * (wj * gv[j] - (p * c1 + c2));
+        }
         ln_store<TDx, V>(dr + g * V, o);
       }
     }
-    for (int g = t + kG * R; g < groups; g += R) {
-      float xv[V], gv[V], o[V];
-      ln_load<TIn, V>(xr + g * V, xv);
-      ln_load<TDy, V>(gr + g * V, gv);
+    if constexpr (kPrefetch) {
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const float wj = w != nullptr ? load_as_f32(w, param_dtype, g * V + j) : 1.0f;
-        const float p = (xv[j] - mu) * rs;
-        o[j] = rs * (wj * gv[j] - (p * c1 + c2));
+      for (int i = 0; i < kG; ++i) {
+        xcur[i] = xnxt[i];
+        gcur[i] = gnxt[i];
       }
-      ln_store<TDx, V>(dr + g * V, o);
+    } else {
+      fetch(rb + gridDim.x, xcur, gcur);
     }
   }
 
@@ -330,6 +391,196 @@ ln_backward_kernel(const TDy* __restrict__ dy, long long lddy, const TIn* __rest
         for (int j = 0; j < V; ++j) {
           wpart[part * F + g * V + j] = wacc[i * V + j];
           if (bpart != nullptr) bpart[part * F + g * V + j] = bacc[i * V + j];
+        }
+      }
+    }
+  }
+}
+
+constexpr int kLnMaxStages = 16;     // rows in flight per block of the staged backward kernel
+constexpr int kLnStatChunk = 64;     // row statistics fetched at a time
+
+// The backward pass with rows staged in shared memory: one or two blocks of R threads per SM; one thread keeps
+// `stages` rows of x and dy (the rows blockIdx.x, blockIdx.x + gridDim.x, ...) in flight as untiled bulk
+// copies, each pair completing on its stage's mbarrier, so the bytes in flight do not depend on how many
+// registers or warps the block has - the register variant above, with one row ahead, stops near half of
+// the HBM bandwidth.  Every thread then takes its columns of the row from shared memory; the arithmetic
+// and the order of every sum are those of ln_backward_kernel.  The block barrier inside the row sums
+// doubles as the signal that a stage has been read and may be refilled.  Requires 16-byte aligned rows,
+// F % 8 == 0 and F <= kLnCache * R.  A wait on a stage has a time limit; when it runs out the block stores
+// DEV_TIMEOUT_ROW_COPY in *status, waits (with the same limit) for its copies still in flight and returns.
+template <class TIn, class TDy, class TDx, int R, bool kParams>
+__global__ void __launch_bounds__(R, R <= 256 ? 2 : 1)
+ln_backward_staged_kernel(const TDy* __restrict__ dy, long long lddy, const TIn* __restrict__ x, long long ldx,
+                          const float* __restrict__ mean, const float* __restrict__ inv_std,
+                          const void* __restrict__ w, int param_dtype, TDx* __restrict__ dx, long long lddx,
+                          float* __restrict__ wpart, float* __restrict__ bpart, long long rows, int F, int stages,
+                          int* status) {
+  constexpr int V = 16 / LnMax<LnMax<sizeof(TIn), sizeof(TDy)>::value, sizeof(TDx)>::value;
+  constexpr int kG = kLnCache / V;
+  extern __shared__ __align__(128) unsigned char ln_stage_smem[];
+  __shared__ __align__(8) uint64_t full[kLnMaxStages];
+  __shared__ float2 scratch[2][R / 32];
+  __shared__ float stat_mean[kLnStatChunk], stat_rs[kLnStatChunk];
+  int phase = 0;
+  const int t = threadIdx.x;
+  const int groups = F / V;
+  const float feat = static_cast<float>(F);
+  const uint32_t xbytes = static_cast<uint32_t>(F) * sizeof(TIn), gbytes = static_cast<uint32_t>(F) * sizeof(TDy);
+  const uint32_t stage_bytes = xbytes + gbytes;
+  // Rows of this block: blockIdx.x + k * gridDim.x, k < n (the grid has at most `rows` blocks).
+  const long long n = (rows - blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+  if (t == 0) {
+    for (int s = 0; s < stages; ++s) ptx::mbar_init(ptx::smem_u32(&full[s]), 1);
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  auto issue = [&](long long k, int s) {
+    const long long row = blockIdx.x + k * gridDim.x;
+    const uint32_t bar = ptx::smem_u32(&full[s]);
+    const uint32_t dst = ptx::smem_u32(ln_stage_smem + static_cast<size_t>(s) * stage_bytes);
+    ptx::mbar_arrive_expect_tx(bar, stage_bytes);
+    ptx::bulk_load(dst, x + row * ldx, xbytes, bar);
+    ptx::bulk_load(dst + xbytes, dy + row * lddy, gbytes, bar);
+  };
+  // A wait with a time limit.
+  auto wait = [&](int s, uint32_t parity) -> bool {
+    const uint32_t bar = ptx::smem_u32(&full[s]);
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+      if ((++spins & 0x3FFu) == 0) {
+        const uint64_t now = ptx::globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > ptx::kWaitLimitNs) return false;
+      }
+    }
+    return true;
+  };
+  if (t == 0) {
+    for (int k = 0; k < stages && k < n; ++k) issue(k, k);
+  }
+
+  float wc[kLnCache];
+#pragma unroll
+  for (int i = 0; i < kG; ++i) {
+    const int g = t + i * R;
+#pragma unroll
+    for (int j = 0; j < V; ++j)
+      wc[i * V + j] = (w != nullptr && g < groups) ? load_as_f32(w, param_dtype, g * V + j) : 1.0f;
+  }
+  float wacc[kParams ? kLnCache : 1], bacc[kParams ? kLnCache : 1];
+  if constexpr (kParams) {
+#pragma unroll
+    for (int i = 0; i < kLnCache; ++i) wacc[i] = bacc[i] = 0.0f;
+  }
+
+  long long failed_at = -1;
+  int stage_index = 0, stat_index = 0;       // k % stages, k % kLnStatChunk
+  uint32_t stage_parity = 0;                  // (k / stages) & 1
+  for (long long k = 0; k < n; ++k) {
+    if (stat_index == 0) {
+      // Every thread read its statistics of the previous chunk before the last row-sum barrier.
+      for (int i = t; i < kLnStatChunk && k + i < n; i += R) {
+        const long long r = blockIdx.x + (k + i) * gridDim.x;
+        stat_mean[i] = mean[r];
+        stat_rs[i] = inv_std[r];
+      }
+      __syncthreads();
+    }
+    const long long row = blockIdx.x + k * gridDim.x;
+    const float mu = stat_mean[stat_index], rs = stat_rs[stat_index];
+    const bool ok = wait(stage_index, stage_parity);
+    const unsigned char* stage = ln_stage_smem + static_cast<size_t>(stage_index) * stage_bytes;
+
+    float pc[kLnCache], gc[kLnCache];
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kG; ++i) {
+      const int g = t + i * R;
+      if (g < groups) {
+        const LnRaw<TIn, V> xq = *reinterpret_cast<const LnRaw<TIn, V>*>(stage + static_cast<size_t>(g) * V * sizeof(TIn));
+        const LnRaw<TDy, V> gq =
+            *reinterpret_cast<const LnRaw<TDy, V>*>(stage + xbytes + static_cast<size_t>(g) * V * sizeof(TDy));
+        ln_unpack<TIn, V>(xq, &pc[i * V]);
+        ln_unpack<TDy, V>(gq, &gc[i * V]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const int e = i * V + j;
+          const float p = (pc[e] - mu) * rs;
+          pc[e] = p;
+          if constexpr (kParams) {
+            wacc[e] += gc[e] * p;
+            bacc[e] += gc[e];
+          }
+          gc[e] *= wc[e];
+          s1 += p * gc[e];
+          s2 += gc[e];
+        }
+      }
+    }
+    // Row sums over the block; the barrier also tells whether any thread's wait ran out.
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, off);
+      s2 += __shfl_xor_sync(0xFFFFFFFFu, s2, off);
+    }
+    if ((t & 31) == 0) scratch[phase][t >> 5] = make_float2(s1, s2);
+    if (__syncthreads_or(ok ? 0 : 1)) {
+      failed_at = k;
+      break;
+    }
+    s1 = 0.0f;
+    s2 = 0.0f;
+#pragma unroll
+    for (int wi = 0; wi < R / 32; ++wi) {
+      s1 += scratch[phase][wi].x;
+      s2 += scratch[phase][wi].y;
+    }
+    phase ^= 1;
+    // All threads have read this stage: refill it.
+    if (t == 0 && k + stages < n) issue(k + stages, stage_index);
+    const float c1 = s1 / feat, c2 = s2 / feat;
+    TDx* dr = dx + row * lddx;
+#pragma unroll
+    for (int i = 0; i < kG; ++i) {
+      const int g = t + i * R;
+      if (g < groups) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) o[j] = rs * (gc[i * V + j] - (pc[i * V + j] * c1 + c2));
+        ln_store<TDx, V>(dr + g * V, o);
+      }
+    }
+    stat_index = stat_index + 1 == kLnStatChunk ? 0 : stat_index + 1;
+    if (++stage_index == stages) {
+      stage_index = 0;
+      stage_parity ^= 1u;
+    }
+  }
+
+  if (failed_at >= 0 && t == 0) {
+    atomicCAS(status, 0, DEV_TIMEOUT_ROW_COPY);
+    // Copies issued and not consumed: rows failed_at ... failed_at + stages - 1 (those below n), in the
+    // stages from stage_index on.
+    for (long long k = failed_at; k < failed_at + stages && k < n; ++k) {
+      wait(stage_index, stage_parity);
+      if (++stage_index == stages) {
+        stage_index = 0;
+        stage_parity ^= 1u;
+      }
+    }
+  }
+  if constexpr (kParams) {
+#pragma unroll
+    for (int i = 0; i < kG; ++i) {
+      const int g = t + i * R;
+      if (g < groups) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          wpart[static_cast<long long>(blockIdx.x) * F + g * V + j] = wacc[i * V + j];
+          if (bpart != nullptr) bpart[static_cast<long long>(blockIdx.x) * F + g * V + j] = bacc[i * V + j];
         }
       }
     }

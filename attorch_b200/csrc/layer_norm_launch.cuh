@@ -9,13 +9,14 @@ namespace ab200 {
 // a [rows, F] problem writes.
 long long layer_norm_parts(long long rows, long long F);
 
-// Both return the number of kernels launched, or a negative Status.
+// Both return the number of kernels launched, or a negative Status.  status: device word for a bounded wait
+// that ran out, or NULL (then rows are not staged in shared memory).
 int launch_layer_norm_forward(const void* x, long long ldx, const void* w, const void* b, int param_dtype,
                               float* mean, float* inv_std, void* y, long long ldy, long long rows, int F,
                               int x_dtype, int y_dtype, float eps, cudaStream_t stream);
 int launch_layer_norm_backward(const void* dy, long long lddy, const void* x, long long ldx, const float* mean,
                                const float* inv_std, const void* w, int param_dtype, void* dx, long long lddx,
                                float* weight_grad, float* bias_grad, float* workspace, long long rows, int F,
-                               int dy_dtype, int x_dtype, int dx_dtype, cudaStream_t stream);
+                               int dy_dtype, int x_dtype, int dx_dtype, int* status, cudaStream_t stream);
 
 }  // namespace ab200

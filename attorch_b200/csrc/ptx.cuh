@@ -96,6 +96,15 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 // Longest time one mbarrier wait may take before a kernel gives up (nanoseconds of %globaltimer).
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
+// Untiled bulk copy global -> shared of `bytes` bytes (a multiple of 16; both addresses 16-byte
+// aligned), completion counted as transaction bytes on an mbarrier of this CTA.  No multicast.
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_dst),
+               "l"(gmem_src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
 // ----------------------------------------------------------------------------------------------
 // TMA: 2-D tiled bulk tensor load, global -> shared, completion on an mbarrier.  No multicast.
 // ----------------------------------------------------------------------------------------------

@@ -15,7 +15,8 @@ import torch
 from torch import Tensor, nn
 
 from . import _lib
-from .linear_layer import Linear, _dtype_id, _ptr, _require_cuda, get_output_dtype as linear_output_dtype
+from .linear_layer import (Linear, _dtype_id, _ptr, _require_cuda, _stream_scratch,
+                           get_output_dtype as linear_output_dtype)
 
 
 def get_norm_dtype(input_dtype: torch.dtype, autocast_to_fp32: bool) -> torch.dtype:
@@ -123,7 +124,8 @@ class LayerNormAutoGrad(torch.autograd.Function):
                 flattened_input.stride(0) if batch_dim > 1 else feat_dim, feat_dim,
                 _dtype_id(grad.dtype), _dtype_id(flattened_input.dtype),
                 _dtype_id(weight.dtype) if weight is not None else 0, _dtype_id(grad_dtype),
-                _ptr(workspace), ws_bytes, stream), 'ab200_layer_norm_backward')
+                _ptr(workspace), ws_bytes, _ptr(_stream_scratch(device)['status']), stream),
+                'ab200_layer_norm_backward')
         # One slot per forward argument (attorch/layer_norm_layer.py:151-153 pads with None).
         return input_grad.view(ctx.input_shape), weight_grad, bias_grad, None, None, None
 

@@ -600,6 +600,7 @@ def layer_norm(args, device):
     stats = torch.empty(2, rows, device=device)
     pgrad = torch.empty(2, feat, device=device)
     ws = torch.empty(lib.ab200_layer_norm_workspace_bytes(rows, feat), dtype=torch.uint8, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
     results = {}
     # Three sets of buffers per case, used in turn: 3 * (64 ... 128 MiB) per tensor is larger than L2.
     for name, xdt, ydt in (('fp32_fp32', torch.float32, torch.float32), ('fp32_bf16', torch.float32, torch.bfloat16),
@@ -623,13 +624,15 @@ def layer_norm(args, device):
                                                      stats[1].data_ptr(), w.data_ptr(), dxs[i].data_ptr(),
                                                      pgrad[0].data_ptr(), pgrad[1].data_ptr(), rows, feat, feat, feat,
                                                      feat, ids[ydt], ids[xdt], _lib.F32, ids[xdt], ws.data_ptr(),
-                                                     ws.numel(), stream), 'ab200_layer_norm_backward')
+                                                     ws.numel(), status.data_ptr(), stream),
+                       'ab200_layer_norm_backward')
 
         xe, ye = xs[0].element_size(), ys[0].element_size()
         for kind, fn, nbytes in (('forward', forward, n * (xe + ye)), ('backward', backward, n * (2 * xe + ye))):
             ms = event_time(fn, args.steps, max(args.warmup, 3))
             results[f'{name}_{kind}'] = {'us': round(ms * 1e3, 2), 'gbs': round(nbytes / (ms * 1e-3) / 1e9, 1)}
         del xs, ys, dys, dxs
+    assert int(status.item()) == 0, 'a layer-normalisation kernel gave up on a wait'
     attorch_b200.check_status()
 
     # The block: LayerNorm -> Linear(gelu) under bf16 autocast, forward + backward, fp32 parameters and input.

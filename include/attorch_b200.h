@@ -53,6 +53,7 @@ extern "C" {
 #define AB200_DEV_TIMEOUT_MMA 2
 #define AB200_DEV_TIMEOUT_EPILOGUE 3
 #define AB200_DEV_TIMEOUT_COLLECTIVE 4
+#define AB200_DEV_TIMEOUT_ROW_COPY 5
 
 /* Activation ids: the act_func strings of attorch/linear_layer.py:42-49 in the order of the
  * dispatcher attorch/act_kernels.py:654-727.  Ids 17..21 take `act_param`. */
@@ -417,13 +418,17 @@ int64_t ab200_layer_norm_workspace_bytes(int64_t rows, int64_t feat);
  *           stores it in the forward's output type and the autograd engine casts, layer_norm_layer.py:117)
  *   weight_grad, bias_grad  [feat] fp32 or NULL (bias_grad only together with weight_grad; weight_grad
  *           needs weight); with them, workspace of ab200_layer_norm_workspace_bytes(rows, feat) bytes
+ *   status  device word as for the GEMM entry points, or NULL.  With it, aligned rows of 520 ... 8192
+ *           elements are staged in shared memory by bulk copies that wait on mbarriers with a time limit;
+ *           a wait that runs out stores AB200_DEV_TIMEOUT_ROW_COPY.  Without it they go through registers.
  * One pass over x and dy for rows of up to 8192 elements: the parameter-gradient sums of a thread's
  * columns stay in its registers over all rows of its block.
  */
 int ab200_layer_norm_backward(const void* dy, const void* x, const float* mean, const float* inv_std,
                               const void* weight, void* dx, float* weight_grad, float* bias_grad, int64_t rows,
                               int64_t feat, int64_t lddy, int64_t ldx, int64_t lddx, int dy_dtype, int x_dtype,
-                              int param_dtype, int dx_dtype, void* workspace, int64_t workspace_bytes, void* stream);
+                              int param_dtype, int dx_dtype, void* workspace, int64_t workspace_bytes, int* status,
+                              void* stream);
 
 /*
  * In-place SUM all-reduce of a gradient bucket over the GPUs of one NVSwitch domain (one process per

@@ -268,10 +268,54 @@ def test_c_abi_argument_checks():
     back = lib.ab200_layer_norm_backward
     assert back(x.data_ptr(), x.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(), x.data_ptr(), x.data_ptr(),
                 x.data_ptr(), None, 4, 64, 64, 64, 64, _lib.F32, _lib.F32, _lib.F32, _lib.F32, x.data_ptr(), 16,
-                stream) == -6                                                      # workspace too small
+                None, stream) == -6                                                      # workspace too small
     assert back(x.data_ptr(), x.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(), x.data_ptr(), x.data_ptr(),
                 None, None, 4, 64, 64, 64, 64, _lib.F16, _lib.F32, _lib.F32, _lib.F16, None, 0,
-                stream) == -3                                                      # dx narrower than x
+                None, stream) == -3                                                      # dx narrower than x
     assert lib.ab200_launch_count() == before
     assert lib.ab200_layer_norm_workspace_bytes(0, 64) == 4
     assert lib.ab200_layer_norm_workspace_bytes(8192, 4096) % (2 * 4096 * 4) == 0
+
+
+@pytest.mark.parametrize('rows,feat', [(300, 1024), (150, 4096), (40, 8192)])
+@pytest.mark.parametrize('x_dtype,dy_dtype', [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                              (torch.bfloat16, torch.bfloat16), (torch.float16, torch.float32)],
+                         ids=['f32', 'f32_bf16', 'bf16', 'f16_f32'])
+def test_staged_and_register_backward_agree(rows, feat, x_dtype, dy_dtype):
+    """
+    The backward pass with rows staged in shared memory (a status word is given) and the one that keeps
+    rows in registers (no status word) do the same arithmetic with different thread-to-column maps: equal
+    up to the order of the row sums.  Both against the oracle.
+    """
+    from attorch_b200 import _lib
+    lib = _lib.load()
+    ids = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+    gen = torch.Generator().manual_seed(rows + feat)
+    x = (torch.randn(rows, feat, generator=gen) * 2 + 0.7).to(x_dtype)
+    dy = torch.randn(rows, feat, generator=gen).to(dy_dtype)
+    w = torch.randn(feat, generator=gen)
+    dx_dtype = torch.float32 if torch.float32 in (x_dtype, dy_dtype) else x_dtype
+    _, mean, inv_std = oracle.layer_norm_forward(x, w, None)
+    edx, edw, edb = oracle.layer_norm_backward(dy, x, mean, inv_std, w, True, grad_dtype=dx_dtype)
+    xg, dyg, wg, stats = x.cuda(), dy.cuda(), w.cuda(), torch.stack([mean, inv_std]).cuda()
+    ws = torch.empty(lib.ab200_layer_norm_workspace_bytes(rows, feat), dtype=torch.uint8, device='cuda')
+    status = torch.zeros(1, dtype=torch.int32, device='cuda')
+    stream = torch.cuda.current_stream().cuda_stream
+    outs = []
+    for status_ptr in (status.data_ptr(), None):
+        dx = torch.empty(rows, feat, dtype=dx_dtype, device='cuda')
+        pg = torch.empty(2, feat, device='cuda')
+        _lib.check(lib.ab200_layer_norm_backward(
+            dyg.data_ptr(), xg.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(), wg.data_ptr(), dx.data_ptr(),
+            pg[0].data_ptr(), pg[1].data_ptr(), rows, feat, feat, feat, feat, ids[dy_dtype], ids[x_dtype], _lib.F32,
+            ids[dx_dtype], ws.data_ptr(), ws.numel(), status_ptr, stream), 'ab200_layer_norm_backward')
+        torch.cuda.synchronize()
+        outs.append((dx.cpu(), pg[0].cpu(), pg[1].cpu()))
+    assert int(status.item()) == 0
+    scale = max(1.0, float(inv_std.max() * w.abs().max() * dy.float().abs().max()))
+    for dx, dw, db in outs:
+        torch.testing.assert_close(dx.float(), edx.float(), rtol=TOL[dx_dtype]['rtol'], atol=TOL[dx_dtype]['atol'] * scale)
+        torch.testing.assert_close(dw, edw, rtol=1e-4, atol=1e-4 * max(1.0, float(edw.abs().max())))
+        torch.testing.assert_close(db, edb, rtol=1e-4, atol=1e-4 * max(1.0, float(edb.abs().max())))
+    torch.testing.assert_close(outs[0][0].float(), outs[1][0].float(), rtol=TOL[dx_dtype]['rtol'],
+                               atol=TOL[dx_dtype]['atol'] * scale)
