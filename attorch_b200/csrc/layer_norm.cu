@@ -125,7 +125,7 @@ int backward_typed(const void* dy, long long lddy, const void* x, long long ldx,
     if (!ok || cudaGetLastError() != cudaSuccess) return ERR_LAUNCH;
     ++launches;
     if (!want_params) return launches;
-    ln_param_finish_kernel<<<dim3((F + 255) / 256, 2), 256, 0, stream>>>(wpart, bpart, static_cast<int>(parts), F,
+    ln_param_finish_kernel<<<dim3((F + kLnFinishCols - 1) / kLnFinishCols, 2), kLnFinishCols * kLnFinishSlices, 0, stream>>>(wpart, bpart, static_cast<int>(parts), F,
                                                                         weight_grad, bias_grad);
     ++launches;
     return cudaGetLastError() == cudaSuccess ? launches : ERR_LAUNCH;
@@ -165,7 +165,7 @@ int backward_typed(const void* dy, long long lddy, const void* x, long long ldx,
     ++launches;
     if (cudaGetLastError() != cudaSuccess) return ERR_LAUNCH;
   }
-  ln_param_finish_kernel<<<dim3((F + 255) / 256, 2), 256, 0, stream>>>(wpart, bpart, static_cast<int>(parts), F,
+  ln_param_finish_kernel<<<dim3((F + kLnFinishCols - 1) / kLnFinishCols, 2), kLnFinishCols * kLnFinishSlices, 0, stream>>>(wpart, bpart, static_cast<int>(parts), F,
                                                                       weight_grad, bias_grad);
   ++launches;
   return cudaGetLastError() == cudaSuccess ? launches : ERR_LAUNCH;

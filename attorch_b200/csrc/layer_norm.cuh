@@ -609,26 +609,39 @@ ln_param_grad_kernel(const TDy* __restrict__ dy, long long lddy, const TIn* __re
   if (bpart != nullptr) bpart[static_cast<long long>(blockIdx.y) * F + col] = ba;
 }
 
-// weight_grad[j] = sum over the partial rows of wpart[., j], in order; the same for the bias.
-__global__ void __launch_bounds__(256)
+// weight_grad[j] = sum over the partial rows of wpart[., j]; the same for the bias (blockIdx.y = 1).
+// A block takes 32 columns; its 32 warps each add every 32nd partial row (four interleaved sums, so four
+// loads in flight), then one warp adds the 32 results in order.  The order is fixed.
+constexpr int kLnFinishCols = 32, kLnFinishSlices = 32;
+
+__global__ void __launch_bounds__(kLnFinishCols * kLnFinishSlices)
 ln_param_finish_kernel(const float* __restrict__ wpart, const float* __restrict__ bpart, int parts, int F,
                        float* __restrict__ weight_grad, float* __restrict__ bias_grad) {
-  const int col = blockIdx.x * 256 + threadIdx.x;
-  if (col >= F) return;
+  __shared__ float red[kLnFinishSlices][kLnFinishCols + 1];
   const float* src = blockIdx.y == 0 ? wpart : bpart;
   float* dst = blockIdx.y == 0 ? weight_grad : bias_grad;
   if (dst == nullptr) return;
-  // Four interleaved sums keep four loads in flight; the order is still fixed.
+  const int c = threadIdx.x % kLnFinishCols, slice = threadIdx.x / kLnFinishCols;
+  const int col = blockIdx.x * kLnFinishCols + c;
   float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-  int p = 0;
-  for (; p + 4 <= parts; p += 4) {
-    a0 += src[static_cast<long long>(p) * F + col];
-    a1 += src[static_cast<long long>(p + 1) * F + col];
-    a2 += src[static_cast<long long>(p + 2) * F + col];
-    a3 += src[static_cast<long long>(p + 3) * F + col];
+  if (col < F) {
+    int p = slice;
+    for (; p + 3 * kLnFinishSlices < parts; p += 4 * kLnFinishSlices) {
+      a0 += src[static_cast<long long>(p) * F + col];
+      a1 += src[static_cast<long long>(p + kLnFinishSlices) * F + col];
+      a2 += src[static_cast<long long>(p + 2 * kLnFinishSlices) * F + col];
+      a3 += src[static_cast<long long>(p + 3 * kLnFinishSlices) * F + col];
+    }
+    for (; p < parts; p += kLnFinishSlices) a0 += src[static_cast<long long>(p) * F + col];
   }
-  for (; p < parts; ++p) a0 += src[static_cast<long long>(p) * F + col];
-  dst[col] = (a0 + a1) + (a2 + a3);
+  red[slice][c] = (a0 + a1) + (a2 + a3);
+  __syncthreads();
+  if (slice == 0 && col < F) {
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kLnFinishSlices; ++i) total += red[i][c];
+    dst[col] = total;
+  }
 }
 
 }  // namespace ab200
