@@ -82,6 +82,8 @@ SIGNATURES = {
                                            _ptr, _i64, _ptr]),
     'ab200_cross_entropy_backward': (_int, [_ptr, _int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64,
                                             _i64, _int, _int, _int, _ptr]),
+    'ab200_linear_backward_input_fused': (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                                                 _int, _int, _ptr, _ptr]),
     'ab200_layer_norm_forward': (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _int, _int,
                                         _f32, _ptr]),
     'ab200_layer_norm_workspace_bytes': (_i64, [_i64, _i64]),

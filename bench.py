@@ -673,6 +673,77 @@ def layer_norm(args, device):
           flush=True)
 
 
+def fused_input_gradient(args, device):
+    """
+    The input gradient of the C2 layer, dX[8192, 4096] = (dY (.) act'(Z))[8192, 4096] * W^T, two ways: the
+    layer's path (ab200_act_backward writes dZ and the bias gradient, ab200_linear_backward_input multiplies)
+    and ab200_linear_backward_input_fused, which forms dZ in the operand path (products written to tensor
+    memory as the A operand) and has no bias gradient.  Reports the time of each and whether the results
+    agree bit for bit.
+    """
+    from attorch_b200 import _lib
+    lib = _lib.load()
+    peaks, peak_source = measured_peaks()
+    M, K, N = (args.tokens or 8192), 4096, 4096
+    dy = (torch.randn(M, N, device=device) * 0.01).bfloat16()
+    d = torch.rand(M, N, device=device).mul_(1.1).half()
+    w = (torch.randn(K, N, device=device) / N ** 0.5).bfloat16()
+    dz = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+    db = torch.empty(N, dtype=torch.float32, device=device)
+    ws = torch.empty(max(lib.ab200_act_backward_workspace_bytes(M, N), 16), dtype=torch.uint8, device=device)
+    gws_bytes = max(lib.ab200_gemm_workspace_bytes(M, K, N), 16)
+    gws = torch.empty(gws_bytes, dtype=torch.uint8, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    stream = torch.cuda.current_stream().cuda_stream
+    flags = _lib.FLAG_FORCE_TCGEN05 | _lib.FLAG_NO_STREAMK
+    results = {}
+    for label, dx_dtype, dx_id in (('bf16_out', torch.bfloat16, _lib.BF16), ('fp32_out', torch.float32, _lib.F32)):
+        dx_two = torch.empty(M, K, dtype=dx_dtype, device=device)
+        dx_one = torch.empty(M, K, dtype=dx_dtype, device=device)
+
+        def act_bwd():
+            _lib.check(lib.ab200_act_backward(dy.data_ptr(), d.data_ptr(), dz.data_ptr(), db.data_ptr(), M, N, N, N, N,
+                                              _lib.BF16, _lib.F32, _lib.ACT_SAVED_DERIVATIVE_F16, 0.0, ws.data_ptr(),
+                                              ws.numel(), stream), 'ab200_act_backward')
+
+        def product():
+            _lib.check(lib.ab200_linear_backward_input(dz.data_ptr(), w.data_ptr(), dx_two.data_ptr(), M, K, N, N, 1, N, 1,
+                                                       K, _lib.BF16, dx_id, gws.data_ptr(), gws_bytes,
+                                                       status.data_ptr(), stream, flags), 'ab200_linear_backward_input')
+
+        def two_kernels():
+            act_bwd()
+            product()
+
+        def fused():
+            _lib.check(lib.ab200_linear_backward_input_fused(dy.data_ptr(), d.data_ptr(), w.data_ptr(), dx_one.data_ptr(),
+                                                             M, K, N, N, N, N, K, _lib.F16, dx_id, status.data_ptr(),
+                                                             stream), 'ab200_linear_backward_input_fused')
+
+        two_kernels()
+        fused()
+        torch.cuda.synchronize()
+        code = int(status.item())
+        assert code == 0, f'device status {code}'
+        diff = (dx_one.float() - dx_two.float()).abs().max().item()
+        entry = {'bit_equal': bool(torch.equal(dx_one, dx_two)), 'max_abs_diff': diff,
+                 'max_abs': dx_two.float().abs().max().item()}
+        for name, fn in (('act_backward_us', act_bwd), ('product_us', product), ('two_kernels_us', two_kernels),
+                         ('fused_us', fused)):
+            entry[name] = round(event_time(fn, args.steps, max(args.warmup, 3)) * 1e3, 2)
+        entry['fused_tflops'] = round(2.0 * M * K * N / (entry['fused_us'] * 1e-6) / 1e12, 1)
+        results[label] = entry
+        del dx_two, dx_one
+    assert int(status.item()) == 0, 'a kernel gave up on a wait'
+    best = results['bf16_out']['fused_tflops']
+    print(json.dumps({'metric': 'fused_input_gradient_tflops', 'value': best, 'unit': 'TFLOP/s', 'n_gpus': 1,
+                      'steps': args.steps, 'warmup': args.warmup, 'higher_is_better': True, 'dtype': 'bf16',
+                      'data': 'synthetic', 'config': {'workload': 'dxfused', 'shape': [M, K, N], **results},
+                      'roofline': {'bound': 'tensor', 'achieved': best, 'peak': peaks['bf16_tflops'], 'unit': 'TFLOP/s',
+                                   'frac': best / peaks['bf16_tflops'], 'traffic': None, 'peak_source': peak_source}}),
+          flush=True)
+
+
 class Comm:
     """Rank, world size and the two collectives the timing protocol needs."""
     def __init__(self, device, world_size, rank):
@@ -1093,7 +1164,7 @@ def main():
     parser.add_argument('--gpus', type=int, default=1)
     parser.add_argument('--steps', type=int, default=200)
     parser.add_argument('--warmup', type=int, default=10)
-    parser.add_argument('--workload', choices=sorted(WORKLOADS) + ['c4', 'act', 'ce', 'ln'], default='c2')
+    parser.add_argument('--workload', choices=sorted(WORKLOADS) + ['c4', 'act', 'ce', 'ln', 'dxfused'], default='c2')
     parser.add_argument('--only', default=None,
                         help='workload act: time just this entry (e.g. kernel_forward, glu_backward)')
     parser.add_argument('--impl', choices=['b200', 'reference'], default='b200')
@@ -1108,7 +1179,7 @@ def main():
                         help='override the tokens per GPU (profiling of reduced cases)')
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.workload in ('c4', 'act', 'ce', 'ln'):
+    if args.workload in ('c4', 'act', 'ce', 'ln', 'dxfused'):
         if args.impl == 'reference':
             print(json.dumps({'impl': 'reference', 'unavailable': f'{args.workload} has no CPU arm; use c2'}))
             return
@@ -1120,6 +1191,8 @@ def main():
             cross_entropy_loss(args, torch.device('cuda', 0))
         elif args.workload == 'ln':
             layer_norm(args, torch.device('cuda', 0))
+        elif args.workload == 'dxfused':
+            fused_input_gradient(args, torch.device('cuda', 0))
         else:
             activation_layer(args, torch.device('cuda', 0))
         return

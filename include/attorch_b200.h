@@ -387,6 +387,26 @@ int ab200_cross_entropy_backward(const void* loss_grad, int loss_grad_dtype, con
                                  int weight_dtype, int grad_dtype, void* stream);
 
 /*
+ * Input gradient with the activation gradient formed in the operand path, as one kernel:
+ *     dx[M, K] = (dy[M, N] (.) derivative[M, N]) * w[K, N]^T
+ * where `derivative` is act'(Z) as ab200_linear_forward stored it (AB200_FLAG_SAVE_DERIVATIVE).  It
+ * stands for act_func_backward_kernel followed by `pre_act_grad @ weight.T` (attorch/linear_layer.py:
+ * 136-153) without the pass that writes pre_act_grad: the products are rounded to bf16 as that pass
+ * rounds them, written to tensor memory and read from there as the A operand of tcgen05.mma (see
+ * csrc/dx_fused.cu).  The bias gradient is not part of it.  The layer's backward does not use this entry
+ * point: it was measured slower than the two kernels it replaces; it is kept so that the measurement can
+ * be repeated (bench.py --workload dxfused).
+ *   dy          [M, N] bf16, row pitch ld_dy;  derivative [M, N] fp16 or bf16 (derivative_dtype), pitch ld_d
+ *   w           [K, N] bf16 (the layer's [in, out] weight), pitch ld_w
+ *   dx          [M, K] bf16 or fp32 (dx_dtype), pitch ld_dx
+ *   N a multiple of 64; dy, derivative and w 16-byte aligned with pitches that are multiples of 8 elements
+ *   status      device word, required (bounded waits report AB200_DEV_TIMEOUT_* there)
+ */
+int ab200_linear_backward_input_fused(const void* dy, const void* derivative, const void* w, void* dx, int64_t M,
+                                      int64_t K, int64_t N, int64_t ld_dy, int64_t ld_d, int64_t ld_w,
+                                      int64_t ld_dx, int derivative_dtype, int dx_dtype, int* status, void* stream);
+
+/*
  * Layer normalisation over the rows of [rows, feat], the step in front of a transformer block's first
  * projection (the caller: examples/wikitext-2/gpt.py:82).  Replaces layer_norm_forward_kernel
  * (attorch/layer_norm_kernels.py:14-103, launched at attorch/layer_norm_layer.py:74-82):
