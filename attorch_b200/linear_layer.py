@@ -22,6 +22,7 @@ _DTYPE_IDS = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: 
 
 # Per (device index, stream) scratch: a grow-only workspace and the device status word.
 _scratch: Dict[Tuple[int, int], Dict[str, Tensor]] = {}
+_scratch_clock = 0
 
 # Flags forwarded to every GEMM entry point (tests use them to pin a kernel family).
 _gemm_flags = 0
@@ -98,11 +99,14 @@ def _ptr(tensor: Optional[Tensor]) -> Optional[int]:
 def _stream_scratch(device: torch.device) -> Dict[str, Tensor]:
     key = (device.index if device.index is not None else torch.cuda.current_device(),
            torch.cuda.current_stream(device).cuda_stream)
+    global _scratch_clock
     entry = _scratch.get(key)
     if entry is None:
         entry = {'status': torch.zeros(1, dtype=torch.int32, device=device),
                  'workspace': torch.empty(0, dtype=torch.uint8, device=device)}
         _scratch[key] = entry
+    _scratch_clock += 1
+    entry['used'] = _scratch_clock
     return entry
 
 
@@ -132,13 +136,33 @@ def check_status(device: Optional[torch.device] = None) -> None:
     (the device status word of include/attorch_b200.h).  The layer never synchronises on its
     own; call this where the program synchronises anyway.
     """
-    for (index, _), entry in list(_scratch.items()):
-        if device is not None and device.index is not None and device.index != index:
+    failure = None
+    for key, entry in list(_scratch.items()):
+        if device is not None and device.index is not None and device.index != key[0]:
             continue
-        code = int(entry['status'].item())
-        if code != 0:
+        code = int(entry['status'].item())          # synchronises with the stream that last used the entry
+        if code != 0 and failure is None:
             entry['status'].zero_()
-            raise _lib.LibraryError(f'device status {code}: {_lib.error_string(code)}')
+            failure = code
+    _trim_scratch()
+    if failure is not None:
+        raise _lib.LibraryError(f'device status {failure}: {_lib.error_string(failure)}')
+
+
+_MAX_SCRATCH_ENTRIES = 32
+
+
+def _trim_scratch() -> None:
+    """
+    Drops the scratch entries (status word, workspace) of streams that have not been used for longest once
+    there are more than _MAX_SCRATCH_ENTRIES of them.  Called from check_status(), after every status word
+    has been read, i.e. when no kernel that could still write one is in flight.
+    """
+    if len(_scratch) <= _MAX_SCRATCH_ENTRIES:
+        return
+    by_age = sorted(_scratch.items(), key=lambda item: item[1].get('used', 0))
+    for key, _ in by_age[:len(_scratch) - _MAX_SCRATCH_ENTRIES]:
+        del _scratch[key]
 
 
 def _require_cuda(tensor: Tensor, what: str) -> None:

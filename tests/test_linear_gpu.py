@@ -513,3 +513,27 @@ def test_deferred_input_gradient():
         results.append((xg.grad.cpu(), layer.weight.grad.cpu(), layer.bias.grad.cpu()))
     for plain, deferred in zip(*results):
         assert torch.equal(plain, deferred)
+
+
+@pytest.mark.gpu
+def test_scratch_of_idle_streams_is_trimmed():
+    """Per-stream scratch (status word, workspace) does not grow without bound: check_status() keeps the
+    most recently used entries only, and a trimmed stream gets a fresh entry when it is used again."""
+    import attorch_b200
+    from attorch_b200 import linear_layer
+    layer = attorch_b200.Linear(64, 64, act_func='relu')
+    x = torch.randn(32, 64, device='cuda')
+    streams = [torch.cuda.Stream() for _ in range(linear_layer._MAX_SCRATCH_ENTRIES + 8)]
+    expected = layer(x)
+    for stream in streams:
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            y = layer(x)
+        torch.cuda.current_stream().wait_stream(stream)
+        assert torch.equal(y, expected)
+    assert len(linear_layer._scratch) > linear_layer._MAX_SCRATCH_ENTRIES
+    attorch_b200.check_status()
+    assert len(linear_layer._scratch) == linear_layer._MAX_SCRATCH_ENTRIES
+    with torch.cuda.stream(streams[0]):                 # the oldest entry was dropped: a new one is made
+        assert torch.equal(layer(x), expected)
+    attorch_b200.check_status()
