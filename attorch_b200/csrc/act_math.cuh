@@ -180,22 +180,85 @@ __device__ __forceinline__ float grad(float x, float p) {
 // forward value and derivative need the same exponential, evaluates it once at v and carries the
 // derivative over to zr with its own derivative, gelu''(v) = phi(v) (2 - v^2): the neglected term is
 // of order (v - zr)^2, four orders of magnitude below the resolution g is stored with.
+//
+// The sequence of roundings is spelled out (no contraction left to the compiler) so that the two-element
+// form below, which uses Blackwell's packed fp32 instructions, gives the same bits.
 template <int A>
 __device__ __forceinline__ void fwd_grad(float v, float zr, float p, float& y, float& g) {
   if constexpr (A == ACT_GELU) {
-    const float e = ex2_approx(-0.72134752f * v * v);               // exp(-v^2 / 2)
-    const float t = rcp_approx(fmaf(0.3275911f * kRsqrt2, fabsf(v), 1.0f));
-    float poly = fmaf(1.061405429f, t, -1.453152027f);
-    poly = fmaf(poly, t, 1.421413741f);
-    poly = fmaf(poly, t, -0.284496736f);
-    poly = fmaf(poly, t, 0.254829592f);
-    const float cdf = 0.5f + copysignf(0.5f - 0.5f * poly * t * e, v);
-    const float pdf = kRsqrt2Pi * e;
-    y = v * cdf;
-    g = fmaf(v, pdf, cdf) + pdf * fmaf(-v, v, 2.0f) * (zr - v);
+    const float vv = __fmul_rn(v, v);
+    const float e = ex2_approx(__fmul_rn(vv, -0.72134752f));                             // exp(-v^2 / 2)
+    const float t = rcp_approx(__fmaf_rn(0.3275911f * kRsqrt2, fabsf(v), 1.0f));
+    float poly = __fmaf_rn(1.061405429f, t, -1.453152027f);
+    poly = __fmaf_rn(poly, t, 1.421413741f);
+    poly = __fmaf_rn(poly, t, -0.284496736f);
+    poly = __fmaf_rn(poly, t, 0.254829592f);
+    const float half_erf = __fmaf_rn(__fmul_rn(__fmul_rn(poly, t), e), -0.5f, 0.5f);    // erf(|v| / sqrt 2) / 2
+    const float cdf = __fadd_rn(0.5f, copysignf(half_erf, v));
+    const float pdf = __fmul_rn(e, kRsqrt2Pi);
+    y = __fmul_rn(v, cdf);
+    const float g1 = __fmaf_rn(v, pdf, cdf);
+    const float q = __fmaf_rn(vv, -1.0f, 2.0f);                                          // 2 - v^2
+    g = __fmaf_rn(__fmul_rn(pdf, q), __fmaf_rn(v, -1.0f, zr), g1);
   } else {
     y = fwd<A>(v, p);
     g = grad<A>(zr, p);
+  }
+}
+
+// Packed fp32 arithmetic (sm_100: two IEEE round-to-nearest operations per instruction).
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<const unsigned long long&>(a)), "l"(reinterpret_cast<const unsigned long long&>(b)),
+        "l"(reinterpret_cast<const unsigned long long&>(c)));
+  return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<const unsigned long long&>(a)), "l"(reinterpret_cast<const unsigned long long&>(b)));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<const unsigned long long&>(a)), "l"(reinterpret_cast<const unsigned long long&>(b)));
+  return d;
+}
+__device__ __forceinline__ float2 both(float c) { return make_float2(c, c); }
+
+// fwd_grad for two elements at once; for gelu the polynomial, the products and the sums run as packed
+// instructions (the two exponentials and reciprocals stay scalar).  Same bits as two calls of fwd_grad.
+template <int A>
+__device__ __forceinline__ void fwd_grad2(float v0, float v1, float zr0, float zr1, float p, float& y0, float& y1,
+                                          float& g0, float& g1) {
+  if constexpr (A == ACT_GELU) {
+    const float2 v = make_float2(v0, v1);
+    const float2 vv = mul2(v, v);
+    const float2 ea = mul2(vv, both(-0.72134752f));
+    const float2 e = make_float2(ex2_approx(ea.x), ex2_approx(ea.y));
+    // Scalar: the absolute value is an operand modifier of the scalar instruction, not an instruction.
+    const float2 t = make_float2(rcp_approx(__fmaf_rn(0.3275911f * kRsqrt2, fabsf(v0), 1.0f)),
+                                 rcp_approx(__fmaf_rn(0.3275911f * kRsqrt2, fabsf(v1), 1.0f)));
+    float2 poly = fma2(both(1.061405429f), t, both(-1.453152027f));
+    poly = fma2(poly, t, both(1.421413741f));
+    poly = fma2(poly, t, both(-0.284496736f));
+    poly = fma2(poly, t, both(0.254829592f));
+    const float2 half_erf = fma2(mul2(mul2(poly, t), e), both(-0.5f), both(0.5f));
+    const float2 cdf = add2(both(0.5f), make_float2(copysignf(half_erf.x, v0), copysignf(half_erf.y, v1)));
+    const float2 pdf = mul2(e, both(kRsqrt2Pi));
+    const float2 y = mul2(v, cdf);
+    const float2 ga = fma2(v, pdf, cdf);
+    const float2 q = fma2(vv, both(-1.0f), both(2.0f));
+    const float2 g = fma2(mul2(pdf, q), fma2(v, both(-1.0f), make_float2(zr0, zr1)), ga);
+    y0 = y.x; y1 = y.y; g0 = g.x; g1 = g.y;
+  } else {
+    fwd_grad<A>(v0, zr0, p, y0, g0);
+    fwd_grad<A>(v1, zr1, p, y1, g1);
   }
 }
 
@@ -253,10 +316,16 @@ template <int N>
 __device__ __forceinline__ void act_fwd_grad(float (&v)[N], const float (&zr)[N], float (&g)[N], int act, float p) {
   dispatch_act(act, [&]<int A>() {
 #pragma unroll
-    for (int i = 0; i < N; ++i) {
+    for (int i = 0; i + 1 < N; i += 2) {
+      float y0, y1;
+      actm::fwd_grad2<A>(v[i], v[i + 1], zr[i], zr[i + 1], p, y0, y1, g[i], g[i + 1]);
+      v[i] = y0;
+      v[i + 1] = y1;
+    }
+    if constexpr (N % 2 == 1) {
       float y;
-      actm::fwd_grad<A>(v[i], zr[i], p, y, g[i]);
-      v[i] = y;
+      actm::fwd_grad<A>(v[N - 1], zr[N - 1], p, y, g[N - 1]);
+      v[N - 1] = y;
     }
   });
 }

@@ -83,6 +83,20 @@ __device__ __forceinline__ float round_through(float v, int dt) {
   return v;
 }
 
+// round_through for two values with one conversion instruction.
+__device__ __forceinline__ void round_through2(float& a, float& b, int dt) {
+  if (dt == DT_BF16) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(&p);
+    a = __uint_as_float(w << 16);
+    b = __uint_as_float(w & 0xFFFF0000u);
+  } else if (dt == DT_F16) {
+    const float2 f = __half22float2(__floats2half2_rn(a, b));
+    a = f.x;
+    b = f.y;
+  }
+}
+
 // Rounds eight fp32 values to T, packed in order into 16 (2-byte T) or 32 (fp32) bytes; two values
 // per conversion instruction for the 2-byte types.
 template <class T>

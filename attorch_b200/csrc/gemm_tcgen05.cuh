@@ -299,11 +299,12 @@ __device__ __forceinline__ void add_bias_chunk(float (&v)[32], const void* bias,
     if (dt == DT_F32) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float4 b = __ldg(reinterpret_cast<const float4*>(p) + i);
-        v[4 * i] += round_through(b.x, round_dt);
-        v[4 * i + 1] += round_through(b.y, round_dt);
-        v[4 * i + 2] += round_through(b.z, round_dt);
-        v[4 * i + 3] += round_through(b.w, round_dt);
+        float4 b = __ldg(reinterpret_cast<const float4*>(p) + i);
+        round_through2(b.x, b.y, round_dt);
+        round_through2(b.z, b.w, round_dt);
+        const float2 lo = actm::add2(make_float2(v[4 * i], v[4 * i + 1]), make_float2(b.x, b.y));
+        const float2 hi = actm::add2(make_float2(v[4 * i + 2], v[4 * i + 3]), make_float2(b.z, b.w));
+        v[4 * i] = lo.x; v[4 * i + 1] = lo.y; v[4 * i + 2] = hi.x; v[4 * i + 3] = hi.y;
       }
     } else {
 #pragma unroll
@@ -711,7 +712,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               // Save act'(Z) instead of Z: backward then needs one multiply per element.
               float zr[32], g[32];
 #pragma unroll
-              for (int i = 0; i < 32; ++i) zr[i] = round_through(v[i], odt);
+              for (int i = 0; i < 32; i += 2) {
+                zr[i] = v[i];
+                zr[i + 1] = v[i + 1];
+                round_through2(zr[i], zr[i + 1], odt);
+              }
               act_fwd_grad(v, zr, g, args.act, args.act_param);
               emit(&tmap_aux, args.aux, args.ld_aux, (args.tma_store & 2) != 0, g, gdt);
             } else {
