@@ -55,7 +55,9 @@ __device__ __forceinline__ float rcp_approx(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float sigmoid(float x) { return rcp_approx(1.0f + ex2_approx(-1.44269504f * x)); }
+__device__ __forceinline__ float sigmoid(float x) {
+  return rcp_approx(__fadd_rn(1.0f, ex2_approx(__fmul_rn(-1.44269504f, x))));
+}
 // tanh as 2*sigmoid(2x) - 1 (act_kernels.py:71-81).
 __device__ __forceinline__ float tanh_(float x) { return 2.0f * sigmoid(2.0f * x) - 1.0f; }
 // erf(x) by Abramowitz & Stegun 7.1.26: 1 - (a1 t + ... + a5 t^5) exp(-x^2), t = 1 / (1 + p |x|);
@@ -93,7 +95,7 @@ __device__ __forceinline__ float fwd(float x, float p) {
   if constexpr (A == ACT_GELU) return x * 0.5f * (1.0f + erf_fast(kRsqrt2 * x));
   if constexpr (A == ACT_GELUAPPROX)
     return x * 0.5f * (1.0f + tanh_(kSqrt2OverPi * x * (1.0f + 0.044715f * x * x)));
-  if constexpr (A == ACT_SILU) return x * sigmoid(x);
+  if constexpr (A == ACT_SILU) return __fmul_rn(x, sigmoid(x));
   if constexpr (A == ACT_RELU6) return fminf(fmaxf(0.0f, x), 6.0f);
   if constexpr (A == ACT_HARDSIGMOID) return fmaxf(0.0f, fminf(1.0f, x / 6.0f + 0.5f));
   if constexpr (A == ACT_HARDTANH) return fmaxf(-1.0f, fminf(1.0f, x));
@@ -145,7 +147,7 @@ __device__ __forceinline__ float grad(float x, float p) {
   }
   if constexpr (A == ACT_SILU) {
     const float s = sigmoid(x);
-    return s * (x * (1.0f - s) + 1.0f);
+    return __fmul_rn(s, __fmaf_rn(x, __fsub_rn(1.0f, s), 1.0f));     // spelled out: fwd_grad2 mirrors it
   }
   if constexpr (A == ACT_RELU6) return (x > 0.0f && x < 6.0f) ? 1.0f : 0.0f;
   if constexpr (A == ACT_HARDSIGMOID) return (x > -3.0f && x < 3.0f) ? (1.0f / 6.0f) : 0.0f;
@@ -255,6 +257,17 @@ __device__ __forceinline__ void fwd_grad2(float v0, float v1, float zr0, float z
     const float2 ga = fma2(v, pdf, cdf);
     const float2 q = fma2(vv, both(-1.0f), both(2.0f));
     const float2 g = fma2(mul2(pdf, q), fma2(v, both(-1.0f), make_float2(zr0, zr1)), ga);
+    y0 = y.x; y1 = y.y; g0 = g.x; g1 = g.y;
+  } else if constexpr (A == ACT_SILU) {
+    // y = v sigmoid(v), g = s (zr (1 - s) + 1) with s = sigmoid(zr): four sigmoids, two packed pairs.
+    const float2 v = make_float2(v0, v1), zr = make_float2(zr0, zr1);
+    const float2 ev = mul2(both(-1.44269504f), v), ez = mul2(both(-1.44269504f), zr);
+    const float2 dv = add2(both(1.0f), make_float2(ex2_approx(ev.x), ex2_approx(ev.y)));
+    const float2 dz = add2(both(1.0f), make_float2(ex2_approx(ez.x), ex2_approx(ez.y)));
+    const float2 sv = make_float2(rcp_approx(dv.x), rcp_approx(dv.y));
+    const float2 sz = make_float2(rcp_approx(dz.x), rcp_approx(dz.y));
+    const float2 y = mul2(v, sv);
+    const float2 g = mul2(sz, fma2(zr, fma2(sz, both(-1.0f), both(1.0f)), both(1.0f)));
     y0 = y.x; y1 = y.y; g0 = g.x; g1 = g.y;
   } else {
     fwd_grad<A>(v0, zr0, p, y0, g0);
