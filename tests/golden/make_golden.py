@@ -16,7 +16,7 @@ Each case is stored as one .npz with the inputs (or the seed that regenerates th
 checksum) and the reference's output, dX, dW and db; the standalone activation layers go into
 act_layers_fp32.npz, the gated linear unit into glu_fp32.npz, bf16 runs of both (element-wise
 kernels only) into elementwise_bf16.npz, the cross-entropy loss into cross_entropy_fp32.npz, layer
-normalisation into layer_norm.npz.  The linear layer itself is not generated in bf16: the
+normalisation into layer_norm.npz and, in bf16, layer_norm_bf16.npz.  The linear layer itself is not generated in bf16: the
 interpreter's bf16 dot product returns garbage.
 """
 
@@ -170,6 +170,7 @@ def main():
     elementwise_bf16_goldens(attorch)
     cross_entropy_goldens(attorch)
     layer_norm_goldens(attorch)
+    layer_norm_bf16_goldens(attorch)
 
 
 ACT_LAYERS = [('Sigmoid', {}), ('LogSigmoid', {}), ('Tanh', {}), ('ReLU', {}), ('GELU', {}),
@@ -386,6 +387,52 @@ def layer_norm_goldens(attorch):
                 data[f'b_{case}'], data[f'db_{case}'] = to_np(layer.bias), to_np(layer.bias.grad)
     np.savez_compressed(OUT_DIR / 'layer_norm.npz', **data)
     print('wrote layer_norm.npz')
+
+
+LAYER_NORM_BF16_CASES = [
+    # shape, parameter dtype, bias
+    ((7, 40), 'bfloat16', True),
+    ((33, 200), 'bfloat16', False),
+    ((4, 6, 64), 'float32', True),
+    ((5, 1040), 'bfloat16', True),
+]
+
+
+def layer_norm_bf16_goldens(attorch):
+    """
+    bf16 runs of the reference's layer normalisation (its kernels have no dot product, so the interpreter
+    runs them): bf16 inputs and upstream gradients, bf16 or fp32 parameters.  As with the other bf16 vectors,
+    the interpreter stores fp32 results as bf16 by dropping the low 16 bits where a GPU rounds to nearest, so
+    these pin the fp32 value in front of the store.  Values are saved as fp32 arrays holding bf16 numbers.
+    """
+    from attorch.layer_norm_kernels import layer_norm_backward_kernel, layer_norm_forward_kernel
+    layer_norm_forward_kernel.configs = layer_norm_forward_kernel.configs[:1]
+    layer_norm_backward_kernel.configs = layer_norm_backward_kernel.configs[:1]
+    gen = torch.Generator().manual_seed(10)
+    data = {}
+    for case, (shape, param_dtype_name, bias) in enumerate(LAYER_NORM_BF16_CASES):
+        param_dtype = getattr(torch, param_dtype_name)
+        rows = int(np.prod(shape[:-1]))
+        x = torch.randn(shape, generator=gen) * (torch.rand(rows, generator=gen) * 3 + 0.2).view(*shape[:-1], 1) \
+            + (torch.randn(rows, generator=gen) * 2).view(*shape[:-1], 1)
+        x = x.bfloat16()
+        dy = torch.randn(shape, generator=gen).bfloat16()
+        layer = attorch.LayerNorm(shape[-1], bias=bias, device='cpu', dtype=param_dtype)
+        with torch.no_grad():
+            layer.weight.copy_(torch.randn(shape[-1], generator=gen))
+            if bias:
+                layer.bias.copy_(torch.randn(shape[-1], generator=gen))
+        xin = x.clone().requires_grad_(True)
+        y = layer(xin)
+        y.backward(dy)
+        assert y.dtype is torch.bfloat16 and xin.grad.dtype is torch.bfloat16
+        data[f'x_{case}'], data[f'dy_{case}'] = to_np(x), to_np(dy)
+        data[f'y_{case}'], data[f'dx_{case}'] = to_np(y), to_np(xin.grad)
+        data[f'w_{case}'], data[f'dw_{case}'] = to_np(layer.weight), to_np(layer.weight.grad)
+        if bias:
+            data[f'b_{case}'], data[f'db_{case}'] = to_np(layer.bias), to_np(layer.bias.grad)
+    np.savez_compressed(OUT_DIR / 'layer_norm_bf16.npz', **data)
+    print('wrote layer_norm_bf16.npz')
 
 
 if __name__ == '__main__':

@@ -112,3 +112,17 @@ LAYER_NORM_CASES = [
     ((9, 200), 'float16', True, False, 1e-5),
     ((9, 200), 'float16', False, False, 1e-6),
 ]
+
+# (shape, parameter dtype, bias): the bf16 layer-normalisation cases of tests/golden/make_golden.py.
+LAYER_NORM_BF16_CASES = [
+    ((7, 40), 'bfloat16', True),
+    ((33, 200), 'bfloat16', False),
+    ((4, 6, 64), 'float32', True),
+    ((5, 1040), 'bfloat16', True),
+]
+
+
+def truncate_to_bf16(t):
+    """fp32 -> bf16 by dropping the low 16 bits, as Triton's CPU interpreter stores (a GPU rounds to nearest)."""
+    import torch
+    return (t.float().contiguous().view(torch.int32) & -65536).view(torch.float32)

@@ -12,7 +12,7 @@ import pytest
 import torch
 
 from oracle import linear_oracle as oracle
-from tests.helpers import GOLDEN_DIR, LAYER_NORM_CASES
+from tests.helpers import GOLDEN_DIR, LAYER_NORM_BF16_CASES, LAYER_NORM_CASES
 
 pytestmark = pytest.mark.gpu
 
@@ -319,3 +319,29 @@ def test_staged_and_register_backward_agree(rows, feat, x_dtype, dy_dtype):
         torch.testing.assert_close(db, edb, rtol=1e-4, atol=1e-4 * max(1.0, float(edb.abs().max())))
     torch.testing.assert_close(outs[0][0].float(), outs[1][0].float(), rtol=TOL[dx_dtype]['rtol'],
                                atol=TOL[dx_dtype]['atol'] * scale)
+
+
+@pytest.mark.parametrize('case', range(len(LAYER_NORM_BF16_CASES)))
+def test_reference_bf16_vectors(case):
+    """
+    Against the reference's own bf16 runs (tests/golden/layer_norm_bf16.npz).  The interpreter that made them
+    stores fp32 values as bf16 by truncation, a GPU rounds to nearest: the kernel's value is the vector's or
+    the next bf16 number away from zero, never more than one step off.
+    """
+    shape, param_dtype_name, bias = LAYER_NORM_BF16_CASES[case]
+    raw = np.load(GOLDEN_DIR / 'layer_norm_bf16.npz')
+    g = {k: torch.from_numpy(np.asarray(raw[k])) for k in raw.files if k.endswith(f'_{case}')}
+    param_dtype = DTYPES[param_dtype_name]
+    layer = make_layer(shape[-1], 1e-5, True, bias, param_dtype, g[f'w_{case}'], g.get(f'b_{case}'))
+    y, dx, dw, db = run(layer, g[f'x_{case}'].bfloat16(), g[f'dy_{case}'].bfloat16())
+    assert y.dtype is torch.bfloat16 and dx.dtype is torch.bfloat16 and dw.dtype is param_dtype
+    for name, got, ref in (('y', y.float(), g[f'y_{case}']), ('dx', dx.float(), g[f'dx_{case}'])):
+        step = torch.maximum(ref.abs(), torch.tensor(1e-30)) * 2.0 ** -7
+        assert bool(((got - ref).abs() <= step).all()), name
+        away = (got.abs() >= ref.abs()) | ((got - ref).abs() <= step * 1e-3)
+        assert away.float().mean() >= 0.98, name      # rounding to nearest never lands below a truncated value
+    scale = max(1.0, float(g[f'dw_{case}'].abs().max()))
+    tol = dict(rtol=1e-4, atol=1e-4 * scale) if param_dtype is torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2 * scale)
+    torch.testing.assert_close(dw.float(), g[f'dw_{case}'], **tol)
+    if bias:
+        torch.testing.assert_close(db.float(), g[f'db_{case}'], **tol)

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from oracle import linear_oracle as oracle
-from tests.helpers import GOLDEN_DIR, LAYER_NORM_CASES
+from tests.helpers import GOLDEN_DIR, LAYER_NORM_BF16_CASES, LAYER_NORM_CASES, truncate_to_bf16
 
 
 def load():
@@ -74,3 +74,33 @@ def test_module_surface_without_gpu():
     assert attorch_b200.nn.LayerNorm is attorch_b200.LayerNorm
     fused = attorch_b200.LayerNormLinear(norm, attorch_b200.Linear(8, 16, act_func='gelu', device='cpu'))
     assert sorted(fused.state_dict()) == ['linear.bias', 'linear.weight', 'norm.weight']
+
+
+@pytest.mark.parametrize('case', range(len(LAYER_NORM_BF16_CASES)))
+def test_against_reference_bf16_vectors(case):
+    """
+    bf16 runs of the reference (tests/golden/layer_norm_bf16.npz).  The interpreter stores by truncation,
+    so what is pinned is the oracle's fp32 value in front of the store: truncated the same way it equals the
+    reference's output bit for bit, except where the two orders of the row sums put the fp32 value on
+    different sides of a bf16 boundary (a handful of elements, then one bf16 step apart).
+    """
+    shape, param_dtype_name, bias = LAYER_NORM_BF16_CASES[case]
+    raw = np.load(GOLDEN_DIR / 'layer_norm_bf16.npz')
+    g = {k: torch.from_numpy(np.asarray(raw[k])) for k in raw.files if k.endswith(f'_{case}')}
+    x, dy = g[f'x_{case}'].bfloat16(), g[f'dy_{case}'].bfloat16()
+    w = g[f'w_{case}'].to(getattr(torch, param_dtype_name))
+    b = g[f'b_{case}'].to(w.dtype) if bias else None
+    y32, mean, inv_std = oracle.layer_norm_forward(x, w, b, output_dtype=torch.float32)
+    dx32, dw32, db32 = oracle.layer_norm_backward(dy, x, mean, inv_std, w, bias, grad_dtype=torch.float32)
+    for name, ours, ref in (('y', y32, g[f'y_{case}']), ('dx', dx32, g[f'dx_{case}'])):
+        got = truncate_to_bf16(ours)
+        same = (got == ref)
+        assert same.float().mean() >= 0.995, name
+        step = torch.maximum(ref.abs(), torch.tensor(1e-30)) * 2.0 ** -7          # one bf16 step, generously
+        assert bool(((got - ref).abs() <= step)[~same].all()), name
+    # Parameter gradients: fp32 sums, cast by the engine to the parameter's dtype (rounding to nearest).
+    scale = max(1.0, float(g[f'dw_{case}'].abs().max()))
+    tol = dict(rtol=1e-5, atol=1e-5 * scale) if w.dtype is torch.float32 else dict(rtol=8e-3, atol=8e-3 * scale)
+    torch.testing.assert_close(dw32.to(w.dtype).float(), g[f'dw_{case}'], **tol)
+    if bias:
+        torch.testing.assert_close(db32.to(w.dtype).float(), g[f'db_{case}'], **tol)
