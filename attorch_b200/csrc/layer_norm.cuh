@@ -26,6 +26,7 @@
 #pragma once
 #include <type_traits>
 
+#include "act_math.cuh"
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -470,10 +471,11 @@ ln_backward_staged_kernel(const TDy* __restrict__ dy, long long lddy, const TIn*
     for (int j = 0; j < V; ++j)
       wc[i * V + j] = (w != nullptr && g < groups) ? load_as_f32(w, param_dtype, g * V + j) : 1.0f;
   }
-  float wacc[kParams ? kLnCache : 1], bacc[kParams ? kLnCache : 1];
+  // Two elements per instruction throughout (packed fp32: same roundings as the one-element forms).
+  float2 wacc[kParams ? kLnCache / 2 : 1], bacc[kParams ? kLnCache / 2 : 1];
   if constexpr (kParams) {
 #pragma unroll
-    for (int i = 0; i < kLnCache; ++i) wacc[i] = bacc[i] = 0.0f;
+    for (int i = 0; i < kLnCache / 2; ++i) wacc[i] = bacc[i] = make_float2(0.0f, 0.0f);
   }
 
   long long failed_at = -1;
@@ -494,8 +496,9 @@ ln_backward_staged_kernel(const TDy* __restrict__ dy, long long lddy, const TIn*
     const bool ok = wait(stage_index, stage_parity);
     const unsigned char* stage = ln_stage_smem + static_cast<size_t>(stage_index) * stage_bytes;
 
-    float pc[kLnCache], gc[kLnCache];
-    float s1 = 0.0f, s2 = 0.0f;
+    float2 pc[kLnCache / 2], gc[kLnCache / 2];
+    float2 s1p = make_float2(0.0f, 0.0f), s2p = make_float2(0.0f, 0.0f);
+    const float2 neg_mu = actm::both(-mu), rs2 = actm::both(rs);
 #pragma unroll
     for (int i = 0; i < kG; ++i) {
       const int g = t + i * R;
@@ -503,23 +506,30 @@ ln_backward_staged_kernel(const TDy* __restrict__ dy, long long lddy, const TIn*
         const LnRaw<TIn, V> xq = *reinterpret_cast<const LnRaw<TIn, V>*>(stage + static_cast<size_t>(g) * V * sizeof(TIn));
         const LnRaw<TDy, V> gq =
             *reinterpret_cast<const LnRaw<TDy, V>*>(stage + xbytes + static_cast<size_t>(g) * V * sizeof(TDy));
-        ln_unpack<TIn, V>(xq, &pc[i * V]);
-        ln_unpack<TDy, V>(gq, &gc[i * V]);
+        float xv[V], gv[V];
+        ln_unpack<TIn, V>(xq, xv);
+        ln_unpack<TDy, V>(gq, gv);
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          const int e = i * V + j;
-          const float p = (pc[e] - mu) * rs;
-          pc[e] = p;
+        for (int j = 0; j < V; j += 2) {
+          const int e = (i * V + j) / 2;
+          const float2 p = actm::mul2(actm::add2(make_float2(xv[j], xv[j + 1]), neg_mu), rs2);
+          float2 gg = make_float2(gv[j], gv[j + 1]);
           if constexpr (kParams) {
-            wacc[e] += gc[e] * p;
-            bacc[e] += gc[e];
+            wacc[e] = actm::fma2(gg, p, wacc[e]);
+            bacc[e] = actm::add2(bacc[e], gg);
           }
-          gc[e] *= wc[e];
-          s1 += p * gc[e];
-          s2 += gc[e];
+          gg = actm::mul2(gg, make_float2(wc[i * V + j], wc[i * V + j + 1]));
+          s1p = actm::fma2(p, gg, s1p);
+          s2p = actm::add2(s2p, gg);
+          pc[e] = p;
+          gc[e] = gg;
         }
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; j += 2) pc[(i * V + j) / 2] = gc[(i * V + j) / 2] = make_float2(0.0f, 0.0f);
       }
     }
+    float s1 = s1p.x + s1p.y, s2 = s2p.x + s2p.y;
     // Row sums over the block; the barrier also tells whether any thread's wait ran out.
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -541,7 +551,7 @@ ln_backward_staged_kernel(const TDy* __restrict__ dy, long long lddy, const TIn*
     phase ^= 1;
     // All threads have read this stage: refill it.
     if (t == 0 && k + stages < n) issue(k + stages, stage_index);
-    const float c1 = s1 / feat, c2 = s2 / feat;
+    const float2 c1 = actm::both(s1 / feat), c2 = actm::both(s2 / feat);
     TDx* dr = dx + row * lddx;
 #pragma unroll
     for (int i = 0; i < kG; ++i) {
@@ -549,7 +559,13 @@ ln_backward_staged_kernel(const TDy* __restrict__ dy, long long lddy, const TIn*
       if (g < groups) {
         float o[V];
 #pragma unroll
-        for (int j = 0; j < V; ++j) o[j] = rs * (gc[i * V + j] - (pc[i * V + j] * c1 + c2));
+        for (int j = 0; j < V; j += 2) {
+          const int e = (i * V + j) / 2;
+          // rs * (g - (p c1 + c2))
+          const float2 r = actm::mul2(rs2, actm::fma2(actm::fma2(pc[e], c1, c2), actm::both(-1.0f), gc[e]));
+          o[j] = r.x;
+          o[j + 1] = r.y;
+        }
         ln_store<TDx, V>(dr + g * V, o);
       }
     }
@@ -578,9 +594,16 @@ ln_backward_staged_kernel(const TDy* __restrict__ dy, long long lddy, const TIn*
       const int g = t + i * R;
       if (g < groups) {
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          wpart[static_cast<long long>(blockIdx.x) * F + g * V + j] = wacc[i * V + j];
-          if (bpart != nullptr) bpart[static_cast<long long>(blockIdx.x) * F + g * V + j] = bacc[i * V + j];
+        for (int j = 0; j < V; j += 2) {
+          const int e = (i * V + j) / 2;
+          float* wp = wpart + static_cast<long long>(blockIdx.x) * F + g * V + j;
+          wp[0] = wacc[e].x;
+          wp[1] = wacc[e].y;
+          if (bpart != nullptr) {
+            float* bp = bpart + static_cast<long long>(blockIdx.x) * F + g * V + j;
+            bp[0] = bacc[e].x;
+            bp[1] = bacc[e].y;
+          }
         }
       }
     }
