@@ -345,3 +345,68 @@ def test_reference_bf16_vectors(case):
     torch.testing.assert_close(dw.float(), g[f'dw_{case}'], **tol)
     if bias:
         torch.testing.assert_close(db.float(), g[f'db_{case}'], **tol)
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16], ids=str)
+def test_full_size_properties(dtype):
+    """
+    The bench's shape, 8192 rows of 4096 features, through properties that need no CPU product: normalised
+    rows have mean 0 and mean square var / (var + eps); each row of dx sums to 0; a sample of rows of dx equals
+    the formula evaluated in float64; dw and db equal float64 column sums taken from the layer's own normalised
+    output; backward is linear in the upstream gradient.
+    """
+    import attorch_b200
+    rows, feat = 8192, 4096
+    gen = torch.Generator(device='cuda').manual_seed(1)
+    x = (torch.randn(rows, feat, device='cuda', generator=gen) * (torch.rand(rows, 1, device='cuda', generator=gen) * 3 + 0.2)
+         + torch.randn(rows, 1, device='cuda', generator=gen) * 2).to(dtype)
+    dy1 = torch.randn(rows, feat, device='cuda', generator=gen).to(dtype)
+    dy2 = torch.randn(rows, feat, device='cuda', generator=gen).to(dtype)
+    w = torch.randn(feat, device='cuda', generator=gen).to(dtype)
+    unit = 2.0 ** -8 if dtype is torch.bfloat16 else 2.0 ** -22          # about one rounding of a value near 1
+
+    plain = attorch_b200.LayerNorm(feat, elementwise_affine=False, dtype=dtype)
+    xin = x.clone().requires_grad_(True)
+    p = plain(xin)
+    p64 = p.detach().double()
+    x64 = x.double()
+    mu, var = x64.mean(dim=1), x64.var(dim=1, unbiased=False)
+    # A row far from zero loses |mean| / std of the fp32 resolution in (x - mean); mean square is var / (var + eps).
+    slack = 32 * unit * (1 + mu.abs() / var.sqrt())
+    assert bool((p64.mean(dim=1).abs() <= slack).all())
+    assert bool(((p64.pow(2).mean(dim=1) - var / (var + 1e-5)).abs() <= 2 * slack).all())
+
+    layer = attorch_b200.LayerNorm(feat, dtype=dtype)
+    with torch.no_grad():
+        layer.weight.copy_(w)
+
+    def backward(dy):
+        layer.zero_grad()
+        xg = x.clone().requires_grad_(True)
+        layer(xg).backward(dy)
+        return xg.grad.double(), layer.weight.grad.double(), layer.bias.grad.double()
+
+    dx1, dw1, db1 = backward(dy1)
+    g = (w.double() * dy1.double())
+    rs = 1.0 / (var + 1e-5).sqrt()
+    row_scale = rs * g.abs().max(dim=1).values                         # magnitude of the terms of a row of dx
+    scale = float(row_scale.max())
+    # Each row of dx sums to zero (the mean of g and its projection on the normalised row are taken out).
+    assert bool((dx1.sum(dim=1).abs() <= (1e-3 if dtype is torch.float32 else 0.3) * row_scale).all())
+    # A sample of rows against the formula in float64.
+    idx = torch.arange(0, rows, 127, device='cuda')
+    ps, gs = ((x64[idx] - mu[idx, None]) * rs[idx, None]), g[idx]
+    ref_dx = rs[idx, None] * (gs - (ps * (ps * gs).mean(dim=1, keepdim=True) + gs.mean(dim=1, keepdim=True)))
+    assert bool(((dx1[idx] - ref_dx).abs() <= 16 * unit * row_scale[idx, None] + 1e-6).all())
+    # Parameter gradients against float64 sums over the rows (p from the layer's own forward: one rounding off).
+    ref_dw = (dy1.double() * p64).sum(dim=0)
+    ref_db = dy1.double().sum(dim=0)
+    col = float((dy1.double().abs() * p64.abs()).sum(dim=0).max())
+    assert float((dw1 - ref_dw).abs().max()) <= 4 * unit * col
+    assert float((db1 - ref_db).abs().max()) <= 4 * unit * float(dy1.double().abs().sum(dim=0).max())
+    # Linearity in the upstream gradient.
+    dx2, dw2, _ = backward(dy2)
+    dx12, dw12, _ = backward((dy1.float() * 0.5 + dy2.float()).to(dtype))
+    assert float((dx12 - (0.5 * dx1 + dx2)).abs().max()) <= 128 * unit * scale
+    assert float((dw12 - (0.5 * dw1 + dw2)).abs().max()) <= 16 * unit * col
+    attorch_b200.check_status()
